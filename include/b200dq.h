@@ -1,0 +1,125 @@
+/* b200dq — C ABI of the B200 (sm_100a) low-bit dequantize-GEMM library.
+ *
+ * The reference (tile-ai/tilelang) exposes every JIT-compiled kernel through a
+ * three-symbol C convention that its ctypes/Cython adapters bind:
+ *     int init(void); int call(<device pointers, scalars>, cudaStream_t);
+ *     const char* get_last_error(void);
+ * (tilelang/jit/adapter/wrapper.py:60-86, used from
+ *  tilelang/jit/adapter/cython/adapter.py:135-139, 338-345). This header keeps
+ * that convention with one `call`-style entry point per kernel family.
+ *
+ * Rules shared by every entry point:
+ *   - returns 0 on success, -1 on error; the message is in b200dq_get_last_error();
+ *   - never throws, never synchronises the device, never allocates device memory
+ *     (scratch is passed in by the caller), launches on the given stream;
+ *   - all pointers are device pointers unless stated otherwise; inputs are only
+ *     borrowed for the duration of the (asynchronous) launch.
+ */
+#ifndef B200DQ_H_
+#define B200DQ_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Weight formats of the private, pre-packed device layout (see pack entry points). */
+enum b200dq_weight_format {
+  B200DQ_WF_U4_SZ = 0,    /* uint4 + per-group scale/zero term; fp16/bf16 activations   */
+  B200DQ_WF_U4_RAW = 1,   /* uint4, weight = q (no scale)                               */
+  B200DQ_WF_S4_RAW = 2,   /* int4 stored as q + 8, weight = q (no scale)                */
+  B200DQ_WF_FP4_E8M0 = 3, /* e2m1 codes + one e8m0 exponent byte per 32 K elements      */
+  B200DQ_WF_I2_I8 = 4,    /* 2-bit codes -> int8 (minus code_bias); int8 activations    */
+  B200DQ_WF_I4_I8 = 5     /* 4-bit codes -> int8 (minus code_bias); int8 activations    */
+};
+enum b200dq_act_type { B200DQ_ACT_F16 = 0, B200DQ_ACT_BF16 = 1, B200DQ_ACT_I8 = 2 };
+enum b200dq_out_type { B200DQ_OUT_F16 = 0, B200DQ_OUT_BF16 = 1, B200DQ_OUT_F32 = 2, B200DQ_OUT_I32 = 3 };
+enum b200dq_gemm_flags {
+  B200DQ_GF_TRANS_C = 1,   /* write C^T (N x M), the orientation of the reference's fp4/w4a8 examples */
+  B200DQ_GF_HAS_BIAS = 2,  /* add bias[M][N] (output dtype) before the cast                           */
+  B200DQ_GF_ROW_SCALE = 4  /* integer path: acc * row_scale[m] * tensor_scale before the cast          */
+};
+
+/* Replaces init() of tilelang/jit/adapter/wrapper.py:60-70: selects nothing, but
+ * raises the dynamic shared-memory limit of every kernel, resolves the driver's
+ * tensor-map encoder and allocates the 16-byte device status word of the current
+ * device. Idempotent, thread-safe, once per device. */
+int b200dq_init(void);
+
+/* Replaces get_last_error() of tilelang/jit/adapter/wrapper.py:72-76. The buffer
+ * is thread-local and valid until the next failing call on the same thread. */
+const char* b200dq_get_last_error(void);
+
+/* Library ABI version (bumped when a struct below changes). */
+int b200dq_version(void);
+
+/* Arguments of the dequantize-GEMM  C[M,N] = A[M,K] * dequant(W[N,K])^T. */
+typedef struct b200dq_gemm_args {
+  const void* a;            /* activations, row-major (M, K), act_type                          */
+  const void* wp;           /* packed weights from b200dq_pack_*                                */
+  const void* sz;           /* scale table from b200dq_pack_* (NULL for the RAW / integer formats) */
+  const void* bias;         /* optional (M, N) bias in the output dtype, or NULL                */
+  const float* row_scale;   /* optional per-token factor (M), or NULL                           */
+  void* c;                  /* output (M, N) or, with TRANS_C, (N, M)                           */
+  void* workspace;          /* scratch of at least b200dq_gemm_workspace_bytes() bytes          */
+  size_t workspace_bytes;
+  int32_t M, N, K;
+  int32_t group_size;       /* K elements per scale group (U4_SZ); 32 for FP4_E8M0; else ignored */
+  int32_t weight_format;    /* enum b200dq_weight_format */
+  int32_t act_type;         /* enum b200dq_act_type      */
+  int32_t out_type;         /* enum b200dq_out_type      */
+  int32_t flags;            /* enum b200dq_gemm_flags    */
+  float tensor_scale;       /* used with ROW_SCALE       */
+  uint32_t code_bias;       /* bytewise bias of the integer decoders, e.g. 0x02020202 */
+  int32_t fp4_exp_bias;     /* 127: OCP e8m0 exponent bytes; 0: raw power-of-two exponents */
+  int32_t token_tile;       /* 0 = choose; else 16, 32, 64, 128 or 256 tokens per CTA tile */
+  int32_t max_ctas;         /* 0 = one per SM; else an upper bound on the grid */
+} b200dq_gemm_args;
+
+/* Replaces call(...) of the kernels generated from
+ *   examples/dequantize_gemm/example_dequant_gemm_fine_grained.py:16-90,
+ *   examples/dequantize_gemm/example_dequant_gemm_bf16_mxfp4_hopper.py:80-378,
+ *   examples/dequantize_gemm/example_dequant_gemm_fp4_hopper.py:108-220,
+ *   examples/dequantize_gemm/example_dequant_gemm_w4a8.py:85-149,
+ *   examples/dequantize_gemm/example_dequant_gemv_fp16xint4.py:11-155,
+ *   examples/bitnet-1.58b/kernel_benchmark/tilelang_bitnet_158_int8xint2_{decode,prefill}.py
+ * for one B200. */
+int b200dq_gemm(const b200dq_gemm_args* args, void* cuda_stream);
+
+/* Scratch bytes b200dq_gemm needs for these sizes (stream-K partial tiles). */
+size_t b200dq_gemm_workspace_bytes(int32_t M, int32_t N, int32_t K, int32_t weight_format,
+                                   int32_t act_type, int32_t token_tile, int32_t max_ctas);
+
+/* Bytes of the packed weight image / scale table for an (N, K) weight. */
+size_t b200dq_packed_weight_bytes(int32_t N, int32_t K, int32_t weight_format);
+size_t b200dq_packed_scale_bytes(int32_t N, int32_t K, int32_t group_size, int32_t weight_format);
+
+/* Offline layout transform, on the device: natural (N, K*bits/8) little-endian
+ * codes (element k in bits [(k % epb)*bits ...] of byte k / epb — the layout of
+ * general_compress, examples/dequantize_gemm/quantize/utils.py:50-67) -> the
+ * tiled, pre-interleaved image the GEMM streams with one bulk copy per k-block.
+ * Plays the role of interleave_weight (quantize/utils.py:71-125) plus the tile
+ * re-ordering the reference leaves to TMA/layout inference. `bits` is 2 or 4. */
+int b200dq_pack_weights(const void* q_natural, void* wp, int32_t N, int32_t K, int32_t bits,
+                        int32_t weight_format, void* cuda_stream);
+
+/* Scale/zero table for U4_SZ: scales and zeros are (N, K/group) in the
+ * activation dtype (zeros may be NULL = fixed zero-point 8); the output holds
+ * per (group, row) the pair {s, (8 - z) * s}. */
+int b200dq_pack_scales_u4(const void* scales, const void* zeros, void* sz, int32_t N, int32_t K,
+                          int32_t group_size, int32_t act_type, void* cuda_stream);
+
+/* Exponent table for FP4_E8M0: (N, K/32) bytes -> [K/64][N_pad] byte pairs. */
+int b200dq_pack_scales_e8m0(const void* exps, void* sz, int32_t N, int32_t K, void* cuda_stream);
+
+/* Reads the device status word of the current device (synchronises `stream`).
+ * Returns 0 if no kernel recorded an error since the last reset, else -1 with a
+ * message naming the wait that gave up; resets the word. */
+int b200dq_check_status(void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200DQ_H_ */

@@ -1,0 +1,369 @@
+// C ABI of the library (declared in include/b200dq.h): argument validation,
+// tensor-map encoding, stream-K schedule and kernel launch.
+//
+// Plays the role of the reference's generated host stub + runtime helpers:
+// argument checks (docs/compiler_internals/tensor_checks.md:19-60), tensor-map
+// creation with validation (src/cuda/runtime.cc:385-560) and the
+// init/call/get_last_error convention (tilelang/jit/adapter/wrapper.py:60-86).
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/b200dq.h"
+#include "pack_kernels.cuh"
+#include "umma_gemm.cuh"
+
+namespace {
+
+using namespace b200dq;
+
+constexpr int kMaxDevices = 32;
+constexpr int kAbiVersion = 1;
+constexpr int kMinSpan = 8;   // fewest k-blocks worth giving a CTA of its own
+
+thread_local char g_err[1024] = "";
+
+int fail(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return -1;
+}
+
+#define CUDA_OK(expr)                                                                   \
+  do {                                                                                  \
+    cudaError_t _e = (expr);                                                            \
+    if (_e != cudaSuccess) return fail("%s failed: %s", #expr, cudaGetErrorString(_e)); \
+  } while (0)
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+struct DeviceState {
+  bool ready = false;
+  int sm_count = 0;
+  DeviceStatus* status = nullptr;
+};
+
+std::mutex g_mu;
+DeviceState g_dev[kMaxDevices];
+EncodeTiledFn g_encode = nullptr;
+
+int current_device_state(DeviceState** out) {
+  int dev = 0;
+  CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail("device index %d out of range", dev);
+  if (!g_dev[dev].ready) {
+    if (b200dq_init() != 0) return -1;
+  }
+  *out = &g_dev[dev];
+  return 0;
+}
+
+int token_tile_for(int M) {
+  if (M <= 16) return 16;
+  if (M <= 32) return 32;
+  if (M <= 64) return 64;
+  if (M <= 128) return 128;
+  return 256;
+}
+
+struct Schedule {
+  int tn, m_tiles, n_tiles, kb_total, grid, span;
+  long long units;
+  size_t workspace_bytes;
+};
+
+int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_ctas, int sm_count, Schedule* s) {
+  const int bke = (act_type == ACT_I8) ? 128 : 64;
+  s->tn = token_tile > 0 ? token_tile : token_tile_for(M);
+  if (s->tn != 16 && s->tn != 32 && s->tn != 64 && s->tn != 128 && s->tn != 256)
+    return fail("token_tile must be 16, 32, 64, 128 or 256 (got %d)", s->tn);
+  s->m_tiles = (M + s->tn - 1) / s->tn;
+  s->n_tiles = (N + kTileRows - 1) / kTileRows;
+  s->kb_total = K / bke;
+  s->units = static_cast<long long>(s->m_tiles) * s->n_tiles * s->kb_total;
+  int cap = sm_count;
+  if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
+  long long g = s->units / kMinSpan;
+  if (g < 1) g = 1;
+  if (g > cap) g = cap;
+  s->span = static_cast<int>((s->units + g - 1) / g);
+  s->grid = static_cast<int>((s->units + s->span - 1) / s->span);
+  s->workspace_bytes = static_cast<size_t>(s->grid) * 2 * s->tn * kTileRows * sizeof(uint32_t);
+  return 0;
+}
+
+int encode_activation_map(CUtensorMap* map, const void* a, int M, int K, int act_type, int tn) {
+  if (g_encode == nullptr) return fail("tensor-map encoder not resolved (b200dq_init not run?)");
+  const int esize = (act_type == ACT_I8) ? 1 : 2;
+  const int bke = (act_type == ACT_I8) ? 128 : 64;
+  if ((reinterpret_cast<uintptr_t>(a) & 15) != 0) return fail("activation pointer must be 16-byte aligned");
+  if ((static_cast<long long>(K) * esize) % 16 != 0) return fail("activation row pitch must be a multiple of 16 bytes");
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * esize};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(bke), static_cast<cuuint32_t>(tn)};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = act_type == ACT_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : act_type == ACT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = g_encode(map, dt, 2, const_cast<void*>(a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with CUresult %d (M=%d K=%d box=%dx%d)",
+                                     static_cast<int>(r), M, K, bke, tn);
+  return 0;
+}
+
+template <int TN, int WF, int ACT>
+int launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStream_t stream) {
+  using Ring = RingConfig<TN, WF>;
+  auto kernel = umma_dequant_gemm_kernel<TN, WF, ACT>;
+  static bool attr_set[kMaxDevices] = {};
+  int dev = 0;
+  CUDA_OK(cudaGetDevice(&dev));
+  if (!attr_set[dev]) {
+    CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring::kSmemBytes));
+    attr_set[dev] = true;
+  }
+  kernel<<<grid, kThreads, Ring::kSmemBytes, stream>>>(tmap, p);
+  CUDA_OK(cudaGetLastError());
+  // stream-K second pass: only tiles cut between CTAs do any work
+  const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
+  if (p.span % p.kb_total != 0 && grid > 1) {
+    constexpr bool kInt = (ACT == ACT_I8);
+    const int t = static_cast<int>(tiles);
+    switch (p.out_type) {
+      case OUT_F16: streamk_fixup_kernel<__half, TN, kInt><<<t, kTileRows, 0, stream>>>(p); break;
+      case OUT_BF16: streamk_fixup_kernel<__nv_bfloat16, TN, kInt><<<t, kTileRows, 0, stream>>>(p); break;
+      case OUT_F32: streamk_fixup_kernel<float, TN, kInt><<<t, kTileRows, 0, stream>>>(p); break;
+      default: streamk_fixup_kernel<int, TN, kInt><<<t, kTileRows, 0, stream>>>(p); break;
+    }
+    CUDA_OK(cudaGetLastError());
+  }
+  return 0;
+}
+
+template <int WF, int ACT>
+int dispatch_tn(int tn, const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStream_t stream) {
+  switch (tn) {
+    case 16: return launch_gemm<16, WF, ACT>(tmap, p, grid, stream);
+    case 32: return launch_gemm<32, WF, ACT>(tmap, p, grid, stream);
+    case 64: return launch_gemm<64, WF, ACT>(tmap, p, grid, stream);
+    case 128: return launch_gemm<128, WF, ACT>(tmap, p, grid, stream);
+    default: return launch_gemm<256, WF, ACT>(tmap, p, grid, stream);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+int b200dq_version(void) { return kAbiVersion; }
+
+const char* b200dq_get_last_error(void) { return g_err; }
+
+int b200dq_init(void) {
+  std::lock_guard<std::mutex> lock(g_mu);
+  int dev = 0;
+  CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail("device index %d out of range", dev);
+  if (g_dev[dev].ready) return 0;
+  cudaDeviceProp prop;
+  CUDA_OK(cudaGetDeviceProperties(&prop, dev));
+  if (prop.major != 10) return fail("b200dq needs an sm_100 GPU, device %d is sm_%d%d", dev, prop.major, prop.minor);
+  if (g_encode == nullptr) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+    if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return fail("driver has no cuTensorMapEncodeTiled");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  DeviceStatus* st = nullptr;
+  CUDA_OK(cudaMalloc(&st, sizeof(DeviceStatus)));
+  CUDA_OK(cudaMemset(st, 0, sizeof(DeviceStatus)));
+  g_dev[dev].status = st;
+  g_dev[dev].sm_count = prop.multiProcessorCount;
+  g_dev[dev].ready = true;
+  return 0;
+}
+
+size_t b200dq_gemm_workspace_bytes(int32_t M, int32_t N, int32_t K, int32_t weight_format, int32_t act_type,
+                                   int32_t token_tile, int32_t max_ctas) {
+  (void)weight_format;
+  Schedule s;
+  // an upper bound that does not need a device: assume at most 256 SMs
+  int sm = 256;
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) sm = g_dev[dev].sm_count;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (make_schedule(M, N, K, act_type, token_tile, max_ctas, sm, &s) != 0) return 0;
+  return s.workspace_bytes;
+}
+
+size_t b200dq_packed_weight_bytes(int32_t N, int32_t K, int32_t weight_format) {
+  const int n_tiles = (N + kTileRows - 1) / kTileRows;
+  const bool int8_target = (weight_format == WF_I2_I8 || weight_format == WF_I4_I8);
+  const int bke = int8_target ? 128 : 64;
+  return static_cast<size_t>(n_tiles) * (K / bke) * w_stage_bytes(weight_format);
+}
+
+size_t b200dq_packed_scale_bytes(int32_t N, int32_t K, int32_t group_size, int32_t weight_format) {
+  const size_t n_pad = static_cast<size_t>((N + kTileRows - 1) / kTileRows) * kTileRows;
+  if (weight_format == WF_U4_SZ) return n_pad * (K / group_size) * sizeof(uint32_t);
+  if (weight_format == WF_FP4_E8M0) return n_pad * (K / 64) * sizeof(uint16_t);
+  return 0;
+}
+
+int b200dq_pack_weights(const void* q_natural, void* wp, int32_t N, int32_t K, int32_t bits, int32_t weight_format,
+                        void* cuda_stream) {
+  if (q_natural == nullptr || wp == nullptr) return fail("pack_weights: null pointer");
+  if (bits != 2 && bits != 4) return fail("pack_weights: bits must be 2 or 4 (got %d)", bits);
+  const bool int8_target = (weight_format == WF_I2_I8 || weight_format == WF_I4_I8);
+  if ((weight_format == WF_I2_I8) != (bits == 2)) return fail("pack_weights: bits=%d does not match weight format %d", bits, weight_format);
+  const int bke = int8_target ? 128 : 64;
+  if (N <= 0 || K <= 0 || K % bke != 0) return fail("pack_weights: K=%d must be a positive multiple of %d", K, bke);
+  if ((reinterpret_cast<uintptr_t>(q_natural) & 3) != 0 || (reinterpret_cast<uintptr_t>(wp) & 15) != 0)
+    return fail("pack_weights: input must be 4-byte and output 16-byte aligned");
+  const int n_tiles = (N + kTileRows - 1) / kTileRows;
+  const int kb_total = K / bke;
+  const int chunks = w_stage_bytes(weight_format) / 2048;
+  const int mode = int8_target ? 1 : (weight_format == WF_FP4_E8M0 ? 2 : 0);
+  const long long total = static_cast<long long>(n_tiles) * kb_total * chunks * 128 * 4;
+  const int threads = 256;
+  const long long blocks = (total + threads - 1) / threads;
+  pack_weights_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint32_t*>(q_natural), static_cast<uint32_t*>(wp), N, K, bits, mode, n_tiles, kb_total,
+      chunks, bke);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int b200dq_pack_scales_u4(const void* scales, const void* zeros, void* sz, int32_t N, int32_t K, int32_t group_size,
+                          int32_t act_type, void* cuda_stream) {
+  if (scales == nullptr || sz == nullptr) return fail("pack_scales_u4: null pointer");
+  if (act_type != ACT_F16 && act_type != ACT_BF16) return fail("pack_scales_u4: activation type must be f16 or bf16");
+  if (group_size <= 0 || group_size % 64 != 0 || K % group_size != 0)
+    return fail("pack_scales_u4: group_size=%d must be a multiple of 64 that divides K=%d", group_size, K);
+  const int groups = K / group_size;
+  const int n_pad = (N + kTileRows - 1) / kTileRows * kTileRows;
+  dim3 grid((n_pad + 255) / 256, groups);
+  auto st = static_cast<cudaStream_t>(cuda_stream);
+  if (act_type == ACT_BF16)
+    pack_scales_u4_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(scales),
+                                                      static_cast<const uint16_t*>(zeros),
+                                                      static_cast<uint32_t*>(sz), N, groups, n_pad);
+  else
+    pack_scales_u4_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(scales),
+                                                       static_cast<const uint16_t*>(zeros),
+                                                       static_cast<uint32_t*>(sz), N, groups, n_pad);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int b200dq_pack_scales_e8m0(const void* exps, void* sz, int32_t N, int32_t K, void* cuda_stream) {
+  if (exps == nullptr || sz == nullptr) return fail("pack_scales_e8m0: null pointer");
+  if (K % 64 != 0) return fail("pack_scales_e8m0: K=%d must be a multiple of 64", K);
+  const int n_pad = (N + kTileRows - 1) / kTileRows * kTileRows;
+  dim3 grid((n_pad + 255) / 256, K / 64);
+  pack_scales_e8m0_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint8_t*>(exps), static_cast<uint16_t*>(sz), N, K / 32, n_pad);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
+  if (a == nullptr) return fail("gemm: null argument struct");
+  if (a->a == nullptr || a->wp == nullptr || a->c == nullptr) return fail("gemm: null tensor pointer");
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0) return fail("gemm: M, N, K must be positive (got %d, %d, %d)", a->M, a->N, a->K);
+  const int wf = a->weight_format, act = a->act_type;
+  const bool int_act = (act == ACT_I8);
+  const bool wf_int = (wf == WF_I2_I8 || wf == WF_I4_I8);
+  if (wf < WF_U4_SZ || wf > WF_I4_I8) return fail("gemm: unknown weight format %d", wf);
+  if (act < ACT_F16 || act > ACT_I8) return fail("gemm: unknown activation type %d", act);
+  if (a->out_type < OUT_F16 || a->out_type > OUT_I32) return fail("gemm: unknown output type %d", a->out_type);
+  if (wf_int != int_act) return fail("gemm: weight format %d and activation type %d do not go together", wf, act);
+  if (wf == WF_FP4_E8M0 && act != ACT_BF16) return fail("gemm: e2m1 weights need bf16 activations");
+  const int bke = int_act ? 128 : 64;
+  if (a->K % bke != 0) return fail("gemm: K=%d must be a multiple of %d", a->K, bke);
+  if ((wf == WF_U4_SZ || wf == WF_FP4_E8M0) && a->sz == nullptr) return fail("gemm: this weight format needs a scale table");
+  int group_kb = 1;
+  if (wf == WF_U4_SZ) {
+    if (a->group_size <= 0 || a->group_size % 64 != 0 || a->K % a->group_size != 0)
+      return fail("gemm: group_size=%d must be a multiple of 64 that divides K=%d", a->group_size, a->K);
+    group_kb = a->group_size / 64;
+  }
+  if ((a->flags & GF_HAS_BIAS) && a->bias == nullptr) return fail("gemm: HAS_BIAS set but bias is null");
+  if ((a->flags & GF_ROW_SCALE) && a->row_scale == nullptr) return fail("gemm: ROW_SCALE set but row_scale is null");
+  if ((reinterpret_cast<uintptr_t>(a->wp) & 15) != 0) return fail("gemm: packed weights must be 16-byte aligned");
+
+  DeviceState* ds = nullptr;
+  if (current_device_state(&ds) != 0) return -1;
+  Schedule s;
+  if (make_schedule(a->M, a->N, a->K, act, a->token_tile, a->max_ctas, ds->sm_count, &s) != 0) return -1;
+  const bool needs_ws = (s.span % s.kb_total != 0) && s.grid > 1;
+  if (needs_ws) {
+    if (a->workspace == nullptr || a->workspace_bytes < s.workspace_bytes)
+      return fail("gemm: workspace too small: need %zu bytes, got %zu", s.workspace_bytes, a->workspace_bytes);
+    if ((reinterpret_cast<uintptr_t>(a->workspace) & 15) != 0) return fail("gemm: workspace must be 16-byte aligned");
+  }
+
+  CUtensorMap tmap;
+  if (encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn) != 0) return -1;
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.wp = static_cast<const uint8_t*>(a->wp);
+  p.sz = a->sz;
+  p.c = a->c;
+  p.partial = static_cast<uint32_t*>(a->workspace);
+  p.bias = a->bias;
+  p.row_scale = a->row_scale;
+  p.tensor_scale = a->tensor_scale;
+  p.code_bias = a->code_bias;
+  p.fp4_exp_bias = a->fp4_exp_bias;
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  p.n_tiles = s.n_tiles; p.m_tiles = s.m_tiles; p.kb_total = s.kb_total;
+  p.span = s.span; p.units = s.units;
+  p.group_kb = group_kb;
+  p.n_pad = s.n_tiles * kTileRows;
+  p.ldc = (a->flags & GF_TRANS_C) ? a->M : a->N;
+  p.flags = a->flags;
+  p.out_type = a->out_type;
+  p.status = ds->status;
+
+  auto stream = static_cast<cudaStream_t>(cuda_stream);
+  if (wf == WF_U4_SZ && act == ACT_F16) return dispatch_tn<WF_U4_SZ, ACT_F16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_U4_SZ && act == ACT_BF16) return dispatch_tn<WF_U4_SZ, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_U4_RAW && act == ACT_F16) return dispatch_tn<WF_U4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_U4_RAW && act == ACT_BF16) return dispatch_tn<WF_U4_RAW, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_S4_RAW && act == ACT_F16) return dispatch_tn<WF_S4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_S4_RAW && act == ACT_BF16) return dispatch_tn<WF_S4_RAW, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_FP4_E8M0) return dispatch_tn<WF_FP4_E8M0, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_I2_I8) return dispatch_tn<WF_I2_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_I4_I8) return dispatch_tn<WF_I4_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
+  return fail("gemm: no kernel for weight format %d with activation type %d", wf, act);
+}
+
+int b200dq_check_status(void* cuda_stream) {
+  DeviceState* ds = nullptr;
+  if (current_device_state(&ds) != 0) return -1;
+  auto stream = static_cast<cudaStream_t>(cuda_stream);
+  DeviceStatus h;
+  CUDA_OK(cudaMemcpyAsync(&h, ds->status, sizeof(h), cudaMemcpyDeviceToHost, stream));
+  CUDA_OK(cudaStreamSynchronize(stream));
+  if (h.error == ERR_NONE) return 0;
+  CUDA_OK(cudaMemsetAsync(ds->status, 0, sizeof(DeviceStatus), stream));
+  CUDA_OK(cudaStreamSynchronize(stream));
+  return fail("device status: error %u (1 = a bounded wait gave up), first at block %u wait site %u, %u waits gave up",
+              h.error, h.where >> 8, h.where & 0xff, h.count);
+}
+
+}  // extern "C"

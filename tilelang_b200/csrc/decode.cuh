@@ -1,0 +1,173 @@
+// Register dequantisation of packed low-bit weights, one 16-byte chunk at a
+// time. Each routine turns 4 packed 32-bit words into 16 registers that are
+// stored to consecutive TMEM columns (or used directly by the SIMT GEMV):
+//   * 16-bit targets: register r holds K elements (2r, 2r+1), even k in the low half;
+//   * 8-bit targets:  register r holds K elements (4r .. 4r+3), lowest k in byte 0.
+//
+// The bit tricks restate what the reference emits from
+// examples/dequantize_gemm/quantize/lop3.py (decode_i4u_to_f16 :6-39, the
+// scale/zeros variants :41-176, decode_i2s_to_i8s / decode_i4s_to_i8s :893-1047)
+// and quantize/mxfp.py:6-49 (fp4 -> bf16 by mask/shift then * 2^126). The
+// reference has fp16 LOP3 decoders only; the bf16 ones here use the same idea
+// with the magic exponent of 128.0 (bf16 has 7 mantissa bits, so 128 + q is exact).
+//
+// Offline layouts expected in each 32-bit word (produced by pack_weight):
+//   u4 -> 16 bit : element e at bit (e % 2) * 16 + (e / 2) * 4        (8 per word)
+//   u2/u4 -> 8 bit: element e at bit (e % 4) * 8 + (e / 4) * nbits    (16 or 8 per word)
+//   e2m1 -> bf16 : see decode_fp4_chunk
+#pragma once
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace b200dq {
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t magic) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(magic));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t bf162_as_u32(__nv_bfloat162 v) {
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ __nv_bfloat162 u32_as_bf162(uint32_t v) {
+  return *reinterpret_cast<__nv_bfloat162*>(&v);
+}
+__device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
+__device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
+
+// sz word: low 16 bits = scale s, high 16 bits = zero term c, both in the
+// activation dtype. Dequantised weight = (q - 8) * s + c, with c = (8 - z) * s
+// rounded once offline (c == 0 for the fixed zero-point 8).
+template <bool kBf16>
+__device__ __forceinline__ void decode_u4_chunk(const uint4& packed, uint32_t sz, uint32_t (&out)[16]) {
+  const uint32_t s2 = __byte_perm(sz, 0, 0x1010);
+  const uint32_t c2 = __byte_perm(sz, 0, 0x3232);
+  const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t t = w[j] >> (4 * i);
+      if constexpr (kBf16) {
+        // 0x4300 = 128.0, 0x4308 = 136.0
+        const uint32_t x = lop3_and_or(t, 0x000f000fu, 0x43004300u);
+        const __nv_bfloat162 y = __hsub2(u32_as_bf162(x), u32_as_bf162(0x43084308u));
+        out[4 * j + i] = bf162_as_u32(__hfma2(y, u32_as_bf162(s2), u32_as_bf162(c2)));
+      } else {
+        // 0x6400 = 1024.0, 0x6408 = 1032.0
+        const uint32_t x = lop3_and_or(t, 0x000f000fu, 0x64006400u);
+        const __half2 y = __hsub2(u32_as_h2(x), u32_as_h2(0x64086408u));
+        out[4 * j + i] = h2_as_u32(__hfma2(y, u32_as_h2(s2), u32_as_h2(c2)));
+      }
+    }
+  }
+}
+
+// No scale at all: weight = q (unsigned) or q - 8 (signed storage), as in the
+// reference's fine-grained example (example_dequant_gemm_fine_grained.py:11-13).
+template <bool kBf16, bool kSigned>
+__device__ __forceinline__ void decode_u4_chunk_noscale(const uint4& packed, uint32_t (&out)[16]) {
+  const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t t = w[j] >> (4 * i);
+      if constexpr (kBf16) {
+        const uint32_t x = lop3_and_or(t, 0x000f000fu, 0x43004300u);
+        out[4 * j + i] = bf162_as_u32(
+            __hsub2(u32_as_bf162(x), u32_as_bf162(kSigned ? 0x43084308u : 0x43004300u)));
+      } else {
+        const uint32_t x = lop3_and_or(t, 0x000f000fu, 0x64006400u);
+        out[4 * j + i] =
+            h2_as_u32(__hsub2(u32_as_h2(x), u32_as_h2(kSigned ? 0x64086408u : 0x64006400u)));
+      }
+    }
+  }
+}
+
+// 2-bit codes -> int8. 16 codes per word, word j of the chunk covers K
+// elements 16j .. 16j+15. `bias` is subtracted bytewise (0x02020202 for the
+// ternary code q = w + 2, 0 for unsigned codes).
+__device__ __forceinline__ void decode_i2_chunk(const uint4& packed, uint32_t bias, uint32_t (&out)[16]) {
+  const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t x = (w[j] >> (2 * i)) & 0x03030303u;
+      out[4 * j + i] = __vsub4(x, bias);
+    }
+  }
+}
+
+// 4-bit codes -> int8. 8 codes per word; a 16-byte chunk yields only 8
+// registers (32 K elements), so the caller decodes two chunks per 64 elements.
+__device__ __forceinline__ void decode_i4_chunk(const uint4& packed, uint32_t bias, uint32_t (&out)[8]) {
+  const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint32_t x = (w[j] >> (4 * i)) & 0x0f0f0f0fu;
+      out[2 * j + i] = __vsub4(x, bias);
+    }
+  }
+}
+
+// e2m1 -> bf16 with a power-of-two block scale.
+// Offline bit layout per 16-bit half (4 codes; code = s e1 e0 m): the first
+// three codes sit where one shift and one mask move them to bf16 bit positions
+// (sign -> 15, e1 e0 m -> 8..6):
+//   code 0: s@15  e1 e0 m @ 8 7 6      (mask 0x81c0, no shift)
+//   code 1: s@12  e1 e0 m @ 5 4 3      (shift left 3)
+//   code 2: s@9   e1 e0 m @ 2 1 0      (shift left 6)
+//   code 3: s@14  e1@13   e0 m @ 11 10 (three pieces)
+// and the two halves of a word carry K elements (8j+2i, 8j+2i+1) for code i.
+// The masked pattern is a bf16 whose exponent field is only e (0..3); times
+// 2^126 it becomes the e2m1 value {0, .5, 1, 1.5, 2, 3, 4, 6} exactly (e = 0 is
+// a bf16 subnormal, which the multiply normalises). `mul_lo`/`mul_hi` are the
+// two factors whose product is 2^126 * 2^(block exponent).
+__device__ __forceinline__ void decode_fp4_word(uint32_t w, uint32_t m1, uint32_t m2, uint32_t* out) {
+  const uint32_t kMask = 0x81c081c0u;
+  uint32_t v[4];
+  v[0] = w & kMask;
+  v[1] = (w << 3) & kMask;
+  v[2] = (w << 6) & kMask;
+  uint32_t t = (w << 1) & 0x80008000u;
+  t = lop3_and_or(w >> 5, 0x01000100u, t);
+  t = lop3_and_or(w >> 4, 0x00c000c0u, t);
+  v[3] = t;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 x = __hmul2(u32_as_bf162(v[i]), u32_as_bf162(m1));
+    out[i] = bf162_as_u32(__hmul2(x, u32_as_bf162(m2)));
+  }
+}
+
+// e8m0 byte e -> the pair of bf16 factors (m1, m2) with m1 * m2 = 2^126 * 2^(e - bias_e).
+// exp_total = 126 + e - bias_e is split so both factors are normal bf16 numbers.
+__device__ __forceinline__ void fp4_scale_factors(int exp_total, uint32_t& m1, uint32_t& m2) {
+  // m1 = 2^a, m2 = 2^b, a + b = exp_total, a = clamp(exp_total, -126, 127) / 2 rounded toward +inf
+  int a = (exp_total + 1) >> 1;
+  int b = exp_total - a;
+  a = max(-126, min(127, a));
+  b = max(-126, min(127, b));
+  const uint32_t ha = static_cast<uint32_t>(a + 127) << 7;
+  const uint32_t hb = static_cast<uint32_t>(b + 127) << 7;
+  m1 = ha | (ha << 16);
+  m2 = hb | (hb << 16);
+}
+
+__device__ __forceinline__ void decode_fp4_chunk(const uint4& packed, int exp_total, uint32_t (&out)[16]) {
+  uint32_t m1, m2;
+  fp4_scale_factors(exp_total, m1, m2);
+  decode_fp4_word(packed.x, m1, m2, &out[0]);
+  decode_fp4_word(packed.y, m1, m2, &out[4]);
+  decode_fp4_word(packed.z, m1, m2, &out[8]);
+  decode_fp4_word(packed.w, m1, m2, &out[12]);
+}
+
+}  // namespace b200dq

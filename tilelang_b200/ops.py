@@ -1,0 +1,235 @@
+"""Torch-facing wrappers around the C ABI: offline weight packing and the GEMM call.
+
+Torch is used for device memory and the current stream only; every computation
+goes through ``libb200dq.so`` (``_lib.py``). The calling rules follow the
+reference adapter: tensors must be contiguous CUDA tensors on one device, the
+launch goes on torch's current stream of that device, inputs are borrowed
+(tilelang/jit/adapter/base.py:60-79, tilelang/jit/adapter/tvm_ffi.py:242-300).
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import (ACT_BF16, ACT_F16, ACT_I8, GF_HAS_BIAS, GF_ROW_SCALE, GF_TRANS_C, OUT_BF16, OUT_F16,
+                   OUT_F32, OUT_I32, WF_FP4_E8M0, WF_I2_I8, WF_I4_I8, WF_S4_RAW, WF_U4_RAW, WF_U4_SZ)
+
+_ACT_OF = {torch.float16: ACT_F16, torch.bfloat16: ACT_BF16, torch.int8: ACT_I8}
+_OUT_OF = {torch.float16: OUT_F16, torch.bfloat16: OUT_BF16, torch.float32: OUT_F32, torch.int32: OUT_I32}
+
+_initialised_devices: set[int] = set()
+_workspaces: dict[int, torch.Tensor] = {}
+
+
+def _ensure_init(device: torch.device) -> None:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx in _initialised_devices:
+        return
+    with torch.cuda.device(idx):
+        _lib.check(_lib.load().b200dq_init(), "b200dq_init")
+    _initialised_devices.add(idx)
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _check_cuda_contig(name: str, t: torch.Tensor, device: Optional[torch.device] = None) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor, got {type(t).__name__}")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if device is not None and t.device != device:
+        raise ValueError(f"{name} is on {t.device}, expected {device}")
+
+
+@dataclass
+class PackedWeight:
+    """A weight in the library's private device layout (see csrc/pack_kernels.cuh)."""
+
+    wp: torch.Tensor                 # uint8 packed image
+    sz: Optional[torch.Tensor]       # scale table or None
+    N: int
+    K: int
+    weight_format: int
+    act_type: int
+    group_size: int = 0
+    code_bias: int = 0
+    fp4_exp_bias: int = 127
+
+    @property
+    def device(self) -> torch.device:
+        return self.wp.device
+
+    def nbytes(self) -> int:
+        return self.wp.numel() + (self.sz.numel() * self.sz.element_size() if self.sz is not None else 0)
+
+
+def _pack_codes(q: torch.Tensor, N: int, K: int, bits: int, weight_format: int) -> torch.Tensor:
+    lib = _lib.load()
+    _check_cuda_contig("packed weight codes", q)
+    if q.dtype not in (torch.uint8, torch.int8):
+        raise TypeError(f"packed weight codes must be uint8/int8, got {q.dtype}")
+    if tuple(q.shape) != (N, K * bits // 8):
+        raise ValueError(f"packed weight codes must have shape {(N, K * bits // 8)}, got {tuple(q.shape)}")
+    _ensure_init(q.device)
+    nbytes = lib.b200dq_packed_weight_bytes(N, K, weight_format)
+    wp = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.check(lib.b200dq_pack_weights(q.data_ptr(), wp.data_ptr(), N, K, bits, weight_format,
+                                           _stream_ptr(q.device)), "b200dq_pack_weights")
+    return wp
+
+
+def pack_w4a16(qweight: torch.Tensor, scales: Optional[torch.Tensor], zeros: Optional[torch.Tensor], N: int, K: int,
+               group_size: int, dtype: torch.dtype, signed_storage: bool = False) -> PackedWeight:
+    """uint4 codes (N, K/2), two per byte with the even k in the low nibble.
+
+    ``scales``/``zeros`` are (N, K/group_size) in ``dtype``; the weight is
+    ``(q - z) * s`` (the reference's "original" zeros mode,
+    examples/dequantize_gemm/quantize/lop3.py:684-689). ``zeros=None`` means the
+    fixed zero-point 8; ``scales=None`` means the raw code ``q`` (or ``q - 8``
+    with ``signed_storage``), as in example_dequant_gemm_fine_grained.py:11-13.
+    """
+    if dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("W4A16 needs float16 or bfloat16 activations")
+    act = _ACT_OF[dtype]
+    if scales is None:
+        if zeros is not None:
+            raise ValueError("zeros without scales is not supported")
+        wf = WF_S4_RAW if signed_storage else WF_U4_RAW
+        return PackedWeight(_pack_codes(qweight, N, K, 4, wf), None, N, K, wf, act)
+    if group_size in (-1, 0, None):
+        group_size = K
+    lib = _lib.load()
+    groups = K // group_size
+    for name, t in (("scales", scales), ("zeros", zeros)):
+        if t is None:
+            continue
+        _check_cuda_contig(name, t, qweight.device)
+        if t.dtype != dtype or tuple(t.shape) != (N, groups):
+            raise ValueError(f"{name} must be {dtype} of shape {(N, groups)}, got {t.dtype} {tuple(t.shape)}")
+    wp = _pack_codes(qweight, N, K, 4, WF_U4_SZ)
+    sz = torch.empty(lib.b200dq_packed_scale_bytes(N, K, group_size, WF_U4_SZ), dtype=torch.uint8,
+                     device=qweight.device)
+    with torch.cuda.device(qweight.device):
+        _lib.check(lib.b200dq_pack_scales_u4(scales.data_ptr(), zeros.data_ptr() if zeros is not None else None,
+                                             sz.data_ptr(), N, K, group_size, act, _stream_ptr(qweight.device)),
+                   "b200dq_pack_scales_u4")
+    return PackedWeight(wp, sz, N, K, WF_U4_SZ, act, group_size=group_size)
+
+
+def pack_mxfp4(qweight: torch.Tensor, scale_bytes: torch.Tensor, N: int, K: int, exp_bias: int = 127) -> PackedWeight:
+    """e2m1 codes (N, K/2) (even k in the low nibble) + one exponent byte per 32 K.
+
+    ``exp_bias=127`` reads the bytes as OCP e8m0; ``exp_bias=0`` as the raw
+    exponent the reference's hopper example applies with ``2**Scale``
+    (example_dequant_gemm_bf16_mxfp4_hopper.py:397).
+    """
+    lib = _lib.load()
+    _check_cuda_contig("scale bytes", scale_bytes, qweight.device)
+    if scale_bytes.dtype != torch.uint8 or tuple(scale_bytes.shape) != (N, K // 32):
+        raise ValueError(f"scale bytes must be uint8 of shape {(N, K // 32)}")
+    wp = _pack_codes(qweight, N, K, 4, WF_FP4_E8M0)
+    sz = torch.empty(lib.b200dq_packed_scale_bytes(N, K, 32, WF_FP4_E8M0), dtype=torch.uint8, device=qweight.device)
+    with torch.cuda.device(qweight.device):
+        _lib.check(lib.b200dq_pack_scales_e8m0(scale_bytes.data_ptr(), sz.data_ptr(), N, K,
+                                               _stream_ptr(qweight.device)), "b200dq_pack_scales_e8m0")
+    return PackedWeight(wp, sz, N, K, WF_FP4_E8M0, ACT_BF16, group_size=32, fp4_exp_bias=exp_bias)
+
+
+def pack_int2(qweight: torch.Tensor, N: int, K: int, code_offset: int = 0) -> PackedWeight:
+    """2-bit codes (N, K/4), code k in bits [2(k%4), 2(k%4)+1] of byte k//4; weight = code - code_offset."""
+    b = code_offset & 0xFF
+    return PackedWeight(_pack_codes(qweight, N, K, 2, WF_I2_I8), None, N, K, WF_I2_I8, ACT_I8,
+                        code_bias=b | (b << 8) | (b << 16) | (b << 24))
+
+
+def pack_int4_for_int8(qweight: torch.Tensor, N: int, K: int, code_offset: int = 0) -> PackedWeight:
+    """4-bit codes (N, K/2) feeding an int8 MMA; weight = code - code_offset."""
+    b = code_offset & 0xFF
+    return PackedWeight(_pack_codes(qweight, N, K, 4, WF_I4_I8), None, N, K, WF_I4_I8, ACT_I8,
+                        code_bias=b | (b << 8) | (b << 16) | (b << 24))
+
+
+def workspace_for(device: torch.device, nbytes: int) -> torch.Tensor:
+    """A per-device scratch tensor, grown on demand and reused by every call."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    ws = _workspaces.get(idx)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.empty(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[idx] = ws
+    return ws
+
+
+def gemm(A: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None,
+         out_dtype: Optional[torch.dtype] = None, bias: Optional[torch.Tensor] = None,
+         row_scale: Optional[torch.Tensor] = None, tensor_scale: float = 1.0, trans_c: bool = False,
+         token_tile: int = 0, max_ctas: int = 0, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = A @ dequant(W)^T on the current stream; returns (and, if given, fills) ``out``."""
+    lib = _lib.load()
+    _check_cuda_contig("A", A)
+    dev = A.device
+    if A.dim() != 2 or A.shape[1] != w.K:
+        raise ValueError(f"A must have shape (M, {w.K}), got {tuple(A.shape)}")
+    if _ACT_OF.get(A.dtype) != w.act_type:
+        raise TypeError(f"A has dtype {A.dtype}, the packed weight expects activation type {w.act_type}")
+    if w.wp.device != dev:
+        raise ValueError(f"A is on {dev}, the packed weight on {w.wp.device}")
+    M = A.shape[0]
+    if out is None:
+        if out_dtype is None:
+            out_dtype = torch.int32 if A.dtype == torch.int8 else A.dtype
+        out = torch.empty((w.N, M) if trans_c else (M, w.N), dtype=out_dtype, device=dev)
+    else:
+        _check_cuda_contig("out", out, dev)
+        want = (w.N, M) if trans_c else (M, w.N)
+        if tuple(out.shape) != want:
+            raise ValueError(f"out must have shape {want}, got {tuple(out.shape)}")
+    if out.dtype not in _OUT_OF:
+        raise TypeError(f"unsupported output dtype {out.dtype}")
+    flags = GF_TRANS_C if trans_c else 0
+    if bias is not None:
+        _check_cuda_contig("bias", bias, dev)
+        if bias.dtype != out.dtype or tuple(bias.shape) != (M, w.N):
+            raise ValueError(f"bias must be {out.dtype} of shape {(M, w.N)}")
+        flags |= GF_HAS_BIAS
+    if row_scale is not None:
+        _check_cuda_contig("row_scale", row_scale, dev)
+        if row_scale.dtype != torch.float32 or row_scale.numel() != M:
+            raise ValueError("row_scale must be float32 with M elements")
+        flags |= GF_ROW_SCALE
+    if M == 0:
+        return out
+    _ensure_init(dev)
+    need = lib.b200dq_gemm_workspace_bytes(M, w.N, w.K, w.weight_format, w.act_type, token_tile, max_ctas)
+    if workspace is None:
+        workspace = workspace_for(dev, need)
+    elif workspace.numel() * workspace.element_size() < need:
+        raise ValueError(f"workspace too small: need {need} bytes")
+    args = _lib.GemmArgs(
+        a=A.data_ptr(), wp=w.wp.data_ptr(), sz=w.sz.data_ptr() if w.sz is not None else None,
+        bias=bias.data_ptr() if bias is not None else None,
+        row_scale=row_scale.data_ptr() if row_scale is not None else None,
+        c=out.data_ptr(), workspace=workspace.data_ptr(),
+        workspace_bytes=workspace.numel() * workspace.element_size(),
+        M=M, N=w.N, K=w.K, group_size=w.group_size, weight_format=w.weight_format, act_type=w.act_type,
+        out_type=_OUT_OF[out.dtype], flags=flags, tensor_scale=float(tensor_scale), code_bias=w.code_bias,
+        fp4_exp_bias=w.fp4_exp_bias, token_tile=token_tile, max_ctas=max_ctas)
+    with torch.cuda.device(dev):
+        _lib.check(lib.b200dq_gemm(ctypes.byref(args), _stream_ptr(dev)), "b200dq_gemm")
+    return out
+
+
+def check_status(device: Optional[torch.device] = None) -> None:
+    """Raise if a kernel recorded a device-side error (a bounded wait that gave up)."""
+    dev = device or torch.device("cuda", torch.cuda.current_device())
+    _ensure_init(dev)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.load().b200dq_check_status(_stream_ptr(dev)), "b200dq_check_status")
