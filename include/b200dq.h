@@ -39,7 +39,7 @@ enum b200dq_out_type { B200DQ_OUT_F16 = 0, B200DQ_OUT_BF16 = 1, B200DQ_OUT_F32 =
 enum b200dq_gemm_flags {
   B200DQ_GF_TRANS_C = 1,   /* write C^T (N x M), the orientation of the reference's fp4/w4a8 examples */
   B200DQ_GF_HAS_BIAS = 2,  /* add bias[M][N] (output dtype) before the cast                           */
-  B200DQ_GF_ROW_SCALE = 4  /* integer path: acc * row_scale[m] * tensor_scale before the cast          */
+  B200DQ_GF_ROW_SCALE = 4  /* integer path: acc / row_scale[m] / tensor_scale before the cast          */
 };
 
 /* Replaces init() of tilelang/jit/adapter/wrapper.py:60-70: selects nothing, but
@@ -58,10 +58,9 @@ int b200dq_version(void);
 /* Arguments of the dequantize-GEMM  C[M,N] = A[M,K] * dequant(W[N,K])^T. */
 typedef struct b200dq_gemm_args {
   const void* a;            /* activations, row-major (M, K), act_type                          */
-  const void* wp;           /* packed weights from b200dq_pack_*                                */
-  const void* sz;           /* scale table from b200dq_pack_* (NULL for the RAW / integer formats) */
+  const void* wp;           /* packed image from b200dq_pack_weights                            */
   const void* bias;         /* optional (M, N) bias in the output dtype, or NULL                */
-  const float* row_scale;   /* optional per-token factor (M), or NULL                           */
+  const float* row_scale;   /* optional per-token divisor (M), or NULL                          */
   void* c;                  /* output (M, N) or, with TRANS_C, (N, M)                           */
   void* workspace;          /* scratch of at least b200dq_gemm_workspace_bytes() bytes          */
   size_t workspace_bytes;
@@ -92,27 +91,25 @@ int b200dq_gemm(const b200dq_gemm_args* args, void* cuda_stream);
 size_t b200dq_gemm_workspace_bytes(int32_t M, int32_t N, int32_t K, int32_t weight_format,
                                    int32_t act_type, int32_t token_tile, int32_t max_ctas);
 
-/* Bytes of the packed weight image / scale table for an (N, K) weight. */
-size_t b200dq_packed_weight_bytes(int32_t N, int32_t K, int32_t weight_format);
-size_t b200dq_packed_scale_bytes(int32_t N, int32_t K, int32_t group_size, int32_t weight_format);
+/* Bytes of the packed weight image (codes and scale words) for an (N, K) weight. */
+size_t b200dq_packed_weight_bytes(int32_t N, int32_t K, int32_t group_size, int32_t weight_format);
 
-/* Offline layout transform, on the device: natural (N, K*bits/8) little-endian
- * codes (element k in bits [(k % epb)*bits ...] of byte k / epb — the layout of
- * general_compress, examples/dequantize_gemm/quantize/utils.py:50-67) -> the
- * tiled, pre-interleaved image the GEMM streams with one bulk copy per k-block.
- * Plays the role of interleave_weight (quantize/utils.py:71-125) plus the tile
- * re-ordering the reference leaves to TMA/layout inference. `bits` is 2 or 4. */
-int b200dq_pack_weights(const void* q_natural, void* wp, int32_t N, int32_t K, int32_t bits,
-                        int32_t weight_format, void* cuda_stream);
-
-/* Scale/zero table for U4_SZ: scales and zeros are (N, K/group) in the
- * activation dtype (zeros may be NULL = fixed zero-point 8); the output holds
- * per (group, row) the pair {s, (8 - z) * s}. */
-int b200dq_pack_scales_u4(const void* scales, const void* zeros, void* sz, int32_t N, int32_t K,
-                          int32_t group_size, int32_t act_type, void* cuda_stream);
-
-/* Exponent table for FP4_E8M0: (N, K/32) bytes -> [K/64][N_pad] byte pairs. */
-int b200dq_pack_scales_e8m0(const void* exps, void* sz, int32_t N, int32_t K, void* cuda_stream);
+/* Offline layout transform, on the device. Input: natural (N, K*bits/8)
+ * little-endian codes (element k in bits [(k % epb)*bits ...] of byte k / epb, the
+ * layout of general_compress, examples/dequantize_gemm/quantize/utils.py:50-67)
+ * plus, per format:
+ *   U4_SZ    : scales and zeros (N, K/group_size) in the activation dtype
+ *              (zeros may be NULL = fixed zero-point 8); weight = (q - z) * s, the
+ *              reference's "original" zeros mode (quantize/lop3.py:684-689);
+ *   FP4_E8M0 : `scales` = (N, K/32) exponent bytes; zeros unused;
+ *   others   : scales and zeros unused (NULL).
+ * Output: the tiled, pre-interleaved image the GEMM streams with one bulk copy
+ * per stage (two k-blocks of codes followed by their scale words). Plays the role
+ * of interleave_weight (quantize/utils.py:71-125) plus the tile re-ordering the
+ * reference leaves to TMA/layout inference. K is padded to a whole stage. */
+int b200dq_pack_weights(const void* q_natural, const void* scales, const void* zeros, void* wp, int32_t N,
+                        int32_t K, int32_t group_size, int32_t weight_format, int32_t act_type,
+                        void* cuda_stream);
 
 /* Reads the device status word of the current device (synchronises `stream`).
  * Returns 0 if no kernel recorded an error since the last reset, else -1 with a

@@ -27,10 +27,7 @@ EXPORTED_SYMBOLS = (
     "b200dq_gemm",
     "b200dq_gemm_workspace_bytes",
     "b200dq_packed_weight_bytes",
-    "b200dq_packed_scale_bytes",
     "b200dq_pack_weights",
-    "b200dq_pack_scales_u4",
-    "b200dq_pack_scales_e8m0",
     "b200dq_check_status",
 )
 
@@ -41,7 +38,6 @@ class GemmArgs(ctypes.Structure):
     _fields_ = [
         ("a", ctypes.c_void_p),
         ("wp", ctypes.c_void_p),
-        ("sz", ctypes.c_void_p),
         ("bias", ctypes.c_void_p),
         ("row_scale", ctypes.c_void_p),
         ("c", ctypes.c_void_p),
@@ -84,15 +80,9 @@ def _declare(lib):
     lib.b200dq_gemm_workspace_bytes.restype = sz
     lib.b200dq_gemm_workspace_bytes.argtypes = [i32, i32, i32, i32, i32, i32, i32]
     lib.b200dq_packed_weight_bytes.restype = sz
-    lib.b200dq_packed_weight_bytes.argtypes = [i32, i32, i32]
-    lib.b200dq_packed_scale_bytes.restype = sz
-    lib.b200dq_packed_scale_bytes.argtypes = [i32, i32, i32, i32]
+    lib.b200dq_packed_weight_bytes.argtypes = [i32, i32, i32, i32]
     lib.b200dq_pack_weights.restype = ctypes.c_int
-    lib.b200dq_pack_weights.argtypes = [vp, vp, i32, i32, i32, i32, vp]
-    lib.b200dq_pack_scales_u4.restype = ctypes.c_int
-    lib.b200dq_pack_scales_u4.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
-    lib.b200dq_pack_scales_e8m0.restype = ctypes.c_int
-    lib.b200dq_pack_scales_e8m0.argtypes = [vp, vp, i32, i32, vp]
+    lib.b200dq_pack_weights.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
     lib.b200dq_check_status.restype = ctypes.c_int
     lib.b200dq_check_status.argtypes = [vp]
 

@@ -54,6 +54,7 @@ struct DeviceState {
 
 std::mutex g_mu;
 DeviceState g_dev[kMaxDevices];
+unsigned long long* g_prof = nullptr;   // profiling builds: per-CTA phase timers
 EncodeTiledFn g_encode = nullptr;
 
 int current_device_state(DeviceState** out) {
@@ -76,20 +77,38 @@ int token_tile_for(int M) {
 }
 
 struct Schedule {
-  int tn, m_tiles, n_tiles, kb_total, grid, span;
+  int tn, m_tiles, n_tiles, st_total, grid, span;
   long long units;
   size_t workspace_bytes;
 };
 
+int k_elems_per_kblock(int act_type) { return act_type == ACT_I8 ? 128 : 64; }
+
+// weight stages (2 k-blocks each) that cover K
+int stages_for(int K, int act_type) {
+  const int per_stage = 2 * k_elems_per_kblock(act_type);
+  return (K + per_stage - 1) / per_stage;
+}
+
+// scale words per row and stage
+int nsz_for(int weight_format, int group_size) {
+  if (weight_format == WF_U4_SZ) return group_size == 64 ? 2 : 1;
+  if (weight_format == WF_FP4_E8M0) return 1;
+  return 0;
+}
+
+int stage_bytes_for(int weight_format, int group_size) {
+  return 2 * codes_per_kblock_bytes(weight_format) + 512 * nsz_for(weight_format, group_size);
+}
+
 int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_ctas, int sm_count, Schedule* s) {
-  const int bke = (act_type == ACT_I8) ? 128 : 64;
   s->tn = token_tile > 0 ? token_tile : token_tile_for(M);
   if (s->tn != 16 && s->tn != 32 && s->tn != 64 && s->tn != 128 && s->tn != 256)
     return fail("token_tile must be 16, 32, 64, 128 or 256 (got %d)", s->tn);
   s->m_tiles = (M + s->tn - 1) / s->tn;
   s->n_tiles = (N + kTileRows - 1) / kTileRows;
-  s->kb_total = K / bke;
-  s->units = static_cast<long long>(s->m_tiles) * s->n_tiles * s->kb_total;
+  s->st_total = stages_for(K, act_type);
+  s->units = static_cast<long long>(s->m_tiles) * s->n_tiles * s->st_total;
   int cap = sm_count;
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   long long g = s->units / kMinSpan;
@@ -104,7 +123,7 @@ int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_cta
 int encode_activation_map(CUtensorMap* map, const void* a, int M, int K, int act_type, int tn) {
   if (g_encode == nullptr) return fail("tensor-map encoder not resolved (b200dq_init not run?)");
   const int esize = (act_type == ACT_I8) ? 1 : 2;
-  const int bke = (act_type == ACT_I8) ? 128 : 64;
+  const int bke = k_elems_per_kblock(act_type);
   if ((reinterpret_cast<uintptr_t>(a) & 15) != 0) return fail("activation pointer must be 16-byte aligned");
   if ((static_cast<long long>(K) * esize) % 16 != 0) return fail("activation row pitch must be a multiple of 16 bytes");
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
@@ -122,8 +141,35 @@ int encode_activation_map(CUtensorMap* map, const void* a, int M, int K, int act
   return 0;
 }
 
+int out_elem_size(int out_type) { return (out_type == OUT_F16 || out_type == OUT_BF16) ? 2 : 4; }
+
+// The epilogue stores through TMA when the output is (M, N) row-major with a
+// 16-byte aligned base and pitch; otherwise it falls back to plain stores.
+bool output_takes_tma(const void* c, int N, int out_type, int flags) {
+  if (flags & GF_TRANS_C) return false;
+  if ((reinterpret_cast<uintptr_t>(c) & 15) != 0) return false;
+  return (static_cast<long long>(N) * out_elem_size(out_type)) % 16 == 0;
+}
+
+int encode_output_map(CUtensorMap* map, void* c, int M, int N, int out_type, int tn) {
+  const int esize = out_elem_size(out_type);
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * esize};
+  cuuint32_t box[2] = {32u, static_cast<cuuint32_t>(tn >= 32 ? 32 : 16)};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = out_type == OUT_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                 : out_type == OUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : out_type == OUT_F32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                        : CU_TENSOR_MAP_DATA_TYPE_INT32;
+  CUresult r = g_encode(map, dt, 2, c, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled (output) failed with CUresult %d (M=%d N=%d)",
+                                     static_cast<int>(r), M, N);
+  return 0;
+}
+
 template <int TN, int WF, int ACT>
-int launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStream_t stream) {
+int launch_gemm(const CUtensorMap& tmap, const CUtensorMap& tmap_c, const GemmParams& p, int grid, cudaStream_t stream) {
   using Ring = RingConfig<TN, WF>;
   auto kernel = umma_dequant_gemm_kernel<TN, WF, ACT>;
   static bool attr_set[kMaxDevices] = {};
@@ -133,11 +179,11 @@ int launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStre
     CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring::kSmemBytes));
     attr_set[dev] = true;
   }
-  kernel<<<grid, kThreads, Ring::kSmemBytes, stream>>>(tmap, p);
+  kernel<<<grid, kThreads, Ring::kSmemBytes, stream>>>(tmap, tmap_c, p);
   CUDA_OK(cudaGetLastError());
   // stream-K second pass: only tiles cut between CTAs do any work
   const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
-  if (p.span % p.kb_total != 0 && grid > 1) {
+  if (p.span % p.st_total != 0 && grid > 1) {
     constexpr bool kInt = (ACT == ACT_I8);
     const int t = static_cast<int>(tiles);
     switch (p.out_type) {
@@ -152,13 +198,13 @@ int launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStre
 }
 
 template <int WF, int ACT>
-int dispatch_tn(int tn, const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStream_t stream) {
+int dispatch_tn(int tn, const CUtensorMap& tmap, const CUtensorMap& tmap_c, const GemmParams& p, int grid, cudaStream_t stream) {
   switch (tn) {
-    case 16: return launch_gemm<16, WF, ACT>(tmap, p, grid, stream);
-    case 32: return launch_gemm<32, WF, ACT>(tmap, p, grid, stream);
-    case 64: return launch_gemm<64, WF, ACT>(tmap, p, grid, stream);
-    case 128: return launch_gemm<128, WF, ACT>(tmap, p, grid, stream);
-    default: return launch_gemm<256, WF, ACT>(tmap, p, grid, stream);
+    case 16: return launch_gemm<16, WF, ACT>(tmap, tmap_c, p, grid, stream);
+    case 32: return launch_gemm<32, WF, ACT>(tmap, tmap_c, p, grid, stream);
+    case 64: return launch_gemm<64, WF, ACT>(tmap, tmap_c, p, grid, stream);
+    case 128: return launch_gemm<128, WF, ACT>(tmap, tmap_c, p, grid, stream);
+    default: return launch_gemm<256, WF, ACT>(tmap, tmap_c, p, grid, stream);
   }
 }
 
@@ -208,73 +254,58 @@ size_t b200dq_gemm_workspace_bytes(int32_t M, int32_t N, int32_t K, int32_t weig
   return s.workspace_bytes;
 }
 
-size_t b200dq_packed_weight_bytes(int32_t N, int32_t K, int32_t weight_format) {
+size_t b200dq_packed_weight_bytes(int32_t N, int32_t K, int32_t group_size, int32_t weight_format) {
+  if (N <= 0 || K <= 0 || weight_format < WF_U4_SZ || weight_format > WF_I4_I8) return 0;
   const int n_tiles = (N + kTileRows - 1) / kTileRows;
   const bool int8_target = (weight_format == WF_I2_I8 || weight_format == WF_I4_I8);
-  const int bke = int8_target ? 128 : 64;
-  return static_cast<size_t>(n_tiles) * (K / bke) * w_stage_bytes(weight_format);
+  const int st_total = stages_for(K, int8_target ? ACT_I8 : ACT_BF16);
+  return static_cast<size_t>(n_tiles) * st_total * stage_bytes_for(weight_format, group_size);
 }
 
-size_t b200dq_packed_scale_bytes(int32_t N, int32_t K, int32_t group_size, int32_t weight_format) {
-  const size_t n_pad = static_cast<size_t>((N + kTileRows - 1) / kTileRows) * kTileRows;
-  if (weight_format == WF_U4_SZ) return n_pad * (K / group_size) * sizeof(uint32_t);
-  if (weight_format == WF_FP4_E8M0) return n_pad * (K / 64) * sizeof(uint16_t);
-  return 0;
-}
-
-int b200dq_pack_weights(const void* q_natural, void* wp, int32_t N, int32_t K, int32_t bits, int32_t weight_format,
-                        void* cuda_stream) {
+int b200dq_pack_weights(const void* q_natural, const void* scales, const void* zeros, void* wp, int32_t N, int32_t K,
+                        int32_t group_size, int32_t weight_format, int32_t act_type, void* cuda_stream) {
   if (q_natural == nullptr || wp == nullptr) return fail("pack_weights: null pointer");
-  if (bits != 2 && bits != 4) return fail("pack_weights: bits must be 2 or 4 (got %d)", bits);
+  if (weight_format < WF_U4_SZ || weight_format > WF_I4_I8) return fail("pack_weights: unknown weight format %d", weight_format);
   const bool int8_target = (weight_format == WF_I2_I8 || weight_format == WF_I4_I8);
-  if ((weight_format == WF_I2_I8) != (bits == 2)) return fail("pack_weights: bits=%d does not match weight format %d", bits, weight_format);
-  const int bke = int8_target ? 128 : 64;
-  if (N <= 0 || K <= 0 || K % bke != 0) return fail("pack_weights: K=%d must be a positive multiple of %d", K, bke);
+  const int bits = weight_format == WF_I2_I8 ? 2 : 4;
+  if (N <= 0 || K <= 0) return fail("pack_weights: N and K must be positive");
+  if (K % (128 / bits) != 0) return fail("pack_weights: K=%d must be a multiple of %d for %d-bit codes", K, 128 / bits, bits);
   if ((reinterpret_cast<uintptr_t>(q_natural) & 3) != 0 || (reinterpret_cast<uintptr_t>(wp) & 15) != 0)
     return fail("pack_weights: input must be 4-byte and output 16-byte aligned");
-  const int n_tiles = (N + kTileRows - 1) / kTileRows;
-  const int kb_total = K / bke;
-  const int chunks = w_stage_bytes(weight_format) / 2048;
-  const int mode = int8_target ? 1 : (weight_format == WF_FP4_E8M0 ? 2 : 0);
-  const long long total = static_cast<long long>(n_tiles) * kb_total * chunks * 128 * 4;
+  PackParams p;
+  memset(&p, 0, sizeof(p));
+  p.q = static_cast<const uint32_t*>(q_natural);
+  p.wp = static_cast<uint32_t*>(wp);
+  p.N = N; p.K = K; p.bits = bits;
+  p.mode = int8_target ? 1 : (weight_format == WF_FP4_E8M0 ? 2 : 0);
+  p.n_tiles = (N + kTileRows - 1) / kTileRows;
+  p.st_total = stages_for(K, int8_target ? ACT_I8 : ACT_BF16);
+  p.code_words_per_kb = codes_per_kblock_bytes(weight_format) / 4;
+  p.elems_per_kblock = int8_target ? 128 : 64;
+  if (weight_format == WF_U4_SZ) {
+    if (scales == nullptr) return fail("pack_weights: this weight format needs scales");
+    if (act_type != ACT_F16 && act_type != ACT_BF16) return fail("pack_weights: scales must be f16 or bf16");
+    if (group_size <= 0 || K % group_size != 0) return fail("pack_weights: group_size=%d must divide K=%d", group_size, K);
+    if (!(group_size == 64 || group_size % 128 == 0 || group_size == K))
+      return fail("pack_weights: group_size=%d must be 64, a multiple of 128, or K", group_size);
+    p.sz_kind = 1;
+    p.scales = static_cast<const uint16_t*>(scales);
+    p.zeros = static_cast<const uint16_t*>(zeros);
+    p.bf16 = (act_type == ACT_BF16);
+    p.group_size = group_size;
+    p.groups = K / group_size;
+  } else if (weight_format == WF_FP4_E8M0) {
+    if (scales == nullptr) return fail("pack_weights: e2m1 weights need their exponent bytes");
+    if (K % 32 != 0) return fail("pack_weights: K=%d must be a multiple of 32", K);
+    p.sz_kind = 2;
+    p.exps = static_cast<const uint8_t*>(scales);
+  }
+  p.nsz = nsz_for(weight_format, group_size);
+  p.stage_words = stage_bytes_for(weight_format, group_size) / 4;
+  const long long total = static_cast<long long>(p.n_tiles) * p.st_total * p.stage_words;
   const int threads = 256;
   const long long blocks = (total + threads - 1) / threads;
-  pack_weights_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
-      static_cast<const uint32_t*>(q_natural), static_cast<uint32_t*>(wp), N, K, bits, mode, n_tiles, kb_total,
-      chunks, bke);
-  CUDA_OK(cudaGetLastError());
-  return 0;
-}
-
-int b200dq_pack_scales_u4(const void* scales, const void* zeros, void* sz, int32_t N, int32_t K, int32_t group_size,
-                          int32_t act_type, void* cuda_stream) {
-  if (scales == nullptr || sz == nullptr) return fail("pack_scales_u4: null pointer");
-  if (act_type != ACT_F16 && act_type != ACT_BF16) return fail("pack_scales_u4: activation type must be f16 or bf16");
-  if (group_size <= 0 || group_size % 64 != 0 || K % group_size != 0)
-    return fail("pack_scales_u4: group_size=%d must be a multiple of 64 that divides K=%d", group_size, K);
-  const int groups = K / group_size;
-  const int n_pad = (N + kTileRows - 1) / kTileRows * kTileRows;
-  dim3 grid((n_pad + 255) / 256, groups);
-  auto st = static_cast<cudaStream_t>(cuda_stream);
-  if (act_type == ACT_BF16)
-    pack_scales_u4_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(scales),
-                                                      static_cast<const uint16_t*>(zeros),
-                                                      static_cast<uint32_t*>(sz), N, groups, n_pad);
-  else
-    pack_scales_u4_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint16_t*>(scales),
-                                                       static_cast<const uint16_t*>(zeros),
-                                                       static_cast<uint32_t*>(sz), N, groups, n_pad);
-  CUDA_OK(cudaGetLastError());
-  return 0;
-}
-
-int b200dq_pack_scales_e8m0(const void* exps, void* sz, int32_t N, int32_t K, void* cuda_stream) {
-  if (exps == nullptr || sz == nullptr) return fail("pack_scales_e8m0: null pointer");
-  if (K % 64 != 0) return fail("pack_scales_e8m0: K=%d must be a multiple of 64", K);
-  const int n_pad = (N + kTileRows - 1) / kTileRows * kTileRows;
-  dim3 grid((n_pad + 255) / 256, K / 64);
-  pack_scales_e8m0_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
-      static_cast<const uint8_t*>(exps), static_cast<uint16_t*>(sz), N, K / 32, n_pad);
+  pack_image_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(cuda_stream)>>>(p);
   CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -291,15 +322,8 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
   if (a->out_type < OUT_F16 || a->out_type > OUT_I32) return fail("gemm: unknown output type %d", a->out_type);
   if (wf_int != int_act) return fail("gemm: weight format %d and activation type %d do not go together", wf, act);
   if (wf == WF_FP4_E8M0 && act != ACT_BF16) return fail("gemm: e2m1 weights need bf16 activations");
-  const int bke = int_act ? 128 : 64;
-  if (a->K % bke != 0) return fail("gemm: K=%d must be a multiple of %d", a->K, bke);
-  if ((wf == WF_U4_SZ || wf == WF_FP4_E8M0) && a->sz == nullptr) return fail("gemm: this weight format needs a scale table");
-  int group_kb = 1;
-  if (wf == WF_U4_SZ) {
-    if (a->group_size <= 0 || a->group_size % 64 != 0 || a->K % a->group_size != 0)
-      return fail("gemm: group_size=%d must be a multiple of 64 that divides K=%d", a->group_size, a->K);
-    group_kb = a->group_size / 64;
-  }
+  if (wf == WF_U4_SZ && (a->group_size <= 0 || a->K % a->group_size != 0))
+    return fail("gemm: group_size=%d must divide K=%d", a->group_size, a->K);
   if ((a->flags & GF_HAS_BIAS) && a->bias == nullptr) return fail("gemm: HAS_BIAS set but bias is null");
   if ((a->flags & GF_ROW_SCALE) && a->row_scale == nullptr) return fail("gemm: ROW_SCALE set but row_scale is null");
   if ((reinterpret_cast<uintptr_t>(a->wp) & 15) != 0) return fail("gemm: packed weights must be 16-byte aligned");
@@ -308,20 +332,26 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
   if (current_device_state(&ds) != 0) return -1;
   Schedule s;
   if (make_schedule(a->M, a->N, a->K, act, a->token_tile, a->max_ctas, ds->sm_count, &s) != 0) return -1;
-  const bool needs_ws = (s.span % s.kb_total != 0) && s.grid > 1;
+  const bool needs_ws = (s.span % s.st_total != 0) && s.grid > 1;
   if (needs_ws) {
     if (a->workspace == nullptr || a->workspace_bytes < s.workspace_bytes)
       return fail("gemm: workspace too small: need %zu bytes, got %zu", s.workspace_bytes, a->workspace_bytes);
     if ((reinterpret_cast<uintptr_t>(a->workspace) & 15) != 0) return fail("gemm: workspace must be 16-byte aligned");
   }
 
-  CUtensorMap tmap;
+  CUtensorMap tmap, tmap_c;
   if (encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn) != 0) return -1;
+  int flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
+  if (output_takes_tma(a->c, a->N, a->out_type, flags)) {
+    if (encode_output_map(&tmap_c, a->c, a->M, a->N, a->out_type, s.tn) != 0) return -1;
+    flags |= GF_TMA_STORE;
+  } else {
+    tmap_c = tmap;   // never dereferenced without GF_TMA_STORE
+  }
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.wp = static_cast<const uint8_t*>(a->wp);
-  p.sz = a->sz;
   p.c = a->c;
   p.partial = static_cast<uint32_t*>(a->workspace);
   p.bias = a->bias;
@@ -330,27 +360,33 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
   p.code_bias = a->code_bias;
   p.fp4_exp_bias = a->fp4_exp_bias;
   p.M = a->M; p.N = a->N; p.K = a->K;
-  p.n_tiles = s.n_tiles; p.m_tiles = s.m_tiles; p.kb_total = s.kb_total;
+  p.n_tiles = s.n_tiles; p.m_tiles = s.m_tiles; p.st_total = s.st_total;
   p.span = s.span; p.units = s.units;
-  p.group_kb = group_kb;
-  p.n_pad = s.n_tiles * kTileRows;
+  p.stage_bytes = stage_bytes_for(wf, a->group_size);
+  p.sz_per_kb = (wf == WF_U4_SZ && a->group_size == 64) ? 1 : 0;
   p.ldc = (a->flags & GF_TRANS_C) ? a->M : a->N;
-  p.flags = a->flags;
+  p.flags = flags;
   p.out_type = a->out_type;
   p.status = ds->status;
+  p.prof = g_prof;
 
   auto stream = static_cast<cudaStream_t>(cuda_stream);
-  if (wf == WF_U4_SZ && act == ACT_F16) return dispatch_tn<WF_U4_SZ, ACT_F16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_U4_SZ && act == ACT_BF16) return dispatch_tn<WF_U4_SZ, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_U4_RAW && act == ACT_F16) return dispatch_tn<WF_U4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_U4_RAW && act == ACT_BF16) return dispatch_tn<WF_U4_RAW, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_S4_RAW && act == ACT_F16) return dispatch_tn<WF_S4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_S4_RAW && act == ACT_BF16) return dispatch_tn<WF_S4_RAW, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_FP4_E8M0) return dispatch_tn<WF_FP4_E8M0, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_I2_I8) return dispatch_tn<WF_I2_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_I4_I8) return dispatch_tn<WF_I4_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_U4_SZ && act == ACT_F16) return dispatch_tn<WF_U4_SZ, ACT_F16>(s.tn, tmap, tmap_c, p, s.grid, stream);
+  if (wf == WF_U4_SZ && act == ACT_BF16) return dispatch_tn<WF_U4_SZ, ACT_BF16>(s.tn, tmap, tmap_c, p, s.grid, stream);
+  if (wf == WF_U4_RAW && act == ACT_F16) return dispatch_tn<WF_U4_RAW, ACT_F16>(s.tn, tmap, tmap_c, p, s.grid, stream);
+  if (wf == WF_U4_RAW && act == ACT_BF16) return dispatch_tn<WF_U4_RAW, ACT_BF16>(s.tn, tmap, tmap_c, p, s.grid, stream);
+  if (wf == WF_S4_RAW && act == ACT_F16) return dispatch_tn<WF_S4_RAW, ACT_F16>(s.tn, tmap, tmap_c, p, s.grid, stream);
+  if (wf == WF_S4_RAW && act == ACT_BF16) return dispatch_tn<WF_S4_RAW, ACT_BF16>(s.tn, tmap, tmap_c, p, s.grid, stream);
+  if (wf == WF_FP4_E8M0) return dispatch_tn<WF_FP4_E8M0, ACT_BF16>(s.tn, tmap, tmap_c, p, s.grid, stream);
+  if (wf == WF_I2_I8) return dispatch_tn<WF_I2_I8, ACT_I8>(s.tn, tmap, tmap_c, p, s.grid, stream);
+  if (wf == WF_I4_I8) return dispatch_tn<WF_I4_I8, ACT_I8>(s.tn, tmap, tmap_c, p, s.grid, stream);
   return fail("gemm: no kernel for weight format %d with activation type %d", wf, act);
 }
+
+#ifdef B200DQ_PROFILE
+// profiling builds only: device buffer of 32 x u64 per CTA for phase timers
+void b200dq_debug_set_profile_buffer(void* buf) { g_prof = static_cast<unsigned long long*>(buf); }
+#endif
 
 int b200dq_check_status(void* cuda_stream) {
   DeviceState* ds = nullptr;

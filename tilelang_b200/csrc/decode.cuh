@@ -37,29 +37,30 @@ __device__ __forceinline__ __nv_bfloat162 u32_as_bf162(uint32_t v) {
 __device__ __forceinline__ uint32_t h2_as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
 __device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
 
-// sz word: low 16 bits = scale s, high 16 bits = zero term c, both in the
-// activation dtype. Dequantised weight = (q - 8) * s + c, with c = (8 - z) * s
-// rounded once offline (c == 0 for the fixed zero-point 8).
+// uint4 with per-group scale s and zero-point z, weight = (q - z) * s.
+// The 4-bit code is masked in place: as a 16-bit float pattern it is the
+// subnormal q * 2^-133 (bf16) or q * 2^-24 (fp16). One fma by P = 2^127 (2^15)
+// with addend -z * 2^-6 (-z * 2^-9) gives (q - z) * 2^-6 (2^-9) -- exact whenever
+// q - z fits the mantissa (always for integer z) -- and one multiply by
+// s * 2^6 (s * 2^9) lands on the same value the reference's oracle computes in
+// fp32 and rounds once: RN((q - z) * s). sz word: low 16 bits = s * 2^6 (2^9),
+// high 16 bits = -z * 2^-6 (2^-9), both prepared offline in the activation dtype.
 template <bool kBf16>
 __device__ __forceinline__ void decode_u4_chunk(const uint4& packed, uint32_t sz, uint32_t (&out)[16]) {
   const uint32_t s2 = __byte_perm(sz, 0, 0x1010);
-  const uint32_t c2 = __byte_perm(sz, 0, 0x3232);
+  const uint32_t nz2 = __byte_perm(sz, 0, 0x3232);
   const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint32_t t = w[j] >> (4 * i);
+      const uint32_t x = (w[j] >> (4 * i)) & 0x000f000fu;
       if constexpr (kBf16) {
-        // 0x4300 = 128.0, 0x4308 = 136.0
-        const uint32_t x = lop3_and_or(t, 0x000f000fu, 0x43004300u);
-        const __nv_bfloat162 y = __hsub2(u32_as_bf162(x), u32_as_bf162(0x43084308u));
-        out[4 * j + i] = bf162_as_u32(__hfma2(y, u32_as_bf162(s2), u32_as_bf162(c2)));
+        const __nv_bfloat162 t = __hfma2(u32_as_bf162(x), u32_as_bf162(0x7f007f00u), u32_as_bf162(nz2));
+        out[4 * j + i] = bf162_as_u32(__hmul2(t, u32_as_bf162(s2)));
       } else {
-        // 0x6400 = 1024.0, 0x6408 = 1032.0
-        const uint32_t x = lop3_and_or(t, 0x000f000fu, 0x64006400u);
-        const __half2 y = __hsub2(u32_as_h2(x), u32_as_h2(0x64086408u));
-        out[4 * j + i] = h2_as_u32(__hfma2(y, u32_as_h2(s2), u32_as_h2(c2)));
+        const __half2 t = __hfma2(u32_as_h2(x), u32_as_h2(0x78007800u), u32_as_h2(nz2));
+        out[4 * j + i] = h2_as_u32(__hmul2(t, u32_as_h2(s2)));
       }
     }
   }

@@ -1,11 +1,14 @@
 // Offline layout transform (device side): natural little-endian packed codes
 // (N, K*bits/8) -> the tiled, pre-interleaved image the GEMM streams.
 //
-// Packed image: [n_tile][k_block][chunk][row 0..127][16 bytes]. One
-// (n_tile, k_block) stage is contiguous (4 KiB, or 8 KiB for 4-bit codes feeding
-// int8), so the kernel fetches it with a single bulk copy, and the dequant
-// thread of row r reads chunk c at byte c*2048 + r*16 — consecutive rows hit
-// consecutive 16-byte slots, which is bank-conflict free.
+// Packed image: [n_tile][stage][ codes of 2 k-blocks | scale words ], where the
+// codes of one k-block are [chunk][row 0..127][16 bytes] and the scale words are
+// [word][row 0..127][4 bytes]. One (n_tile, stage) record is contiguous, so the
+// kernel fetches it with a single bulk copy, and the dequant thread of row r
+// reads chunk c at byte c*2048 + r*16: consecutive rows hit consecutive 16-byte
+// slots, which is bank-conflict free. The scale words of the k-blocks travel in
+// the same record, so the dequant warps never touch global memory. K is padded
+// to a whole stage with zero codes and zero scales.
 //
 // Inside a 32-bit word the codes are permuted for the shift-and-mask decoders
 // (decode.cuh). For integer codes this is the permutation of the reference's
@@ -51,72 +54,86 @@ __host__ __device__ inline uint32_t twiddle_fp4_word(uint32_t w) {
   return out;
 }
 
-// mode: 0 = integer codes -> 16-bit target, 1 = integer codes -> 8-bit target, 2 = e2m1 -> bf16
-__global__ void pack_weights_kernel(const uint32_t* __restrict__ q, uint32_t* __restrict__ wp, int N, int K,
-                                    int bits, int mode, int n_tiles, int kb_total, int chunks,
-                                    int elems_per_kblock) {
-  // one thread per output word
-  const long long total = static_cast<long long>(n_tiles) * kb_total * chunks * 128 * 4;
+struct PackParams {
+  const uint32_t* q;        // natural codes, (N, K*bits/8) bytes viewed as words
+  const uint16_t* scales;   // U4_SZ: (N, groups) in the activation dtype
+  const uint16_t* zeros;    // U4_SZ: (N, groups) or nullptr (zero-point 8)
+  const uint8_t* exps;      // FP4_E8M0: (N, K/32) exponent bytes
+  uint32_t* wp;             // packed image
+  int N, K, bits;
+  int mode;                 // 0 integer codes -> 16-bit, 1 integer codes -> 8-bit, 2 e2m1 -> bf16
+  int sz_kind;              // 0 none, 1 u4 scale/zero words, 2 e8m0 byte quads
+  int bf16;                 // activation dtype of the scale words
+  int n_tiles, st_total;
+  int code_words_per_kb;    // 1024 or 2048
+  int stage_words;          // 2 * code_words_per_kb + 128 * nsz
+  int elems_per_kblock;     // 64 or 128
+  int group_size;           // U4_SZ
+  int groups;               // K / group_size (U4_SZ)
+  int nsz;                  // scale words per row and stage (0, 1 or 2)
+};
+
+// One thread per 32-bit word of the packed image:
+//   [n_tile][stage][ codes: [k-block 2][chunk][row 128][4 words] | scale words: [nsz][row 128] ]
+__global__ void pack_image_kernel(const PackParams p) {
+  const long long total = static_cast<long long>(p.n_tiles) * p.st_total * p.stage_words;
   const long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
   if (idx >= total) return;
-  const int j = static_cast<int>(idx & 3);                 // word in the 16-byte slot
-  const int r = static_cast<int>((idx >> 2) & 127);        // row in tile
-  long long rest = idx >> 9;
-  const int c = static_cast<int>(rest % chunks); rest /= chunks;
-  const int kb = static_cast<int>(rest % kb_total);
-  const int nt = static_cast<int>(rest / kb_total);
-  const int n = nt * 128 + r;
-  const int elems_per_word = 32 / bits;
-  const int k0 = kb * elems_per_kblock + (c * 4 + j) * elems_per_word;
-  uint32_t w = 0;
-  if (n < N && k0 < K) {
-    const long long word_idx = (static_cast<long long>(n) * K + k0) / elems_per_word;
-    w = q[word_idx];
-  }
-  uint32_t out;
-  if (mode == 0) out = interleave_word(w, bits, 16);
-  else if (mode == 1) out = interleave_word(w, bits, 8);
-  else out = twiddle_fp4_word(w);
-  wp[idx] = out;
-}
-
-template <bool kBf16>
-__global__ void pack_scales_u4_kernel(const uint16_t* __restrict__ scales, const uint16_t* __restrict__ zeros,
-                                      uint32_t* __restrict__ sz, int N, int groups, int n_pad) {
-  const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  const int g = blockIdx.y;
-  if (n >= n_pad) return;
+  const int wi = static_cast<int>(idx % p.stage_words);
+  const long long rest = idx / p.stage_words;
+  const int stg = static_cast<int>(rest % p.st_total);
+  const int nt = static_cast<int>(rest / p.st_total);
   uint32_t out = 0;
-  if (n < N) {
-    const uint16_t s_raw = scales[static_cast<size_t>(n) * groups + g];
-    float s, z = 8.f;
-    if constexpr (kBf16) {
-      s = __bfloat162float(__ushort_as_bfloat16(s_raw));
-      if (zeros) z = __bfloat162float(__ushort_as_bfloat16(zeros[static_cast<size_t>(n) * groups + g]));
-      const float c = (8.f - z) * s;
-      out = s_raw | (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(c))) << 16);
-    } else {
-      s = __half2float(__ushort_as_half(s_raw));
-      if (zeros) z = __half2float(__ushort_as_half(zeros[static_cast<size_t>(n) * groups + g]));
-      const float c = (8.f - z) * s;
-      out = s_raw | (static_cast<uint32_t>(__half_as_ushort(__float2half_rn(c))) << 16);
+  if (wi < 2 * p.code_words_per_kb) {
+    const int h = wi / p.code_words_per_kb;
+    const int r = wi % p.code_words_per_kb;
+    const int j = r & 3;
+    const int row = (r >> 2) & 127;
+    const int c = r >> 9;
+    const int n = nt * 128 + row;
+    const int elems_per_word = 32 / p.bits;
+    const int k0 = (stg * 2 + h) * p.elems_per_kblock + (c * 4 + j) * elems_per_word;
+    uint32_t w = 0;
+    if (n < p.N && k0 < p.K) w = p.q[(static_cast<long long>(n) * p.K + k0) / elems_per_word];
+    if (p.mode == 0) out = interleave_word(w, p.bits, 16);
+    else if (p.mode == 1) out = interleave_word(w, p.bits, 8);
+    else out = twiddle_fp4_word(w);
+  } else {
+    const int r = wi - 2 * p.code_words_per_kb;
+    const int si = r >> 7;
+    const int row = r & 127;
+    const int n = nt * 128 + row;
+    if (n < p.N) {
+      if (p.sz_kind == 1) {
+        const int k_start = (stg * 2 + (p.nsz == 2 ? si : 0)) * 64;
+        if (k_start < p.K) {
+          const int g = min(k_start / p.group_size, p.groups - 1);
+          const uint16_t s_raw = p.scales[static_cast<size_t>(n) * p.groups + g];
+          uint16_t lo, hi;
+          if (p.bf16) {
+            const float s = __bfloat162float(__ushort_as_bfloat16(s_raw));
+            const float z = p.zeros ? __bfloat162float(__ushort_as_bfloat16(p.zeros[static_cast<size_t>(n) * p.groups + g])) : 8.f;
+            lo = __bfloat16_as_ushort(__float2bfloat16_rn(s * 64.f));
+            hi = __bfloat16_as_ushort(__float2bfloat16_rn(-z * 0.015625f));
+          } else {
+            const float s = __half2float(__ushort_as_half(s_raw));
+            const float z = p.zeros ? __half2float(__ushort_as_half(p.zeros[static_cast<size_t>(n) * p.groups + g])) : 8.f;
+            lo = __half_as_ushort(__float2half_rn(s * 512.f));
+            hi = __half_as_ushort(__float2half_rn(-z * 0.001953125f));
+          }
+          out = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+        }
+      } else if (p.sz_kind == 2) {
+        const int blocks32 = p.K / 32;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int kb32 = stg * 4 + b;
+          if (kb32 < blocks32) out |= static_cast<uint32_t>(p.exps[static_cast<size_t>(n) * blocks32 + kb32]) << (8 * b);
+        }
+      }
     }
   }
-  sz[static_cast<size_t>(g) * n_pad + n] = out;
-}
-
-__global__ void pack_scales_e8m0_kernel(const uint8_t* __restrict__ exps, uint16_t* __restrict__ sz, int N,
-                                        int blocks32, int n_pad) {
-  const int n = blockIdx.x * blockDim.x + threadIdx.x;
-  const int kb = blockIdx.y;
-  if (n >= n_pad) return;
-  uint16_t out = 0;
-  if (n < N) {
-    const uint8_t e0 = exps[static_cast<size_t>(n) * blocks32 + 2 * kb];
-    const uint8_t e1 = exps[static_cast<size_t>(n) * blocks32 + 2 * kb + 1];
-    out = static_cast<uint16_t>(e0) | (static_cast<uint16_t>(e1) << 8);
-  }
-  sz[static_cast<size_t>(kb) * n_pad + n] = out;
+  p.wp[idx] = out;
 }
 
 }  // namespace b200dq

@@ -53,8 +53,7 @@ def _check_cuda_contig(name: str, t: torch.Tensor, device: Optional[torch.device
 class PackedWeight:
     """A weight in the library's private device layout (see csrc/pack_kernels.cuh)."""
 
-    wp: torch.Tensor                 # uint8 packed image
-    sz: Optional[torch.Tensor]       # scale table or None
+    wp: torch.Tensor                 # uint8 packed image: codes and scale words, stage by stage
     N: int
     K: int
     weight_format: int
@@ -68,10 +67,11 @@ class PackedWeight:
         return self.wp.device
 
     def nbytes(self) -> int:
-        return self.wp.numel() + (self.sz.numel() * self.sz.element_size() if self.sz is not None else 0)
+        return self.wp.numel()
 
 
-def _pack_codes(q: torch.Tensor, N: int, K: int, bits: int, weight_format: int) -> torch.Tensor:
+def _pack(q: torch.Tensor, scales: Optional[torch.Tensor], zeros: Optional[torch.Tensor], N: int, K: int,
+          bits: int, group_size: int, weight_format: int, act_type: int) -> torch.Tensor:
     lib = _lib.load()
     _check_cuda_contig("packed weight codes", q)
     if q.dtype not in (torch.uint8, torch.int8):
@@ -79,11 +79,13 @@ def _pack_codes(q: torch.Tensor, N: int, K: int, bits: int, weight_format: int) 
     if tuple(q.shape) != (N, K * bits // 8):
         raise ValueError(f"packed weight codes must have shape {(N, K * bits // 8)}, got {tuple(q.shape)}")
     _ensure_init(q.device)
-    nbytes = lib.b200dq_packed_weight_bytes(N, K, weight_format)
+    nbytes = lib.b200dq_packed_weight_bytes(N, K, group_size, weight_format)
     wp = torch.empty(nbytes, dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
-        _lib.check(lib.b200dq_pack_weights(q.data_ptr(), wp.data_ptr(), N, K, bits, weight_format,
-                                           _stream_ptr(q.device)), "b200dq_pack_weights")
+        _lib.check(lib.b200dq_pack_weights(q.data_ptr(), scales.data_ptr() if scales is not None else None,
+                                           zeros.data_ptr() if zeros is not None else None, wp.data_ptr(), N, K,
+                                           group_size, weight_format, act_type, _stream_ptr(q.device)),
+                   "b200dq_pack_weights")
     return wp
 
 
@@ -104,10 +106,9 @@ def pack_w4a16(qweight: torch.Tensor, scales: Optional[torch.Tensor], zeros: Opt
         if zeros is not None:
             raise ValueError("zeros without scales is not supported")
         wf = WF_S4_RAW if signed_storage else WF_U4_RAW
-        return PackedWeight(_pack_codes(qweight, N, K, 4, wf), None, N, K, wf, act)
+        return PackedWeight(_pack(qweight, None, None, N, K, 4, 0, wf, act), N, K, wf, act)
     if group_size in (-1, 0, None):
         group_size = K
-    lib = _lib.load()
     groups = K // group_size
     for name, t in (("scales", scales), ("zeros", zeros)):
         if t is None:
@@ -115,14 +116,8 @@ def pack_w4a16(qweight: torch.Tensor, scales: Optional[torch.Tensor], zeros: Opt
         _check_cuda_contig(name, t, qweight.device)
         if t.dtype != dtype or tuple(t.shape) != (N, groups):
             raise ValueError(f"{name} must be {dtype} of shape {(N, groups)}, got {t.dtype} {tuple(t.shape)}")
-    wp = _pack_codes(qweight, N, K, 4, WF_U4_SZ)
-    sz = torch.empty(lib.b200dq_packed_scale_bytes(N, K, group_size, WF_U4_SZ), dtype=torch.uint8,
-                     device=qweight.device)
-    with torch.cuda.device(qweight.device):
-        _lib.check(lib.b200dq_pack_scales_u4(scales.data_ptr(), zeros.data_ptr() if zeros is not None else None,
-                                             sz.data_ptr(), N, K, group_size, act, _stream_ptr(qweight.device)),
-                   "b200dq_pack_scales_u4")
-    return PackedWeight(wp, sz, N, K, WF_U4_SZ, act, group_size=group_size)
+    wp = _pack(qweight, scales, zeros, N, K, 4, group_size, WF_U4_SZ, act)
+    return PackedWeight(wp, N, K, WF_U4_SZ, act, group_size=group_size)
 
 
 def pack_mxfp4(qweight: torch.Tensor, scale_bytes: torch.Tensor, N: int, K: int, exp_bias: int = 127) -> PackedWeight:
@@ -132,29 +127,24 @@ def pack_mxfp4(qweight: torch.Tensor, scale_bytes: torch.Tensor, N: int, K: int,
     exponent the reference's hopper example applies with ``2**Scale``
     (example_dequant_gemm_bf16_mxfp4_hopper.py:397).
     """
-    lib = _lib.load()
     _check_cuda_contig("scale bytes", scale_bytes, qweight.device)
     if scale_bytes.dtype != torch.uint8 or tuple(scale_bytes.shape) != (N, K // 32):
         raise ValueError(f"scale bytes must be uint8 of shape {(N, K // 32)}")
-    wp = _pack_codes(qweight, N, K, 4, WF_FP4_E8M0)
-    sz = torch.empty(lib.b200dq_packed_scale_bytes(N, K, 32, WF_FP4_E8M0), dtype=torch.uint8, device=qweight.device)
-    with torch.cuda.device(qweight.device):
-        _lib.check(lib.b200dq_pack_scales_e8m0(scale_bytes.data_ptr(), sz.data_ptr(), N, K,
-                                               _stream_ptr(qweight.device)), "b200dq_pack_scales_e8m0")
-    return PackedWeight(wp, sz, N, K, WF_FP4_E8M0, ACT_BF16, group_size=32, fp4_exp_bias=exp_bias)
+    wp = _pack(qweight, scale_bytes, None, N, K, 4, 32, WF_FP4_E8M0, ACT_BF16)
+    return PackedWeight(wp, N, K, WF_FP4_E8M0, ACT_BF16, group_size=32, fp4_exp_bias=exp_bias)
 
 
 def pack_int2(qweight: torch.Tensor, N: int, K: int, code_offset: int = 0) -> PackedWeight:
     """2-bit codes (N, K/4), code k in bits [2(k%4), 2(k%4)+1] of byte k//4; weight = code - code_offset."""
     b = code_offset & 0xFF
-    return PackedWeight(_pack_codes(qweight, N, K, 2, WF_I2_I8), None, N, K, WF_I2_I8, ACT_I8,
+    return PackedWeight(_pack(qweight, None, None, N, K, 2, 0, WF_I2_I8, ACT_I8), N, K, WF_I2_I8, ACT_I8,
                         code_bias=b | (b << 8) | (b << 16) | (b << 24))
 
 
 def pack_int4_for_int8(qweight: torch.Tensor, N: int, K: int, code_offset: int = 0) -> PackedWeight:
     """4-bit codes (N, K/2) feeding an int8 MMA; weight = code - code_offset."""
     b = code_offset & 0xFF
-    return PackedWeight(_pack_codes(qweight, N, K, 4, WF_I4_I8), None, N, K, WF_I4_I8, ACT_I8,
+    return PackedWeight(_pack(qweight, None, None, N, K, 4, 0, WF_I4_I8, ACT_I8), N, K, WF_I4_I8, ACT_I8,
                         code_bias=b | (b << 8) | (b << 16) | (b << 24))
 
 
@@ -214,7 +204,7 @@ def gemm(A: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None,
     elif workspace.numel() * workspace.element_size() < need:
         raise ValueError(f"workspace too small: need {need} bytes")
     args = _lib.GemmArgs(
-        a=A.data_ptr(), wp=w.wp.data_ptr(), sz=w.sz.data_ptr() if w.sz is not None else None,
+        a=A.data_ptr(), wp=w.wp.data_ptr(),
         bias=bias.data_ptr() if bias is not None else None,
         row_scale=row_scale.data_ptr() if row_scale is not None else None,
         c=out.data_ptr(), workspace=workspace.data_ptr(),
