@@ -143,33 +143,16 @@ int encode_activation_map(CUtensorMap* map, const void* a, int M, int K, int act
 
 int out_elem_size(int out_type) { return (out_type == OUT_F16 || out_type == OUT_BF16) ? 2 : 4; }
 
-// The epilogue stores through TMA when the output is (M, N) row-major with a
-// 16-byte aligned base and pitch; otherwise it falls back to plain stores.
-bool output_takes_tma(const void* c, int N, int out_type, int flags) {
+// The epilogue uses 16-byte stores when the output is (M, N) row-major with a
+// 16-byte aligned base and pitch; otherwise it falls back to element stores.
+bool output_takes_vector_stores(const void* c, int N, int out_type, int flags) {
   if (flags & GF_TRANS_C) return false;
   if ((reinterpret_cast<uintptr_t>(c) & 15) != 0) return false;
   return (static_cast<long long>(N) * out_elem_size(out_type)) % 16 == 0;
 }
 
-int encode_output_map(CUtensorMap* map, void* c, int M, int N, int out_type, int tn) {
-  const int esize = out_elem_size(out_type);
-  cuuint64_t dims[2] = {static_cast<cuuint64_t>(N), static_cast<cuuint64_t>(M)};
-  cuuint64_t strides[1] = {static_cast<cuuint64_t>(N) * esize};
-  cuuint32_t box[2] = {32u, static_cast<cuuint32_t>(tn >= 32 ? 32 : 16)};
-  cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapDataType dt = out_type == OUT_F16    ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
-                                 : out_type == OUT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                 : out_type == OUT_F32  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                                        : CU_TENSOR_MAP_DATA_TYPE_INT32;
-  CUresult r = g_encode(map, dt, 2, c, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled (output) failed with CUresult %d (M=%d N=%d)",
-                                     static_cast<int>(r), M, N);
-  return 0;
-}
-
 template <int TN, int WF, int ACT>
-int launch_gemm(const CUtensorMap& tmap, const CUtensorMap& tmap_c, const GemmParams& p, int grid, cudaStream_t stream) {
+int launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStream_t stream) {
   using Ring = RingConfig<TN, WF>;
   auto kernel = umma_dequant_gemm_kernel<TN, WF, ACT>;
   static bool attr_set[kMaxDevices] = {};
@@ -179,7 +162,7 @@ int launch_gemm(const CUtensorMap& tmap, const CUtensorMap& tmap_c, const GemmPa
     CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring::kSmemBytes));
     attr_set[dev] = true;
   }
-  kernel<<<grid, kThreads, Ring::kSmemBytes, stream>>>(tmap, tmap_c, p);
+  kernel<<<grid, kThreads, Ring::kSmemBytes, stream>>>(tmap, p);
   CUDA_OK(cudaGetLastError());
   // stream-K second pass: only tiles cut between CTAs do any work
   const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
@@ -198,13 +181,13 @@ int launch_gemm(const CUtensorMap& tmap, const CUtensorMap& tmap_c, const GemmPa
 }
 
 template <int WF, int ACT>
-int dispatch_tn(int tn, const CUtensorMap& tmap, const CUtensorMap& tmap_c, const GemmParams& p, int grid, cudaStream_t stream) {
+int dispatch_tn(int tn, const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStream_t stream) {
   switch (tn) {
-    case 16: return launch_gemm<16, WF, ACT>(tmap, tmap_c, p, grid, stream);
-    case 32: return launch_gemm<32, WF, ACT>(tmap, tmap_c, p, grid, stream);
-    case 64: return launch_gemm<64, WF, ACT>(tmap, tmap_c, p, grid, stream);
-    case 128: return launch_gemm<128, WF, ACT>(tmap, tmap_c, p, grid, stream);
-    default: return launch_gemm<256, WF, ACT>(tmap, tmap_c, p, grid, stream);
+    case 16: return launch_gemm<16, WF, ACT>(tmap, p, grid, stream);
+    case 32: return launch_gemm<32, WF, ACT>(tmap, p, grid, stream);
+    case 64: return launch_gemm<64, WF, ACT>(tmap, p, grid, stream);
+    case 128: return launch_gemm<128, WF, ACT>(tmap, p, grid, stream);
+    default: return launch_gemm<256, WF, ACT>(tmap, p, grid, stream);
   }
 }
 
@@ -339,15 +322,10 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
     if ((reinterpret_cast<uintptr_t>(a->workspace) & 15) != 0) return fail("gemm: workspace must be 16-byte aligned");
   }
 
-  CUtensorMap tmap, tmap_c;
+  CUtensorMap tmap;
   if (encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn) != 0) return -1;
   int flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
-  if (output_takes_tma(a->c, a->N, a->out_type, flags)) {
-    if (encode_output_map(&tmap_c, a->c, a->M, a->N, a->out_type, s.tn) != 0) return -1;
-    flags |= GF_TMA_STORE;
-  } else {
-    tmap_c = tmap;   // never dereferenced without GF_TMA_STORE
-  }
+  if (output_takes_vector_stores(a->c, a->N, a->out_type, flags)) flags |= GF_VEC_STORE;
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
@@ -371,15 +349,15 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
   p.prof = g_prof;
 
   auto stream = static_cast<cudaStream_t>(cuda_stream);
-  if (wf == WF_U4_SZ && act == ACT_F16) return dispatch_tn<WF_U4_SZ, ACT_F16>(s.tn, tmap, tmap_c, p, s.grid, stream);
-  if (wf == WF_U4_SZ && act == ACT_BF16) return dispatch_tn<WF_U4_SZ, ACT_BF16>(s.tn, tmap, tmap_c, p, s.grid, stream);
-  if (wf == WF_U4_RAW && act == ACT_F16) return dispatch_tn<WF_U4_RAW, ACT_F16>(s.tn, tmap, tmap_c, p, s.grid, stream);
-  if (wf == WF_U4_RAW && act == ACT_BF16) return dispatch_tn<WF_U4_RAW, ACT_BF16>(s.tn, tmap, tmap_c, p, s.grid, stream);
-  if (wf == WF_S4_RAW && act == ACT_F16) return dispatch_tn<WF_S4_RAW, ACT_F16>(s.tn, tmap, tmap_c, p, s.grid, stream);
-  if (wf == WF_S4_RAW && act == ACT_BF16) return dispatch_tn<WF_S4_RAW, ACT_BF16>(s.tn, tmap, tmap_c, p, s.grid, stream);
-  if (wf == WF_FP4_E8M0) return dispatch_tn<WF_FP4_E8M0, ACT_BF16>(s.tn, tmap, tmap_c, p, s.grid, stream);
-  if (wf == WF_I2_I8) return dispatch_tn<WF_I2_I8, ACT_I8>(s.tn, tmap, tmap_c, p, s.grid, stream);
-  if (wf == WF_I4_I8) return dispatch_tn<WF_I4_I8, ACT_I8>(s.tn, tmap, tmap_c, p, s.grid, stream);
+  if (wf == WF_U4_SZ && act == ACT_F16) return dispatch_tn<WF_U4_SZ, ACT_F16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_U4_SZ && act == ACT_BF16) return dispatch_tn<WF_U4_SZ, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_U4_RAW && act == ACT_F16) return dispatch_tn<WF_U4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_U4_RAW && act == ACT_BF16) return dispatch_tn<WF_U4_RAW, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_S4_RAW && act == ACT_F16) return dispatch_tn<WF_S4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_S4_RAW && act == ACT_BF16) return dispatch_tn<WF_S4_RAW, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_FP4_E8M0) return dispatch_tn<WF_FP4_E8M0, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_I2_I8) return dispatch_tn<WF_I2_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_I4_I8) return dispatch_tn<WF_I4_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
   return fail("gemm: no kernel for weight format %d with activation type %d", wf, act);
 }
 

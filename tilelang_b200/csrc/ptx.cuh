@@ -79,6 +79,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking probe: unlike try_wait, which may suspend the thread for a
+// hardware-chosen time before answering, test_wait answers at once.
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait. `abort_flag` lives in shared memory; once set, every wait of the
 // CTA returns at once. Returns false if the wait gave up (or the CTA aborted).
 __device__ __noinline__ void mbar_wait_failed(volatile int* abort_flag, DeviceStatus* st,
@@ -109,6 +123,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       }
     }
   }
+}
+
+// Warp-wide wait with a single polling lane: 32 lanes spinning on the same
+// barrier flood the shared-memory pipe that the producer's TMA issue and every
+// mbarrier arrive also go through (measured: one TMA issue rose from 60 to 500
+// cycles), so lane 0 polls and the others park on the warp barrier.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               DeviceStatus* st, uint32_t site, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag, st, site) ? 1 : 0;
+  __syncwarp();
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
 // ---------------------------------- TMA --------------------------------------

@@ -26,7 +26,7 @@
 //                 narrow token tiles NI = 2 or 3 issuers take k-blocks round-robin,
 //                 each into its own accumulator; the epilogue adds them.
 //   warps 4-11  : two dequant warpgroups, alternating weight stages
-//   warps 12-15 : epilogue (tcgen05.ld -> convert -> smem -> TMA store)
+//   warps 12-15 : epilogue (tcgen05.ld -> convert -> smem transpose -> 16-byte stores)
 //
 // k-block = 64 16-bit (128 8-bit) K elements = one 128 B swizzle atom of activations.
 //   full_w/empty_w : packed weight ring, per stage      (TMA -> dequant warps)
@@ -76,7 +76,7 @@ enum GemmFlags : int {
   GF_TRANS_C = 1,      // write C^T (N x M) instead of C (M x N)
   GF_HAS_BIAS = 2,     // add bias[M][N] (output dtype) in the epilogue
   GF_ROW_SCALE = 4,    // integer path: acc / row_scale[m] / tensor_scale before the cast
-  GF_TMA_STORE = 8,    // internal: the output qualifies for TMA stores
+  GF_VEC_STORE = 8,    // internal: base and pitch of the output allow 16-byte stores
 };
 
 struct GemmParams {
@@ -102,27 +102,34 @@ struct GemmParams {
 };
 
 constexpr int kTileRows = 128;        // weight rows per CTA tile (= TMEM lanes)
-constexpr int kAccCols = 256;         // first TMEM column of the dequantised ring
-constexpr int kASlots = 8;            // TMEM ring slots, 32 columns (one k-block) each
 constexpr int kThreads = 512;
-constexpr int kStagingBytesPerWarp = 2 * 32 * 32 * 4;   // double-buffered 32x32 4-byte tile
+constexpr int kStageBufBytes = 2048;                    // one epilogue staging buffer: 32 n x 32 m x 2 B
+constexpr int kStagingBytesPerWarp = 2 * kStageBufBytes;   // double-buffered
+constexpr int kMaxSlots = 16;
 
 __host__ __device__ constexpr int codes_per_kblock_bytes(int wf) { return wf == WF_I4_I8 ? 8192 : 4096; }
 // scale words carried by one stage in shared memory (upper bound, bytes)
 __host__ __device__ constexpr int sz_smem_bytes(int wf) { return wf == WF_U4_SZ ? 1024 : (wf == WF_FP4_E8M0 ? 512 : 0); }
 __host__ __device__ constexpr int issuers_for(int tn) { return tn >= 256 ? 1 : (tn >= 128 ? 2 : 3); }
 
+// TMEM plan: accumulators of the NI issuers in columns [0, kAccCols), then a ring
+// of kSlots dequantised k-blocks (32 columns each). The activation ring in shared
+// memory has at most as many stages, so one "consumed" barrier per slot serves both.
 template <int TN, int WF>
 struct RingConfig {
+  static constexpr int kNI = issuers_for(TN);
+  static constexpr int kAccCols = ((kNI * TN + 31) / 32) * 32;
+  static constexpr int kSlots = (512 - kAccCols) / 32 > 14 ? 14 : (512 - kAccCols) / 32;
   static constexpr int kBStageBytes = TN * 128;
   static constexpr int kCodeBytes = 2 * codes_per_kblock_bytes(WF);          // per stage
   static constexpr int kWStageSmem = kCodeBytes + sz_smem_bytes(WF);         // smem stride
-  static constexpr int kNB = TN >= 256 ? 4 : (TN >= 128 ? 6 : 8);
-  static constexpr int kWBudget = TN >= 256 ? 56 * 1024 : (TN >= 128 ? 76 * 1024 : 112 * 1024);
+  static constexpr int kNB = TN >= 256 ? 5 : kSlots;
+  static constexpr int kWBudget = TN >= 256 ? 37 * 1024 : (TN >= 128 ? 74 * 1024 : 110 * 1024);
   static constexpr int kNW = kWBudget / kWStageSmem;
   static constexpr int kStaging = 4 * kStagingBytesPerWarp;
   static constexpr int kSmemBytes = kNB * kBStageBytes + kNW * kWStageSmem + kStaging + 1024 /*align*/ + 1024 /*ctl*/;
-  static_assert(kNW >= 3 && kNW <= 32, "weight ring depth");
+  static_assert(kSlots >= 8 && kSlots <= kMaxSlots && kNB <= kSlots, "ring depths");
+  static_assert(kNW >= 2 && kNW <= 32, "weight ring depth");
   static_assert(kWStageSmem % 128 == 0, "stage stride keeps 128 B alignment");
   static_assert(kSmemBytes <= 232448, "over the 227 KiB shared-memory limit");
 };
@@ -130,9 +137,9 @@ struct RingConfig {
 struct SharedCtl {
   uint64_t full_w[32];
   uint64_t empty_w[32];
-  uint64_t full_b[8];
-  uint64_t a_full[kASlots];
-  uint64_t cons[kASlots];
+  uint64_t full_b[kMaxSlots];
+  uint64_t a_full[kMaxSlots];
+  uint64_t cons[kMaxSlots];
   uint64_t acc_full;
   uint64_t acc_empty;
   uint32_t tmem_base;
@@ -162,8 +169,10 @@ struct SegmentWalk {
     s.st_begin = static_cast<int>(pos - tile * p.st_total);
     const long long left = end - pos;
     s.st_end = static_cast<int>(min(static_cast<long long>(p.st_total), s.st_begin + left));
-    s.m_tile = static_cast<int>(tile % p.m_tiles);
-    s.n_tile = static_cast<int>(tile / p.m_tiles);
+    // n fastest: the CTAs working at the same time share a few token slabs (which
+    // stay in L2) and stream different weight tiles
+    s.n_tile = static_cast<int>(tile % p.n_tiles);
+    s.m_tile = static_cast<int>(tile / p.n_tiles);
     const bool whole = (s.st_begin == 0 && s.st_end == p.st_total);
     s.slot = whole ? -1 : (static_cast<int>(blockIdx.x) * 2 + (first ? 0 : 1));
     first = false;
@@ -217,52 +226,72 @@ __device__ __forceinline__ void store_values_direct(const GemmParams& p, const u
   }
 }
 
-// Fast path: the warp's 32 (n) x NV (m) block goes to shared memory as [m][n]
-// and leaves with one TMA store, which also clips at the M and N edges.
+// Fast path: the warp's 32 (n) x NV (m) block is transposed through shared
+// memory ([m][n], one warp-private buffer) and leaves as 16-byte stores, each
+// covering 8 (or 4) consecutive n of one output row. Needs a 16-byte aligned
+// base and row pitch; rows beyond M and 16-byte groups beyond N are skipped.
 template <typename OutT, bool kIntAcc, int NV>
-__device__ __forceinline__ void store_values_tma(const GemmParams& p, const CUtensorMap* tmap_c, const uint32_t* acc,
-                                                 int m0, int n, int n0_warp, uint8_t* stage_buf, int lane,
-                                                 bool plain) {
-  OutT* s = reinterpret_cast<OutT*>(stage_buf);
-  if (plain) {
+__device__ __forceinline__ void store_values_vec(const GemmParams& p, const uint32_t* acc, int m0, int n,
+                                                 int n0_warp, uint8_t* sbuf, int lane, bool plain) {
+  constexpr int ES = static_cast<int>(sizeof(OutT));
+  constexpr int RPP = (kStagingBytesPerWarp / (32 * ES)) < NV ? (kStagingBytesPerWarp / (32 * ES)) : NV;   // rows per pass
+  constexpr int VPR = 32 * ES / 16;          // 16-byte vectors per row: 4 (2-byte) or 8 (4-byte)
+  constexpr int RPI = 32 / VPR;              // rows covered by one warp-wide vector store
+  OutT* s = reinterpret_cast<OutT*>(sbuf);
+  OutT* c = reinterpret_cast<OutT*>(p.c);
 #pragma unroll
-    for (int j = 0; j < NV; ++j) {
-      if constexpr (kIntAcc && std::is_same<OutT, int>::value) s[j * 32 + lane] = static_cast<int>(acc[j]);
-      else if constexpr (kIntAcc) s[j * 32 + lane] = cast_out<OutT>(static_cast<float>(static_cast<int>(acc[j])));
-      else s[j * 32 + lane] = cast_out<OutT>(__uint_as_float(acc[j]));
-    }
-  } else {
-    const bool n_ok = n < p.N;
+  for (int pass = 0; pass < NV / RPP; ++pass) {
+    __syncwarp();   // previous pass's reads are done
+    if (plain) {
 #pragma unroll
-    for (int j = 0; j < NV; ++j) {
-      const int m = m0 + j;
-      if (n_ok && m < p.M) s[j * 32 + lane] = finish_value<OutT, kIntAcc>(p, acc[j], m, n);
+      for (int j = 0; j < RPP; ++j) {
+        const uint32_t raw = acc[pass * RPP + j];
+        if constexpr (kIntAcc && std::is_same<OutT, int>::value) s[j * 32 + lane] = static_cast<int>(raw);
+        else if constexpr (kIntAcc) s[j * 32 + lane] = cast_out<OutT>(static_cast<float>(static_cast<int>(raw)));
+        else s[j * 32 + lane] = cast_out<OutT>(__uint_as_float(raw));
+      }
+    } else {
+      const bool n_ok = n < p.N;
+#pragma unroll
+      for (int j = 0; j < RPP; ++j) {
+        const int m = m0 + pass * RPP + j;
+        if (n_ok && m < p.M) s[j * 32 + lane] = finish_value<OutT, kIntAcc>(p, acc[pass * RPP + j], m, n);
+      }
     }
-  }
-  fence_proxy_async_smem();
-  __syncwarp();
-  if (lane == 0) {
-    tma_store_2d(tmap_c, stage_buf, n0_warp, m0);
-    tma_store_commit();
+    __syncwarp();
+    const int vcol = lane % VPR;                       // which 16-byte group of the row
+    const int ncol = n0_warp + vcol * (16 / ES);
+#pragma unroll
+    for (int it = 0; it < RPP / RPI; ++it) {
+      const int r = it * RPI + lane / VPR;
+      const int m = m0 + pass * RPP + r;
+      if (m < p.M && ncol < p.N) {
+        const uint4 v = *reinterpret_cast<const uint4*>(sbuf + r * 32 * ES + vcol * 16);
+        *reinterpret_cast<uint4*>(c + static_cast<size_t>(m) * p.ldc + ncol) = v;
+      }
+    }
   }
 }
 
 template <int TN, int WF, int ACT>
 __global__ void __launch_bounds__(kThreads, 1)
-umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_c,
-                         const GemmParams p) {
+umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
   using Ring = RingConfig<TN, WF>;
   constexpr int NB = Ring::kNB;
   constexpr int NW = Ring::kNW;
   constexpr int WSS = Ring::kWStageSmem;
   constexpr int CPK = codes_per_kblock_bytes(WF);   // code bytes per k-block
-  constexpr int NI = issuers_for(TN);
+  constexpr int NI = Ring::kNI;
+  constexpr int NS = Ring::kSlots;       // dequantised TMEM ring slots
+  constexpr int kAccCols = Ring::kAccCols;
   constexpr bool kInt = (ACT == ACT_I8);
   constexpr bool kBf16 = (ACT == ACT_BF16);
   constexpr int BKE = kInt ? 128 : 64;   // K elements per k-block
   constexpr int NV = TN >= 32 ? 32 : 16; // accumulator columns per tcgen05.ld
-  static_assert(NI * TN <= kAccCols, "accumulators overlap the dequantised ring");
 
+#ifdef B200DQ_PROFILE
+  __shared__ long long prof_ts_b[kMaxSlots];   // issue time of the activation load in each stage
+#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_b = smem;                                   // NB x (TN x 128 B), 1024-aligned stages
@@ -278,7 +307,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   if (threadIdx.x == 0) {
     for (int i = 0; i < NW; ++i) { mbar_init(&ctl->full_w[i], 1); mbar_init(&ctl->empty_w[i], 4); }
     for (int i = 0; i < NB; ++i) mbar_init(&ctl->full_b[i], 1);
-    for (int i = 0; i < kASlots; ++i) { mbar_init(&ctl->a_full[i], 4); mbar_init(&ctl->cons[i], 1); }
+    for (int i = 0; i < NS; ++i) { mbar_init(&ctl->a_full[i], 4); mbar_init(&ctl->cons[i], 1); }
     mbar_init(&ctl->acc_full, NI);
     mbar_init(&ctl->acc_empty, 4);
     ctl->abort_flag = 0;
@@ -290,7 +319,6 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   }
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&tmap_a);
-    if (p.flags & GF_TMA_STORE) tma_prefetch_desc(&tmap_c);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -298,91 +326,162 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
   const uint32_t tmem_base = ctl->tmem_base;
 
   if (warp == 0) {
-    // ---------------- producer: weights run ahead by the depth of their ring,
-    // activations follow `kLag` stages behind in the same instruction stream ----
+    // ---------------- producer: two independent streams (weight stages and
+    // activation k-blocks) served by one thread; each is issued as soon as its
+    // ring has room, polled without blocking so neither delays the other ----
     if (lane == 0) {
-      constexpr int kLag = NW - NB / 2;
       SegmentWalk walk_w(p), walk_b(p);
       Segment sw_seg, sb_seg;
       bool have_w = walk_w.next(p, sw_seg), have_b = walk_b.next(p, sb_seg);
-      int st_w = have_w ? sw_seg.st_begin : 0, st_b = have_b ? sb_seg.st_begin : 0;
+      int st_w = have_w ? sw_seg.st_begin : 0, kb_b = have_b ? sb_seg.st_begin * 2 : 0;
       uint32_t wc = 0;   // weight stages issued
       uint32_t bc = 0;   // k-blocks of activations issued
+      uint64_t t_idle = 0;
+      uint32_t idle = 0;
+      PROF_DECL(pp_w); PROF_DECL(pp_b); PROF_DECL(pp_idle); PROF_DECL(pp_iters);
+      PROF_T0(tp);
       while (have_w || have_b) {
+        bool progressed = false;
+
         if (have_w) {
           const uint32_t s = wc % NW;
-          mbar_wait(&ctl->empty_w[s], ((wc / NW) & 1) ^ 1, abort_flag, st, 1);
-          mbar_arrive_expect_tx(&ctl->full_w[s], p.stage_bytes);
-          const uint8_t* src = p.wp + (static_cast<size_t>(sw_seg.n_tile) * p.st_total + st_w) * p.stage_bytes;
-          tma_bulk_g2s(smem_w + s * WSS, src, p.stage_bytes, &ctl->full_w[s]);
-          ++wc;
-          if (++st_w >= sw_seg.st_end) { have_w = walk_w.next(p, sw_seg); st_w = sw_seg.st_begin; }
-        }
-        if (have_b && (!have_w || wc >= static_cast<uint32_t>(kLag) + bc / 2 + 1)) {
-#pragma unroll
-          for (int h = 0; h < 2; ++h, ++bc) {
-            const uint32_t s = bc % NB;
-            if (bc >= static_cast<uint32_t>(NB)) {
-              const uint32_t prev = bc - NB;   // k-block that used this stage before
-              mbar_wait(&ctl->cons[prev % kASlots], (prev / kASlots) & 1, abort_flag, st, 2);
-            }
-            mbar_arrive_expect_tx(&ctl->full_b[s], Ring::kBStageBytes);
-            tma_load_2d(smem_b + s * Ring::kBStageBytes, &tmap_a, (st_b * 2 + h) * BKE, sb_seg.m_tile * TN,
-                        &ctl->full_b[s]);
+          if (mbar_test_wait(&ctl->empty_w[s], ((wc / NW) & 1) ^ 1)) {
+            mbar_arrive_expect_tx(&ctl->full_w[s], p.stage_bytes);
+            const uint8_t* src = p.wp + (static_cast<size_t>(sw_seg.n_tile) * p.st_total + st_w) * p.stage_bytes;
+            tma_bulk_g2s(smem_w + s * WSS, src, p.stage_bytes, &ctl->full_w[s]);
+            ++wc;
+            if (++st_w >= sw_seg.st_end) { have_w = walk_w.next(p, sw_seg); st_w = sw_seg.st_begin; }
+            progressed = true;
+            PROF_ADD(pp_iters, tp);
           }
-          if (++st_b >= sb_seg.st_end) { have_b = walk_b.next(p, sb_seg); st_b = sb_seg.st_begin; }
+        }
+        if (have_b) {
+          const uint32_t s = bc % NB;
+          bool room = bc < static_cast<uint32_t>(NB);
+          if (!room) {
+            const uint32_t prev = bc - NB;   // k-block that used this stage before
+            room = mbar_test_wait(&ctl->cons[prev % NS], (prev / NS) & 1);
+          }
+          PROF_ADD(pp_idle, tp);
+          if (room) {
+#ifdef B200DQ_PROFILE
+            prof_ts_b[s] = clock64();
+#endif
+            mbar_arrive_expect_tx(&ctl->full_b[s], Ring::kBStageBytes);
+            tma_load_2d(smem_b + s * Ring::kBStageBytes, &tmap_a, kb_b * BKE, sb_seg.m_tile * TN, &ctl->full_b[s]);
+            PROF_ADD(pp_w, tp);
+            ++bc;
+            if (++kb_b >= sb_seg.st_end * 2) { have_b = walk_b.next(p, sb_seg); kb_b = sb_seg.st_begin * 2; }
+            progressed = true;
+            PROF_ADD(pp_b, tp);
+          }
+        }
+
+        if (progressed) {
+          idle = 0;
+        } else if (((++idle) & 0x3f) == 0) {
+          // bounded: give up if nothing moved for the wait limit
+          if (*abort_flag) break;
+          const uint64_t now = globaltimer_ns();
+          if (idle == 0x40) t_idle = now;
+          else if (now - t_idle > B200DQ_WAIT_LIMIT_NS) { mbar_wait_failed(abort_flag, st, 1); break; }
         }
       }
+#ifdef B200DQ_PROFILE
+      if (p.prof) { unsigned long long* o = p.prof + blockIdx.x * 32 + 28; o[0] = pp_w; o[1] = pp_b; o[2] = pp_idle; o[3] = pp_iters; }
+#endif
     }
   } else if (warp >= 1 && warp <= 3) {
     // ---------------- MMA issuers ----------------
+    // The tensor pipe queues only a couple of MMAs, so the issuer must never be
+    // away from it for long: the barriers of its next k-block are checked between
+    // the second and third MMA of the current one, and ring positions are stepped
+    // without divisions.
     const int me = warp - 1;
     if (me < NI && lane == 0) {
       constexpr uint32_t idesc =
           kInt ? make_idesc(2u, 1u, 1u, 128u, TN) : make_idesc(1u, kBf16 ? 1u : 0u, kBf16 ? 1u : 0u, 128u, TN);
       const uint32_t acc_tmem = tmem_base + me * TN;
-      uint32_t kc = 0, tc = 0;
+      const uint32_t b_base = smem_u32(smem_b);
+      // ring state of this issuer's next k-block (global k-block counter kc = me, me+NI, ...)
+      uint32_t sa = me % NS, pa = 0;   // dequantised slot and its a_full parity
+      uint32_t sb = me % NB, pb = 0;   // activation stage and its full_b parity
+      uint32_t mine = me;              // global index of this issuer's next k-block
+      uint32_t kc_seg = 0;             // global index of the segment's first k-block
+      uint32_t tc = 0;
       bool ok = true;
       SegmentWalk walk(p);
       Segment w;
-      PROF_DECL(pm_acc); PROF_DECL(pm_a); PROF_DECL(pm_b); PROF_DECL(pm_issue); PROF_DECL(pm_commit);
+      PROF_DECL(pm_acc); PROF_DECL(pm_a); PROF_DECL(pm_b); PROF_DECL(pm_issue); PROF_DECL(pm_commit); PROF_DECL(pm_lat);
+#ifdef B200DQ_PROFILE
+      long long pm_latmin = 1ll << 40;
+#endif
       PROF_T0(tm);
       while (walk.next(p, w)) {
         ok &= mbar_wait(&ctl->acc_empty, (tc & 1) ^ 1, abort_flag, st, 3);
         tc_fence_after_sync();
         PROF_ADD(pm_acc, tm);
-        const int nkb = (w.st_end - w.st_begin) * 2;
+        const uint32_t kc_end = kc_seg + static_cast<uint32_t>(w.st_end - w.st_begin) * 2;
         bool fresh = true;
-        for (int i = 0; i < nkb; ++i, ++kc) {
-          if (NI > 1 && static_cast<int>(kc % NI) != me) continue;
-          const uint32_t sa = kc % kASlots;
-          const uint32_t sb = kc % NB;
-          ok &= mbar_wait(&ctl->a_full[sa], (kc / kASlots) & 1, abort_flag, st, 4);
-          PROF_ADD(pm_a, tm);
-          ok &= mbar_wait(&ctl->full_b[sb], (kc / NB) & 1, abort_flag, st, 5);
-          PROF_ADD(pm_b, tm);
-          tc_fence_after_sync();
+        bool ready = false;   // barriers of k-block `mine` already passed
+        while (mine < kc_end) {
+          if (!ready) {
+            ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
+            PROF_ADD(pm_a, tm);
+            ok &= mbar_wait(&ctl->full_b[sb], pb, abort_flag, st, 5);
+            PROF_ADD(pm_b, tm);
+            tc_fence_after_sync();
+          }
           const uint32_t a_tmem = tmem_base + kAccCols + sa * 32;
-          const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + sb * Ring::kBStageBytes));
+          const uint64_t b_desc = make_smem_desc_sw128(b_base + sb * Ring::kBStageBytes);
+          const uint32_t sa_cur = sa;
+          // advance ring state to this issuer's next k-block
+          mine += NI;
+          sa += NI; if (sa >= static_cast<uint32_t>(NS)) { sa -= NS; pa ^= 1; }
+          sb += NI; if (sb >= static_cast<uint32_t>(NB)) { sb -= NB; pb ^= 1; }
           if (ok) {
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint32_t accf = (!fresh || j > 0) ? 1u : 0u;
-              if constexpr (kInt) umma_ts_i8(acc_tmem, a_tmem + j * 8, b_desc + j * 2, idesc, accf);
-              else umma_ts_f16(acc_tmem, a_tmem + j * 8, b_desc + j * 2, idesc, accf);
+            if constexpr (kInt) {
+              umma_ts_i8(acc_tmem, a_tmem, b_desc, idesc, fresh ? 0u : 1u);
+              umma_ts_i8(acc_tmem, a_tmem + 8, b_desc + 2, idesc, 1u);
+            } else {
+              umma_ts_f16(acc_tmem, a_tmem, b_desc, idesc, fresh ? 0u : 1u);
+              umma_ts_f16(acc_tmem, a_tmem + 8, b_desc + 2, idesc, 1u);
+            }
+          }
+          ready = false;
+          if (mine < kc_end) {
+            PROF_ADD(pm_issue, tm);
+            ok &= mbar_wait(&ctl->full_b[sb], pb, abort_flag, st, 5);
+            PROF_ADD(pm_b, tm);
+#ifdef B200DQ_PROFILE
+            { const long long lat = clock64() - prof_ts_b[sb]; pm_lat += lat; if (lat < pm_latmin) pm_latmin = lat; }
+#endif
+            ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
+            PROF_ADD(pm_a, tm);
+            tc_fence_after_sync();
+            ready = true;
+          }
+          if (ok) {
+            if constexpr (kInt) {
+              umma_ts_i8(acc_tmem, a_tmem + 16, b_desc + 4, idesc, 1u);
+              umma_ts_i8(acc_tmem, a_tmem + 24, b_desc + 6, idesc, 1u);
+            } else {
+              umma_ts_f16(acc_tmem, a_tmem + 16, b_desc + 4, idesc, 1u);
+              umma_ts_f16(acc_tmem, a_tmem + 24, b_desc + 6, idesc, 1u);
             }
           }
           fresh = false;
           PROF_ADD(pm_issue, tm);
-          tc_commit(&ctl->cons[sa]);
+          tc_commit(&ctl->cons[sa_cur]);
           PROF_ADD(pm_commit, tm);
         }
         if (!fresh) tc_commit(&ctl->acc_full);
         else mbar_arrive(&ctl->acc_full);
+        kc_seg = kc_end;
         ++tc;
       }
 #ifdef B200DQ_PROFILE
-      if (p.prof && me == 0) { unsigned long long* o = p.prof + blockIdx.x * 32; o[0] = pm_acc; o[1] = pm_a; o[2] = pm_b; o[3] = pm_issue; o[4] = kc; o[5] = pm_commit; }
+      if (p.prof && me == 0) { unsigned long long* o = p.prof + blockIdx.x * 32; o[0] = pm_acc; o[1] = pm_a; o[2] = pm_b; o[3] = pm_issue; o[4] = kc_seg; o[5] = pm_commit; o[6] = pm_lat; o[7] = pm_latmin; }
 #endif
     }
   } else if (warp >= 4 && warp < 12) {
@@ -428,7 +527,13 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         for (int h = 0; h < 2; ++h) {
           const uint32_t szv = h == 0 ? sz0 : sz1;
           uint32_t regs[32];
+#ifdef B200DQ_EXP_NODECODE
+#pragma unroll
+          for (int q = 0; q < 32; ++q) regs[q] = c[h][q & 1].x + szv + q;
+          if (true) {} else if (false) {
+#else
           if constexpr (WF == WF_I4_I8) {
+#endif
 #pragma unroll
             for (int q = 0; q < 4; ++q)
               decode_i4_chunk(c[h][q], p.code_bias, *reinterpret_cast<uint32_t (*)[8]>(&regs[8 * q]));
@@ -453,16 +558,22 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             }
           }
           const uint32_t kc = sc * 2 + h;
-          const uint32_t sa = kc % kASlots;
+          const uint32_t sa = kc % NS;
           PROF_ADD(pd_dec, td);
-          if (kc >= static_cast<uint32_t>(kASlots)) {
-            const uint32_t prev = kc - kASlots;
-            ok &= mbar_wait(&ctl->cons[sa], (prev / kASlots) & 1, abort_flag, st, 7);
+          if (kc >= static_cast<uint32_t>(NS)) {
+            const uint32_t prev = kc - NS;
+#ifndef B200DQ_EXP_NO_CONS
+            ok &= mbar_wait(&ctl->cons[sa], (prev / NS) & 1, abort_flag, st, 7);
+#endif
           }
           PROF_ADD(pd_a, td);
           tc_fence_after_sync();
+#ifndef B200DQ_EXP_NOST
           tmem_st_32x32b_x32(tmem_base + lane_addr + kAccCols + sa * 32, regs);
           tc_wait_st();
+#else
+          if (regs[0] == 0x12345678u && regs[17] == 0x9abcdef0u) tmem_st_32x32b_x32(tmem_base + lane_addr + kAccCols + sa * 32, regs);
+#endif
           tc_fence_before_sync();
           __syncwarp();
           if (lane == 0) mbar_arrive(&ctl->a_full[sa]);
@@ -483,9 +594,9 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     uint8_t* my_stage = smem_o + quarter * kStagingBytesPerWarp;
-    const bool use_tma = (p.flags & GF_TMA_STORE) != 0;
+    const bool use_vec = (p.flags & GF_VEC_STORE) != 0;
     const bool plain = (p.flags & (GF_HAS_BIAS | GF_ROW_SCALE)) == 0;
-    uint32_t tc = 0, kc = 0, buf = 0;
+    uint32_t tc = 0, kc = 0;
     bool ok = true;
     SegmentWalk walk(p);
     Segment w;
@@ -534,19 +645,14 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
           uint32_t* dst = p.partial + (static_cast<size_t>(w.slot) * TN + c * NV) * kTileRows + row_in_tile;
 #pragma unroll
           for (int j = 0; j < NV; ++j) dst[j * kTileRows] = acc[j];
-        } else if (use_tma) {
+        } else if (use_vec) {
           if (m0 < p.M && n0_warp < p.N) {
-            uint8_t* sbuf = my_stage + buf * (kStagingBytesPerWarp / 2);
-            // the store that last read this buffer must have finished reading it
-            if (lane == 0) tma_store_wait_read<1>();
-            __syncwarp();
             switch (p.out_type) {
-              case OUT_F16: store_values_tma<__half, kInt, NV>(p, &tmap_c, acc, m0, n, n0_warp, sbuf, lane, plain); break;
-              case OUT_BF16: store_values_tma<__nv_bfloat16, kInt, NV>(p, &tmap_c, acc, m0, n, n0_warp, sbuf, lane, plain); break;
-              case OUT_F32: store_values_tma<float, kInt, NV>(p, &tmap_c, acc, m0, n, n0_warp, sbuf, lane, plain); break;
-              default: store_values_tma<int, kInt, NV>(p, &tmap_c, acc, m0, n, n0_warp, sbuf, lane, plain); break;
+              case OUT_F16: store_values_vec<__half, kInt, NV>(p, acc, m0, n, n0_warp, my_stage, lane, plain); break;
+              case OUT_BF16: store_values_vec<__nv_bfloat16, kInt, NV>(p, acc, m0, n, n0_warp, my_stage, lane, plain); break;
+              case OUT_F32: store_values_vec<float, kInt, NV>(p, acc, m0, n, n0_warp, my_stage, lane, plain); break;
+              default: store_values_vec<int, kInt, NV>(p, acc, m0, n, n0_warp, my_stage, lane, plain); break;
             }
-            buf ^= 1;
           }
         } else if (n < p.N) {
           switch (p.out_type) {
@@ -563,8 +669,6 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
       if (lane == 0) mbar_arrive(&ctl->acc_empty);
       ++tc;
     }
-    // shared memory must outlive the bulk stores that read it
-    if (lane == 0) tma_store_wait_read<0>();
 #ifdef B200DQ_PROFILE
     if (p.prof && lane == 0 && quarter == 0) { unsigned long long* o = p.prof + blockIdx.x * 32 + 24; o[0] = pe_wait; o[1] = pe_ld; o[2] = pe_store; o[3] = tc; }
 #endif
@@ -596,8 +700,8 @@ streamk_fixup_kernel(const GemmParams p) {
   const int c_first = static_cast<int>(t_begin / p.span);
   const int c_last = static_cast<int>((t_end - 1) / p.span);
   if (c_first == c_last) return;   // whole tile done by one CTA
-  const int m_tile = static_cast<int>(tile % p.m_tiles);
-  const int n_tile = static_cast<int>(tile / p.m_tiles);
+  const int n_tile = static_cast<int>(tile % p.n_tiles);
+  const int m_tile = static_cast<int>(tile / p.n_tiles);
   const int row = threadIdx.x;
   const int n = n_tile * kTileRows + row;
   if (n >= p.N) return;

@@ -1,0 +1,332 @@
+"""Kernel factories with the call surface of the reference's dequantize-GEMM examples.
+
+A factory takes problem sizes and dtypes and returns a kernel object that is
+called on torch CUDA tensors, exactly where a ``tilelang.jit``-compiled kernel is
+called in the reference (lazy mode of tilelang/jit/__init__.py:505-550, 574-638;
+call semantics of tilelang/jit/adapter/tvm_ffi.py:242-300: with ``out_idx`` the
+callee allocates the output with ``torch.empty`` on the first input's device and
+returns it, a wrong input count raises ``ValueError``; without ``out_idx`` the
+caller passes the output). Tunables of the reference (``block_M``, ``num_stages``,
+``threads``, ``split`` ...) are accepted and ignored: tile shapes are fixed by
+the hand-written kernel.
+
+Weights arrive in the reference's natural packed layout (two uint4 per byte along
+K, low nibble first: example_dequant_gemm_fine_grained.py:11-13,
+quantize/utils.py:50-67). The kernels stream a private pre-tiled image, so the
+first call with a given weight tensor repacks it on the device
+(``ops.pack_*``) and caches the image, keyed by the tensors' storage and version;
+``kernel.pack(...)`` does the same ahead of time.
+"""
+from __future__ import annotations
+
+from typing import Any, Optional, Sequence
+
+import torch
+
+from . import ops
+from .profiler import Profiler, TensorSupplyType
+
+_DTYPES = {
+    "float16": torch.float16, "half": torch.float16, "fp16": torch.float16,
+    "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+    "float32": torch.float32, "float": torch.float32, "fp32": torch.float32,
+    "int8": torch.int8, "uint8": torch.uint8, "int32": torch.int32,
+}
+
+
+def as_torch_dtype(dt: Any) -> torch.dtype:
+    """Accepts torch dtypes and the reference's dtype strings ("float16", T.bfloat16 ...)."""
+    if isinstance(dt, torch.dtype):
+        return dt
+    key = str(dt).replace("torch.", "")
+    if key in _DTYPES:
+        return _DTYPES[key]
+    raise ValueError(f"unsupported dtype {dt!r}")
+
+
+class Param:
+    """Shape/dtype of one kernel parameter (the reference's ``KernelParam``)."""
+
+    def __init__(self, name: str, shape: Sequence[int], dtype: torch.dtype):
+        self.name, self.shape, self.dtype = name, tuple(shape), dtype
+
+    def __repr__(self) -> str:
+        return f"Param({self.name}, {self.shape}, {self.dtype})"
+
+
+class DequantKernel:
+    """A callable on torch tensors, standing where the reference's ``JITKernel`` stands
+    (tilelang/jit/kernel.py:40-211, 494-521)."""
+
+    def __init__(self, name: str, params: list[Param], out_idx: Optional[list[int]], impl, pack_fn=None,
+                 description: str = ""):
+        self.name = name
+        self.params = params
+        self.out_idx = out_idx
+        self._impl = impl
+        self._pack_fn = pack_fn
+        self._description = description
+        self._cache: dict = {}
+
+    # -- reference surface ---------------------------------------------------
+    def __call__(self, *inputs):
+        n_out = len(self.out_idx) if self.out_idx else 0
+        expected = len(self.params) - n_out
+        if len(inputs) != expected:
+            raise ValueError(f"Expected {expected} inputs, got {len(inputs)} with {len(self.params)} params "
+                             f"and out_idx={self.out_idx}")
+        return self._impl(self, *inputs)
+
+    def get_profiler(self, tensor_supply_type: TensorSupplyType = TensorSupplyType.Auto) -> Profiler:
+        return Profiler(self, tensor_supply_type)
+
+    def get_kernel_source(self) -> str:
+        return self._description
+
+    # -- library extras ------------------------------------------------------
+    def pack(self, *weight_tensors) -> ops.PackedWeight:
+        """Repack the weight tensors into the device layout now (otherwise done on first call)."""
+        return self._packed(*weight_tensors)
+
+    def _packed(self, *tensors) -> ops.PackedWeight:
+        key = tuple((t.data_ptr(), t._version, tuple(t.shape)) if t is not None else None for t in tensors)
+        hit = self._cache.get(key)
+        if hit is None:
+            hit = self._pack_fn(*tensors)
+            if len(self._cache) >= 64:
+                self._cache.clear()
+            self._cache[key] = hit
+        return hit
+
+
+def _input_params(out_idx, params):
+    return params
+
+
+# ---------------------------------------------------------------------------
+# W4A16 / MXFP4: matmul(M, N, K, in_dtype, out_dtype, accum_dtype, num_bits, group_size, ...)
+# ---------------------------------------------------------------------------
+
+def matmul(M: int, N: int, K: int, in_dtype, out_dtype, accum_dtype, num_bits: int = 4,
+           group_size: Optional[int] = None, with_scaling: Optional[bool] = None, with_zeros: bool = False,
+           zeros_mode: str = "original", source_format: Any = "uint", scale_size: int = 32,
+           fast_dequant: bool = True, with_bias: bool = False, fp4_format: str = "e2m1",
+           scale_exp_bias: int = 127, storage_dtype: Any = "uint8", trans_c: bool = False,
+           block_M=None, block_N=None, block_K=None, num_stages=None, threads=None, split=1,
+           **ignored) -> DequantKernel:
+    """Dequantize-GEMM factory: ``C[M,N] = A[M,K] @ dequant(qB[N,K*num_bits/8])^T``.
+
+    Covers the reference's
+    * ``matmul`` of example_dequant_gemm_fine_grained.py:16-30 (no scale: call
+      without ``group_size``; inputs ``(A, qB)``),
+    * the grouped W4A16 rule of quantize/lop3.py:684-689 (``group_size`` given;
+      inputs ``(A, qB, Scale[, Zeros][, Bias])``, scales/zeros of shape (N, K/group)),
+    * ``matmul`` of example_dequant_gemm_bf16_mxfp4_hopper.py:83-104
+      (``source_format`` "fp4"/"e2m1"/"uint32" with ``scale_size`` 32; inputs
+      ``(A, qB, Scale[, Bias])``, Scale (N, K/32) uint8).
+
+    ``fp4_format``: "e2m1" true e2m1 codes in natural nibble order (default);
+    ``scale_exp_bias``: 127 for OCP e8m0 bytes, 0 for the raw ``2**Scale`` of the
+    reference's hopper example. Only ``zeros_mode="original"`` ((q - z) * s) exists.
+    """
+    in_t, out_t, acc_t = as_torch_dtype(in_dtype), as_torch_dtype(out_dtype), as_torch_dtype(accum_dtype)
+    if num_bits != 4:
+        raise ValueError("matmul: only num_bits=4 weights are supported on the 16-bit activation path")
+    if in_t not in (torch.float16, torch.bfloat16):
+        raise ValueError("matmul: in_dtype must be float16 or bfloat16 (int8 activations: matmul_int8xint4)")
+    if acc_t != torch.float32:
+        raise ValueError("matmul: accumulation is float32 (tcgen05 kind::f16 accumulates in fp32)")
+    if zeros_mode != "original":
+        raise ValueError("matmul: only zeros_mode='original' ((q - z) * s) is implemented")
+    is_fp4 = str(source_format).lower() in ("fp4", "e2m1", "mxfp4", "uint32", "fp")
+    if with_scaling is None:
+        with_scaling = bool(group_size) or is_fp4
+    qk = K * num_bits // 8
+
+    params = [Param("A", (M, K), in_t), Param("B", (N, qk), torch.uint8)]
+    if is_fp4:
+        if in_t != torch.bfloat16:
+            raise ValueError("matmul: e2m1 weights need bfloat16 activations")
+        if fp4_format != "e2m1":
+            raise ValueError("matmul: the device decoder takes natural-order true e2m1 codes; convert other "
+                             "layouts with tilelang_b200.quantize first")
+        params.append(Param("Scale", (N, K // scale_size), torch.uint8))
+        if scale_size != 32:
+            raise ValueError("matmul: MXFP4 uses one exponent byte per 32 K elements")
+    elif with_scaling:
+        g = K if group_size in (None, -1, 0) else group_size
+        params.append(Param("Scale", (N, K // g), in_t))
+        if with_zeros:
+            params.append(Param("Zeros", (N, K // g), in_t))
+    if with_bias:
+        params.append(Param("Bias", (M, N), out_t))
+    params.append(Param("C", (N, M) if trans_c else (M, N), out_t))
+
+    def pack_fn(qB, scale=None, zeros=None):
+        if is_fp4:
+            return ops.pack_mxfp4(qB.view(torch.uint8), scale, N, K, exp_bias=scale_exp_bias)
+        if with_scaling:
+            g = K if group_size in (None, -1, 0) else group_size
+            return ops.pack_w4a16(qB.view(torch.uint8), scale, zeros, N, K, g, in_t)
+        return ops.pack_w4a16(qB.view(torch.uint8), None, None, N, K, 0, in_t)
+
+    def impl(kernel: DequantKernel, A, qB, *rest):
+        rest = list(rest)
+        scale = rest.pop(0) if (is_fp4 or with_scaling) else None
+        zeros = rest.pop(0) if (with_scaling and with_zeros and not is_fp4) else None
+        bias = rest.pop(0) if with_bias else None
+        _check(A, params[0])
+        _check(qB, params[1], any_int8=True)
+        pw = kernel._packed(qB, scale, zeros)
+        return ops.gemm(A, pw, out_dtype=out_t, bias=bias, trans_c=trans_c)
+
+    desc = (f"b200dq umma_dequant_gemm: M={M} N={N} K={K} in={in_t} out={out_t} "
+            f"{'mxfp4' if is_fp4 else 'w4a16'} group={group_size} zeros={with_zeros} bias={with_bias}")
+    return DequantKernel("matmul", params, [-1], impl, pack_fn, desc)
+
+
+def _check(t: torch.Tensor, p: Param, any_int8: bool = False) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{p.name}: expected a torch.Tensor")
+    if tuple(t.shape) != p.shape:
+        raise ValueError(f"{p.name}: expected shape {p.shape}, got {tuple(t.shape)}")
+    ok = t.dtype == p.dtype or (any_int8 and t.dtype in (torch.int8, torch.uint8))
+    if not ok:
+        raise TypeError(f"{p.name}: expected dtype {p.dtype}, got {t.dtype}")
+
+
+# ---------------------------------------------------------------------------
+# small-M entry point of the reference: dequantize_gemv
+# ---------------------------------------------------------------------------
+
+def dequantize_gemv(M: int, N: int, K: int, in_dtype, out_dtype, accum_dtype, num_bits: int = 4,
+                    storage_dtype: Any = "int8", source_format: str = "uint", n_partition: int = 4,
+                    reduce_thread: int = 32, fast_decoding: bool = False, trans_A: bool = False,
+                    trans_B: bool = True, group_size: int = -1, with_scaling: bool = False) -> DequantKernel:
+    """``kernel(A, qB, C)`` with the caller's preallocated C, as in
+    example_dequant_gemv_fp16xint4.py:11-29, 199-205. The reference kernel ignores
+    ``group_size``/``with_scaling`` (its body never reads a Scale tensor, :77-155)
+    and so does this one: C = A @ q^T with the raw unsigned codes.
+
+    ``fast_decoding=True`` means the caller passes weights already permuted by the
+    reference's ``interleave_weight``; they are un-permuted on the device view
+    (``tilelang_b200.quantize.deinterleave_weight``) before packing.
+    """
+    if trans_A or not trans_B:
+        raise ValueError("dequantize_gemv: only trans_A=False, trans_B=True (as in the reference)")
+    in_t, out_t = as_torch_dtype(in_dtype), as_torch_dtype(out_dtype)
+    if source_format != "uint" or num_bits != 4:
+        raise ValueError("dequantize_gemv: uint4 weights only")
+    params = [Param("A", (M, K), in_t), Param("B", (N, K // 2), torch.int8), Param("C", (M, N), out_t)]
+
+    def pack_fn(qB):
+        q = qB
+        if fast_decoding:
+            from .quantize import deinterleave_weight
+            q = deinterleave_weight(qB, 4, "float16")
+        return ops.pack_w4a16(q.view(torch.uint8), None, None, N, K, 0, in_t)
+
+    def impl(kernel: DequantKernel, A, qB, C):
+        _check(A, params[0])
+        _check(qB, params[1], any_int8=True)
+        _check(C, params[2])
+        ops.gemm(A, kernel._packed(qB), out=C)
+        return None
+
+    return DequantKernel("dequantize_gemv", params, None, impl, pack_fn,
+                         f"b200dq umma_dequant_gemm (small-M tiles): M={M} N={N} K={K} in={in_t}")
+
+
+# ---------------------------------------------------------------------------
+# W4A8: int8 activations x int4 weights -> int32, transposed output
+# ---------------------------------------------------------------------------
+
+def matmul_int8xint4(M: int, N: int, K: int, in_dtype="int8", out_dtype="int32", accum_dtype="int32",
+                     num_bits: int = 4, block_M=None, block_N=None, block_K=None, num_stages=None, threads=None,
+                     **ignored) -> DequantKernel:
+    """``Ct[N, M] int32 = sext4(B) @ A^T`` (example_dequant_gemm_w4a8.py:85-149; decode rule :10-21)."""
+    if as_torch_dtype(in_dtype) != torch.int8 or as_torch_dtype(out_dtype) != torch.int32 or num_bits != 4:
+        raise ValueError("matmul_int8xint4: int8 activations, 4-bit weights, int32 output")
+    params = [Param("A", (M, K), torch.int8), Param("B", (N, K // 2), torch.uint8), Param("Ct", (N, M), torch.int32)]
+
+    def pack_fn(qB):
+        # two's-complement nibbles -> offset-8 codes: code = (w + 8) & 15 = nibble ^ 8
+        q = qB.view(torch.uint8) ^ 0x88
+        return ops.pack_int4_for_int8(q, N, K, code_offset=8)
+
+    def impl(kernel: DequantKernel, A, qB):
+        _check(A, params[0])
+        _check(qB, params[1], any_int8=True)
+        return ops.gemm(A, kernel._packed(qB), out_dtype=torch.int32, trans_c=True)
+
+    return DequantKernel("matmul_int8xint4", params, [2], impl, pack_fn, f"b200dq kind::i8 W4A8: M={M} N={N} K={K}")
+
+
+# ---------------------------------------------------------------------------
+# BitNet b1.58: int8 activations x 2-bit weights -> int32
+# ---------------------------------------------------------------------------
+
+def _bitnet_factory(name: str, M: int, N: int, K: int, in_dtype, out_dtype, accum_dtype, fast_decoding: bool,
+                    code_offset: int) -> DequantKernel:
+    in_t, out_t = as_torch_dtype(in_dtype), as_torch_dtype(out_dtype)
+    if in_t != torch.int8:
+        raise ValueError(f"{name}: int8 activations only (the reference's float16 variant is not part of this path)")
+    if out_t not in (torch.int32, torch.float32, torch.float16, torch.bfloat16):
+        raise ValueError(f"{name}: unsupported output dtype {out_t}")
+    params = [Param("A", (M, K), torch.int8), Param("B", (N, K // 4), torch.int8), Param("C", (M, N), out_t)]
+
+    def pack_fn(qB):
+        q = qB
+        if fast_decoding:
+            from .quantize import deinterleave_weight
+            q = deinterleave_weight(qB, 2, "int8")
+        return ops.pack_int2(q.view(torch.uint8), N, K, code_offset=code_offset)
+
+    def impl(kernel: DequantKernel, A, qB, C):
+        _check(A, params[0])
+        _check(qB, params[1], any_int8=True)
+        _check(C, params[2])
+        ops.gemm(A, kernel._packed(qB), out=C)
+        return None
+
+    return DequantKernel(name, params, None, impl, pack_fn, f"b200dq kind::i8 int8xint2: M={M} N={N} K={K}")
+
+
+def bitnet_158_int8xint2_decode(M: int, N: int, K: int, in_dtype="int8", out_dtype="int32", accum_dtype="int32",
+                                fast_decoding: bool = True, n_partition: int = 4, reduce_thread: int = 32,
+                                code_offset: int = 0) -> DequantKernel:
+    """``kernel(A, qW, C)``: C int32 = A @ W^T with 2-bit codes, four per byte.
+    examples/bitnet-1.58b/kernel_benchmark/tilelang_bitnet_158_int8xint2_decode.py:66-175;
+    with ``fast_decoding`` the weights come through the reference's
+    ``general_compress`` + ``interleave_weight(qw, 2, "int8")`` (:178-236, 248-250).
+    The reference decodes unsigned codes (:139-144): ``code_offset=0``; the ternary
+    mapping code = w + 2 uses ``code_offset=2`` (its ``decode_i2s_to_i8s``, :16-39)."""
+    return _bitnet_factory("bitnet_158_int8xint2_decode", M, N, K, in_dtype, out_dtype, accum_dtype, fast_decoding,
+                           code_offset)
+
+
+def bitnet_158_int8xint2_prefill(M: int, N: int, K: int, in_dtype="int8", out_dtype="int32", accum_dtype="int32",
+                                 fast_decoding: bool = True, block_row_warps=2, block_col_warps=2,
+                                 warp_row_tiles=32, warp_col_tiles=32, chunk=64, code_offset: int = 0) -> DequantKernel:
+    """Same contract for large M
+    (examples/bitnet-1.58b/kernel_benchmark/tilelang_bitnet_158_int8xint2_prefill.py:72-298)."""
+    return _bitnet_factory("bitnet_158_int8xint2_prefill", M, N, K, in_dtype, out_dtype, accum_dtype, fast_decoding,
+                           code_offset)
+
+
+class BitLinear:
+    """The BitNet linear layer's inference forward on top of the int8 x int2 kernel:
+    per-token absmax int8 quantisation of the activations, ternary GEMM, then
+    ``out / s_act / s_w`` (examples/bitnet-1.58b/utils_quant.py:156-170, 199-209).
+    Weights are ternary codes w + 2 in 2 bits."""
+
+    def __init__(self, W_t: torch.Tensor, s_w: float, out_dtype: torch.dtype = torch.bfloat16):
+        from .quantize import compress_codes
+        N, K = W_t.shape
+        self.N, self.K, self.s_w, self.out_dtype = N, K, float(s_w), out_dtype
+        codes = compress_codes((W_t.to(torch.int16) + 2).to(torch.uint8), 2)
+        self.weight = ops.pack_int2(codes, N, K, code_offset=2)
+
+    def forward_quantized(self, A_q: torch.Tensor, s_act: torch.Tensor) -> torch.Tensor:
+        return ops.gemm(A_q, self.weight, out_dtype=self.out_dtype, row_scale=s_act.reshape(-1).float().contiguous(),
+                        tensor_scale=self.s_w)
