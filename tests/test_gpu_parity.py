@@ -1,0 +1,280 @@
+"""GPU parity: every kernel family through the public factories / C ABI against the
+CPU oracle on the same seeded inputs. Integer paths must be bit-exact; 16-bit
+float outputs follow the reference's rule (rtol = atol = 1e-2, at most 1 % of the
+elements outside: tilelang/profiler/__init__.py:104-111) and the stricter bound
+max |x - ref| / max(|ref|, rms(ref)) <= 1e-2."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import tilelang_b200 as tb
+from tilelang_b200 import ops, quantize
+from oracle import ref_programs as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+RTOL = ATOL = 1e-2          # tolerance stated by the path's north star for fp16/bf16 outputs
+MAX_MISMATCH = 0.01
+
+
+def gen(seed):
+    g = torch.Generator()
+    g.manual_seed(seed)
+    return g
+
+
+def w4_inputs(M, N, K, group, dtype, zeros, seed=0):
+    """Seeded synthetic inputs with the value laws of the benchmark configs: A ~ N(0,1),
+    q ~ U{0..15}, s ~ U[0.005, 0.02], z ~ U[6, 10] (or the fixed zero-point 8)."""
+    A = torch.randn(M, K, generator=gen(seed)).to(dtype)
+    q = torch.randint(0, 16, (N, K), generator=gen(seed + 1), dtype=torch.uint8)
+    qB = torch.from_numpy(R.general_compress(q.numpy(), 4))
+    s = (torch.rand(N, K // group, generator=gen(seed + 2)) * 0.015 + 0.005).to(dtype)
+    z = (torch.rand(N, K // group, generator=gen(seed + 3)) * 4 + 6).to(dtype) if zeros else None
+    return A, qB, s, z
+
+
+def check_float(out, ref, strict=1e-2):
+    """`strict` bounds max |x - ref| / max(|ref|, rms(ref)). It is 1e-2 for fp16/bf16
+    outputs. fp32 outputs of weights with real-valued zero-points get 2e-2: about
+    0.5 % of those weights are one bf16 ulp away from the oracle's (q - z needs 9
+    significant bits when |q - z| >= 8 and bf16 holds 8), all q = 15 entries of an
+    affected group at once, which an unrounded output exposes."""
+    out, ref = out.float().cpu(), ref.float().cpu()
+    assert R.mismatch_ratio(out, ref, RTOL, ATOL) <= MAX_MISMATCH
+    assert R.max_rel_error(out, ref) <= strict
+    assert torch.isfinite(out).all()
+
+
+# ------------------------------- W4A16 ---------------------------------------
+
+@pytest.mark.parametrize("M,N,K,group,dtype,zeros", [
+    (16, 1024, 1024, 128, torch.float16, False),     # benchmark config 1 (fixed zero-point 8)
+    (1, 1024, 1024, 128, torch.float16, False),
+    (16, 1024, 1024, 128, torch.bfloat16, True),
+    (33, 384, 512, 64, torch.bfloat16, True),        # group 64, ragged M
+    (128, 512, 1024, 128, torch.bfloat16, True),
+    (300, 640, 2048, 128, torch.bfloat16, True),     # M tail on a 256-token tile, N multiple of 128
+    (77, 200, 512, 128, torch.bfloat16, True),       # N tail inside a 128-row tile
+    (64, 256, 1408, 128, torch.bfloat16, False),     # K = 11 groups: K padded to a whole stage
+    (40, 320, 256, 256, torch.float16, True),        # one group per row (group == K)
+])
+def test_w4a16_grouped(M, N, K, group, dtype, zeros):
+    A, qB, s, z = w4_inputs(M, N, K, group, dtype, zeros)
+    kernel = tb.matmul(M, N, K, dtype, dtype, "float32", num_bits=4, group_size=group, with_zeros=zeros)
+    args = [A.to(DEV), qB.to(DEV), s.to(DEV)] + ([z.to(DEV)] if zeros else [])
+    C = kernel(*args)
+    torch.cuda.synchronize()
+    tb.check_status()
+    assert C.shape == (M, N) and C.dtype == dtype
+    check_float(C, R.ref_w4a16(A, qB, s, z, group, dtype))
+
+
+def test_w4a16_dequant_is_bit_exact_for_fixed_zero_point():
+    """With z = 8 the device dequantisation is RN((q - 8) * s), the oracle's value, so a
+    one-hot activation row reads the dequantised weights back bit for bit."""
+    N, K, group = 256, 256, 128
+    for dtype in (torch.float16, torch.bfloat16):
+        _, qB, s, _ = w4_inputs(1, N, K, group, dtype, False, seed=5)
+        A = torch.eye(K, dtype=dtype)[:64]                      # rows e_0 .. e_63
+        kernel = tb.matmul(64, N, K, dtype, dtype, "float32", group_size=group)
+        C = kernel(A.to(DEV), qB.to(DEV), s.to(DEV)).cpu()
+        W = R.dequant_w4_group(qB, s, None, group, dtype)       # (N, K)
+        assert torch.equal(C, W[:, :64].T.contiguous())
+
+
+def test_w4a16_no_scale_matches_fine_grained_reference():
+    # example_dequant_gemm_fine_grained.py:125-131: C = A @ unpack(qB)^T
+    M, N, K = 64, 256, 512
+    A = torch.randn(M, K, generator=gen(1)).to(torch.float16)
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(2), dtype=torch.uint8)
+    kernel = tb.matmul(M, N, K, "float16", "float16", "float32", num_bits=4)
+    C = kernel(A.to(DEV), qB.view(torch.int8).to(DEV))
+    check_float(C, R.ref_w4a16_noscale(A, qB, torch.float16))
+
+
+def test_w4a16_reference_profiler_flow():
+    """The reference's own check: Integer supply (unsigned in {0,1,2}) + assert_allclose."""
+    M, N, K = 32, 256, 256
+    kernel = tb.matmul(M, N, K, "float16", "float16", "float32", num_bits=4)
+    prof = kernel.get_profiler(tb.TensorSupplyType.Integer)
+    out = prof.run_once()
+    assert out is not None
+
+    def ref_program(A, qB):
+        return R.ref_w4a16_noscale(A.cpu(), qB.cpu().view(torch.uint8), torch.float16)
+
+    prof.assert_allclose(ref_program, rtol=1e-2, atol=1e-2)
+    prof.assert_consistent(repeat=3)
+
+
+def test_w4a16_bias_fp32_out_and_transposed_out():
+    M, N, K, group = 48, 256, 256, 128
+    A, qB, s, z = w4_inputs(M, N, K, group, torch.bfloat16, True, seed=9)
+    ref = R.ref_w4a16(A, qB, s, z, group, torch.float32)
+    pw = ops.pack_w4a16(qB.to(DEV), s.to(DEV), z.to(DEV), N, K, group, torch.bfloat16)
+    out32 = ops.gemm(A.to(DEV), pw, out_dtype=torch.float32)
+    check_float(out32, ref, strict=2e-2)
+    outT = ops.gemm(A.to(DEV), pw, trans_c=True)
+    assert outT.shape == (N, M)
+    check_float(outT.T, ref)
+    bias = torch.randn(M, N, generator=gen(4)).to(torch.bfloat16)
+    outb = ops.gemm(A.to(DEV), pw, bias=bias.to(DEV))
+    check_float(outb, ref + bias.float())
+
+
+def test_w4a16_stream_k_split_is_deterministic_and_matches_unsplit():
+    """A grid that cuts tiles between CTAs (scratch partial tiles + fix-up pass) gives
+    the same result as one CTA per whole tile, up to fp32 summation order."""
+    M, N, K, group = 40, 384, 2048, 128
+    A, qB, s, z = w4_inputs(M, N, K, group, torch.bfloat16, True, seed=11)
+    pw = ops.pack_w4a16(qB.to(DEV), s.to(DEV), z.to(DEV), N, K, group, torch.bfloat16)
+    whole = ops.gemm(A.to(DEV), pw, max_ctas=3, out_dtype=torch.float32)        # 3 tiles, 3 CTAs: no split
+    split = ops.gemm(A.to(DEV), pw, max_ctas=7, out_dtype=torch.float32)        # spans cut tiles
+    again = ops.gemm(A.to(DEV), pw, max_ctas=7, out_dtype=torch.float32)
+    assert torch.equal(split, again)
+    assert torch.allclose(split, whole, rtol=1e-5, atol=1e-4)
+    check_float(split, R.ref_w4a16(A, qB, s, z, group, torch.float32), strict=2e-2)
+
+
+def test_w4a16_linearity_at_full_width():
+    """Size-independent property at the benchmark's full N and K: f(a + b) = f(a) + f(b)
+    for activations whose sums are exact in bf16 (small integers)."""
+    N, K, group = 28672, 8192, 128
+    g = gen(21)
+    q = torch.randint(0, 256, (N, K // 2), generator=g, dtype=torch.uint8).to(DEV)
+    s = (torch.rand(N, K // group, generator=g) * 0.015 + 0.005).to(torch.bfloat16).to(DEV)
+    z = (torch.rand(N, K // group, generator=g) * 4 + 6).to(torch.bfloat16).to(DEV)
+    pw = ops.pack_w4a16(q, s, z, N, K, group, torch.bfloat16)
+    a = torch.randint(-2, 3, (16, K), generator=g).to(torch.bfloat16).to(DEV)
+    b = torch.randint(-2, 3, (16, K), generator=g).to(torch.bfloat16).to(DEV)
+    fa = ops.gemm(a, pw, out_dtype=torch.float32)
+    fb = ops.gemm(b, pw, out_dtype=torch.float32)
+    fab = ops.gemm(a + b, pw, out_dtype=torch.float32)
+    torch.cuda.synchronize()
+    tb.check_status()
+    scale = fab.abs().max().item()
+    assert (fab - (fa + fb)).abs().max().item() <= 1e-4 * scale
+    # one output row against the oracle, all 28672 columns
+    ref = R.ref_w4a16(a[:1].cpu(), q.cpu(), s.cpu(), z.cpu(), group, torch.float32)
+    check_float(fa[:1], ref, strict=2e-2)
+
+
+# ------------------------------- small-M entry point ------------------------------------
+
+def test_dequantize_gemv_reference_flow():
+    # example_dequant_gemv_fp16xint4.py:158-217: weights pre-permuted by interleave_weight
+    M, N, K = 1, 1024, 1024
+    A = torch.rand(M, K, generator=gen(3)).to(torch.float16)
+    qB = torch.randint(0, 127, (N, K // 2), generator=gen(4), dtype=torch.int8)
+    kernel = tb.dequantize_gemv(M, N, K, "float16", "float16", "float16", 4, "int8", "uint", 4, 32, True)
+    C = torch.zeros(M, N, dtype=torch.float16, device=DEV)
+    qB_fast = quantize.interleave_weight(qB, 4, "float16")
+    assert kernel(A.to(DEV), qB_fast.to(DEV), C) is None
+    check_float(C, R.ref_w4a16_noscale(A, qB.view(torch.uint8), torch.float16))
+
+
+# ------------------------------- MXFP4 ---------------------------------------
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 256), (32, 384, 512), (200, 256, 1024)])
+def test_mxfp4_e8m0(M, N, K):
+    A = torch.randn(M, K, generator=gen(1)).to(torch.bfloat16)
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(2), dtype=torch.uint8)       # all 16 codes
+    e = torch.randint(-8, 1, (N, K // 32), generator=gen(3))
+    scale = (e + 127).to(torch.uint8)
+    kernel = tb.matmul(M, N, K, "bfloat16", "bfloat16", "float32", source_format="fp4", num_bits=4, scale_size=32)
+    C = kernel(A.to(DEV), qB.to(DEV), scale.to(DEV))
+    check_float(C, R.ref_mxfp4(A, qB, scale, None, exp_bias=127, fmt="e2m1"))
+
+
+def test_mxfp4_dequant_bit_exact_and_all_codes():
+    N, K = 128, 256
+    qB = torch.arange(256, dtype=torch.uint8).repeat(N * K // 2 // 256).reshape(N, K // 2)
+    scale = torch.randint(119, 128, (N, K // 32), generator=gen(5)).to(torch.uint8)
+    A = torch.eye(K, dtype=torch.bfloat16)[:128]
+    kernel = tb.matmul(128, N, K, "bfloat16", "bfloat16", "float32", source_format="fp4")
+    C = kernel(A.to(DEV), qB.to(DEV), scale.to(DEV)).cpu()
+    W = R.dequant_mxfp4(qB, scale, 127, "e2m1")
+    assert torch.equal(C, W[:, :128].T.contiguous())
+
+
+def test_mxfp4_reference_twiddled_bytes_with_raw_exponent_and_bias():
+    """Byte-level drop-in for the reference's fast_dequant=True inputs: twiddled codes
+    and 2**Scale with no bias (example_dequant_gemm_bf16_mxfp4_hopper.py:381-423)."""
+    M, N, K = 64, 256, 256
+    A = (torch.rand(M, K, generator=gen(1)) * 2 - 1).to(torch.bfloat16)
+    qB_tw = torch.randint(0, 256, (N, K // 2), generator=gen(2), dtype=torch.uint8)
+    scale = torch.randint(0, 3, (N, K // 32), generator=gen(3)).to(torch.uint8)
+    bias = (torch.rand(M, N, generator=gen(4)) * 2 - 1).to(torch.bfloat16)
+    kernel = tb.matmul(M, N, K, "bfloat16", "bfloat16", "float32", source_format="fp4", with_bias=True,
+                       scale_exp_bias=0)
+    C = kernel(A.to(DEV), quantize.untwiddle_fp4(qB_tw).to(DEV), scale.to(DEV), bias.to(DEV))
+    check_float(C, R.ref_mxfp4(A, qB_tw, scale, bias, exp_bias=0, fmt="twiddled"))
+
+
+# ------------------------------- integer paths (bit-exact) -------------------
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 256), (64, 384, 640), (128, 256, 256), (300, 200, 1152)])
+def test_w4a8_bit_exact(M, N, K):
+    A = torch.randint(-128, 128, (M, K), generator=gen(1), dtype=torch.int8)
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(2), dtype=torch.uint8)
+    kernel = tb.matmul_int8xint4(M, N, K, "int8", "int32", "int32")
+    Ct = kernel(A.to(DEV), qB.to(DEV))
+    assert Ct.shape == (N, M) and Ct.dtype == torch.int32
+    assert torch.equal(Ct.cpu(), R.ref_w4a8(A, qB))
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 256), (64, 3200, 3200), (37, 8640, 3200), (200, 3200, 8640)])
+def test_bitnet_int8xint2_bit_exact(M, N, K):
+    """Ternary weights P(-1,0,1) = (.25,.5,.25), 2-bit code = w + 2; int8 activations from
+    per-token absmax quantisation; int32 result must be exact, then acc / s_act / s_w."""
+    W = torch.multinomial(torch.tensor([0.25, 0.5, 0.25]), N * K, replacement=True, generator=gen(1)).reshape(N, K) - 1
+    x = torch.randn(M, K, generator=gen(2)).to(torch.bfloat16)
+    A_q, s_act = R.bitnet_activation_quant(x)
+    s_w = 37.5
+    codes = quantize.compress_codes((W + 2).to(torch.uint8), 2)
+    kernel = tb.bitnet_158_int8xint2_prefill(M, N, K, "int8", "int32", "int32", fast_decoding=False, code_offset=2)
+    C = torch.zeros(M, N, dtype=torch.int32, device=DEV)
+    kernel(A_q.to(DEV), codes.view(torch.int8).to(DEV), C)
+    ref32 = R.ref_bitnet_int32(A_q, W.to(torch.int8))
+    assert torch.equal(C.cpu(), ref32)
+    layer = tb.BitLinear(W.to(torch.int8).to(DEV), s_w, out_dtype=torch.bfloat16)
+    out = layer.forward_quantized(A_q.to(DEV), s_act.to(DEV))
+    assert torch.equal(out.cpu(), R.ref_bitnet_linear(A_q, s_act, W.to(torch.int8), s_w, torch.bfloat16))
+
+
+def test_bitnet_decode_reference_flow():
+    # tilelang_bitnet_158_int8xint2_decode.py:238-258: A in [0,4), W in {0,1}, unsigned codes,
+    # general_compress + interleave_weight(qw, 2, "int8")
+    M, N, K = 1, 256, 256
+    A = torch.randint(0, 4, (M, K), generator=gen(1), dtype=torch.int8)
+    B = torch.randint(0, 2, (N, K), generator=gen(2), dtype=torch.int8)
+    qw = R.interleave_weight(R.general_compress(B.numpy(), 2).view(np.int8), 2, "int8")
+    kernel = tb.bitnet_158_int8xint2_decode(M, N, K, "int8", "int32", "int32", fast_decoding=True)
+    C = torch.zeros(M, N, dtype=torch.int32, device=DEV)
+    kernel(A.to(DEV), torch.from_numpy(qw).to(DEV), C)
+    assert torch.equal(C.cpu(), R.ref_bitnet_int32(A, B))
+
+
+# ------------------------------- C ABI error paths ---------------------------
+
+def test_c_abi_rejects_bad_arguments_without_launching():
+    import ctypes
+    from tilelang_b200 import _lib
+    lib = _lib.load()
+    A = torch.zeros(4, 100, dtype=torch.bfloat16, device=DEV)       # pitch 200 B: not a multiple of 16
+    args = _lib.GemmArgs(a=A.data_ptr(), wp=A.data_ptr(), c=A.data_ptr(), M=4, N=128, K=100, group_size=128,
+                         weight_format=_lib.WF_U4_SZ, act_type=_lib.ACT_BF16, out_type=_lib.OUT_BF16)
+    assert lib.b200dq_gemm(ctypes.byref(args), None) == -1
+    assert "group_size" in _lib.last_error() or "pitch" in _lib.last_error()
+    tb.check_status()
+
+
+def test_empty_batch_returns_empty_output():
+    N, K = 256, 256
+    _, qB, s, _ = w4_inputs(1, N, K, 128, torch.float16, False)
+    pw = ops.pack_w4a16(qB.to(DEV), s.to(DEV), None, N, K, 128, torch.float16)
+    out = ops.gemm(torch.zeros(0, K, dtype=torch.float16, device=DEV), pw)
+    assert out.shape == (0, N)

@@ -1,0 +1,117 @@
+"""CPU: the C-ABI library loads and exports every symbol ``include/b200dq.h``
+declares; host-side helpers and argument checks that need no GPU."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import tilelang_b200
+from tilelang_b200 import _lib, kernels, quantize
+from oracle import ref_programs as R
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "b200dq.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(b200dq_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    syms = declared_symbols()
+    assert syms, "header declares no entry points?"
+    for s in syms:
+        assert hasattr(lib, s), f"{s} declared in include/b200dq.h but not exported"
+    assert set(_lib.EXPORTED_SYMBOLS) <= set(syms)
+    assert lib.b200dq_version() >= 1
+
+
+def test_size_queries_need_no_gpu():
+    lib = _lib.load()
+    # 28672 x 8192 uint4, group 128: 224 tiles x 64 stages x (8192 + 512) bytes
+    assert lib.b200dq_packed_weight_bytes(28672, 8192, 128, _lib.WF_U4_SZ) == 224 * 64 * 8704
+    assert lib.b200dq_packed_weight_bytes(3200, 8640, 0, _lib.WF_I2_I8) == 25 * 34 * 8192
+    assert lib.b200dq_gemm_workspace_bytes(16, 28672, 8192, _lib.WF_U4_SZ, _lib.ACT_BF16, 0, 0) > 0
+    assert lib.b200dq_gemm_workspace_bytes(0, 1, 1, 0, 0, 0, 0) == 0
+
+
+def test_gemm_args_struct_matches_header_field_order():
+    text = open(os.path.join(ROOT, "include", "b200dq.h")).read()
+    body = text[text.index("typedef struct b200dq_gemm_args {"):text.index("} b200dq_gemm_args;")]
+    body = re.sub(r"/\*.*?\*/", "", body, flags=re.S)
+    names = []
+    for decl in body.split("{", 1)[1].split(";"):
+        decl = decl.strip()
+        if not decl:
+            continue
+        parts = [p.strip().lstrip("*") for p in decl.split(",")]
+        names.append(parts[0].split()[-1].lstrip("*"))
+        names.extend(parts[1:])
+    assert names == [f[0] for f in _lib.GemmArgs._fields_]
+
+
+def test_errors_are_reported_not_thrown():
+    lib = _lib.load()
+    assert lib.b200dq_gemm(None, None) == -1
+    assert "null" in _lib.last_error()
+    args = _lib.GemmArgs(M=-1, N=4, K=4)
+    assert lib.b200dq_gemm(ctypes.byref(args), None) == -1
+
+
+def test_codecs_match_oracle():
+    torch.manual_seed(1)
+    codes = torch.randint(0, 16, (4, 64), dtype=torch.uint8)
+    assert np.array_equal(quantize.compress_codes(codes, 4).numpy(), R.general_compress(codes.numpy(), 4))
+    assert torch.equal(quantize.decompress_codes(quantize.compress_codes(codes, 4), 4), codes)
+    raw = torch.randint(-128, 128, (4, 32), dtype=torch.int8)
+    for nb, tgt in [(4, "float16"), (4, "int8"), (2, "int8"), (2, "float16"), (1, "int8"), (1, "float16")]:
+        inter = quantize.interleave_weight(raw, nb, tgt)
+        assert np.array_equal(inter.numpy(), R.interleave_weight(raw.numpy(), nb, tgt))
+        assert torch.equal(quantize.deinterleave_weight(inter, nb, tgt), raw)
+
+
+def test_untwiddle_fp4_gives_natural_order():
+    qb = torch.randint(0, 256, (3, 32), dtype=torch.uint8)
+    assert torch.equal(R.decode_fp4_e2m1(quantize.untwiddle_fp4(qb)), R.decode_fp4_twiddled(qb).float())
+
+
+def test_factory_signatures_and_checks():
+    k = tilelang_b200.matmul(16, 1024, 1024, "float16", "float16", "float32", num_bits=4, group_size=128)
+    assert [p.name for p in k.params] == ["A", "B", "Scale", "C"] and k.out_idx == [-1]
+    assert k.params[1].shape == (1024, 512) and k.params[2].shape == (1024, 8)
+    with pytest.raises(ValueError):
+        k(torch.zeros(16, 1024, dtype=torch.float16))          # wrong input count (tvm_ffi.py:244-246)
+    kz = tilelang_b200.matmul(4, 256, 256, "bfloat16", "bfloat16", "float32", group_size=128, with_zeros=True)
+    assert [p.name for p in kz.params] == ["A", "B", "Scale", "Zeros", "C"]
+    kf = tilelang_b200.matmul(4, 256, 256, "bfloat16", "bfloat16", "float32", source_format="fp4", with_bias=True)
+    assert [p.name for p in kf.params] == ["A", "B", "Scale", "Bias", "C"] and kf.params[2].dtype == torch.uint8
+    with pytest.raises(ValueError):
+        tilelang_b200.matmul(4, 256, 256, "int8", "int32", "int32")
+    gv = tilelang_b200.dequantize_gemv(1, 1024, 1024, "float16", "float16", "float16", 4, "int8", "uint", 4, 32, True)
+    assert gv.out_idx is None and len(gv.params) == 3
+    w8 = tilelang_b200.matmul_int8xint4(128, 256, 256, "int8", "int32", "int32")
+    assert w8.params[2].shape == (256, 128)
+
+
+def test_no_cpu_fallback():
+    k = tilelang_b200.matmul(4, 256, 256, "float16", "float16", "float32", group_size=128)
+    A = torch.zeros(4, 256, dtype=torch.float16)
+    qB = torch.zeros(256, 128, dtype=torch.uint8)
+    S = torch.ones(256, 2, dtype=torch.float16)
+    with pytest.raises((ValueError, RuntimeError)):
+        k(A, qB, S)
+
+
+def test_product_does_not_import_oracle():
+    pkg = os.path.join(ROOT, "tilelang_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh", ".h")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert not re.search(r"^\s*(from|import)\s+oracle", src, flags=re.M), f"{f} imports the oracle"
+                assert "oracle/" not in src and "oracle." not in src, f"{f} refers to the oracle"

@@ -42,7 +42,7 @@ __device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_c
 // subnormal q * 2^-133 (bf16) or q * 2^-24 (fp16). One fma by P = 2^127 (2^15)
 // with addend -z * 2^-6 (-z * 2^-9) gives (q - z) * 2^-6 (2^-9) -- exact whenever
 // q - z fits the mantissa (always for integer z) -- and one multiply by
-// s * 2^6 (s * 2^9) lands on the same value the reference's oracle computes in
+// s * 2^6 (s * 2^9) lands on the same value the reference's ref_program computes in
 // fp32 and rounds once: RN((q - z) * s). sz word: low 16 bits = s * 2^6 (2^9),
 // high 16 bits = -z * 2^-6 (2^-9), both prepared offline in the activation dtype.
 template <bool kBf16>
