@@ -1,0 +1,391 @@
+#!/usr/bin/env python
+"""Benchmark of the dequantize-GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--m M] [--allgather]
+
+Workload (``config.workload``): the Llama-70B-MLP-shaped W4A16 GEMM with group
+zeros -- N = 28672, K = 8192, uint4 weights two per byte, group 128, bf16 scales
+U[0.005, 0.02] and bf16 zeros U[6, 10], A bf16 ~ N(0,1), fp32 accumulate, bf16 out
+-- at M = 4096 tokens (the tensor-bound end of the configuration's M sweep). A step
+is one GEMM over one batch of synthetic activations. ``value`` is TFLOPS
+(2 M N K / time) with everything resident in HBM; ``sweep`` holds the other M of the
+configuration (GB/s against the HBM roofline for M <= 16, TFLOPS otherwise), each
+timed alone with a 256 MB L2 flush before every call; ``e2e`` is the same GEMM
+through the public kernel-factory call with the activations coming from pinned host
+memory and the result going back to it inside the timed region (weights stay
+resident: they are model parameters, packed once).
+
+With ``--gpus N`` (launched under torchrun, one rank per GPU) the weight is
+column-sharded over the ranks (``tilelang_b200.parallel``); the total work is
+fixed ("strong" scaling), C stays column-sharded as a row-parallel consumer takes
+it, and ``--allgather`` adds the all-gather of C to every step.
+
+``--impl reference`` times the reference's own CPU path for this GEMM -- its torch
+``ref_program`` (dequantise, fp32 matmul, cast), restated in ``oracle/`` -- on all
+host threads, on a bounded slice of the weight rows per step.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+N_FULL, K_FULL, GROUP = 28672, 8192, 128
+SWEEP_M = (1, 16, 128, 1024, 4096)
+METRIC = "dequant-GEMM TFLOPS (M>=128) & HBM GB/s (M<=16) per B200, % of roofline"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def algorithmic_bytes(M, N, K, group):
+    # one read of every input and one write of the output, packed sizes
+    return M * K * 2 + N * K // 2 + 2 * N * (K // group) * 2 + M * N * 2
+
+
+def make_inputs(M, N, K, group, device, seed=0):
+    """Seeded synthetic stand-ins for real checkpoint tensors (one generator per tensor)."""
+    def gen(i):
+        g = torch.Generator(device="cpu")
+        g.manual_seed(seed + i)
+        return g
+    A = torch.randn(M, K, generator=gen(0), dtype=torch.float32).to(torch.bfloat16)
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(1), dtype=torch.uint8)          # two uniform uint4 per byte
+    s = (torch.rand(N, K // group, generator=gen(2)) * 0.015 + 0.005).to(torch.bfloat16)
+    z = (torch.rand(N, K // group, generator=gen(3)) * 4.0 + 6.0).to(torch.bfloat16)
+    return A, qB, s, z
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._pump, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def time_with_flush(fn, iters, flush):
+    """Median milliseconds of ``fn`` over ``iters`` calls, L2 flushed before each."""
+    times = []
+    for _ in range(iters):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    return statistics.median(times)
+
+
+def cpu_reference_tflops(M, n_rows, threads, reps=1, seed=0):
+    """The reference's CPU path (torch ref_program restated in oracle/) on a slice of
+    ``n_rows`` weight rows: dequantise to bf16, fp32 matmul, cast -- dequantisation included."""
+    from oracle import ref_programs as R
+    torch.set_num_threads(threads)
+    A, qB, s, z = make_inputs(M, n_rows, K_FULL, GROUP, "cpu", seed)
+    R.ref_w4a16(A[:8], qB[:128], s[:128], z[:128], GROUP, torch.bfloat16)      # warm the thread pool
+    best = None
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        R.ref_w4a16(A, qB, s, z, GROUP, torch.bfloat16)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return 2.0 * M * n_rows * K_FULL / best / 1e12, best
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    M = args.m
+    n_rows = 1024 if M >= 1024 else 4096
+    vals, secs = [], []
+    for i in range(args.warmup + args.steps):
+        v, dt = cpu_reference_tflops(M, n_rows, threads, reps=1, seed=i)
+        if i >= args.warmup:
+            vals.append(v)
+            secs.append(dt)
+    value = statistics.mean(vals)
+    sample = f"weight rows [0, {n_rows}) of {N_FULL} per step, M={M}, K={K_FULL}, dequantisation included"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * statistics.mean(secs),
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(M, args.gpus, args.allgather),
+        "cpu_baseline": {"value": value, "unit": "TFLOPS", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(M, gpus, allgather):
+    return {"workload": f"W4A16 dequant-GEMM with group zeros, Llama-70B-MLP shape: M={M}, N={N_FULL}, K={K_FULL}, "
+                        f"group_size={GROUP}, bf16 activations/scales/zeros, fp32 accumulate, bf16 out",
+            "M": M, "N": N_FULL, "K": K_FULL, "group_size": GROUP,
+            "parallelism": "single GPU" if gpus == 1 else f"column-parallel over N, {gpus} ranks, "
+                           + ("all-gather of C per step" if allgather else "C left column-sharded (no collective)"),
+            "l2": "working set (A + packed W + C = 0.43 GB at M=4096) exceeds the 126 MB L2; sweep entries flush L2 "
+                  "(256 MB write) before every timed call"}
+
+
+def load_traffic_note():
+    """Per-launch DRAM traffic of the dominant kernel from the committed ncu summary."""
+    path = os.path.join(ROOT, "profiles", "traffic.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return json.load(f)
+    return {}
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch.distributed as dist
+    from tilelang_b200 import ops, kernels
+    from tilelang_b200.parallel import plan_column_shards
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    peaks = measured_peaks()
+    M = args.m
+
+    shard = plan_column_shards(N_FULL, world)[rank]
+    n_local = shard.size
+    A_h, qB_h, s_h, z_h = make_inputs(M, N_FULL, K_FULL, GROUP, "cpu")
+    rows = slice(shard.start, shard.stop)
+    qB, s, z = qB_h[rows].to(dev), s_h[rows].contiguous().to(dev), z_h[rows].contiguous().to(dev)
+    A = A_h.to(dev)
+    pw = ops.pack_w4a16(qB, s, z, n_local, K_FULL, GROUP, torch.bfloat16)
+    C = torch.empty(M, n_local, dtype=torch.bfloat16, device=dev)
+    C_full = torch.empty(world * M, n_local, dtype=torch.bfloat16, device=dev) if (args.allgather and world > 1) else None
+    torch.cuda.synchronize()
+
+    def step():
+        ops.gemm(A, pw, out=C)
+        if C_full is not None:
+            dist.all_gather_into_tensor(C_full, C)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    launches_per_step = 2      # the GEMM and the stream-K fix-up pass
+    with ClockSampler(local_rank) as clocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        barrier()
+        ms_total = e0.elapsed_time(e1)
+        time.sleep(0.25)
+    ops.check_status(dev)
+    t = torch.tensor([ms_total], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_step = t.item() / args.steps
+    flops = 2.0 * M * N_FULL * K_FULL
+    value = flops / (ms_step * 1e-3) / 1e12
+
+    # ---- end to end through the public factory call, host buffers -------------------
+    kernel = kernels.matmul(M, n_local, K_FULL, "bfloat16", "bfloat16", "float32", num_bits=4, group_size=GROUP,
+                            with_zeros=True)
+    kernel.pack(qB, s, z)
+    A_pin = A_h.pin_memory()
+    C_pin = torch.empty(M, n_local, dtype=torch.bfloat16).pin_memory()
+    A_dev = [torch.empty_like(A) for _ in range(2)]
+    copy_in, copy_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    compute = torch.cuda.current_stream(dev)
+
+    def e2e_steps(n):
+        """H2D of the activations, GEMM, D2H of the result; the copies of neighbouring
+        steps overlap the GEMM on their own streams (two activation buffers)."""
+        buf_free = [None, None]           # event: last GEMM that read each activation buffer
+        prev_out, prev_done = None, None
+        for i in range(n):
+            b = i % 2
+            with torch.cuda.stream(copy_in):
+                if buf_free[b] is not None:
+                    copy_in.wait_event(buf_free[b])
+                A_dev[b].copy_(A_pin, non_blocking=True)
+                ready = torch.cuda.Event()
+                ready.record(copy_in)
+            compute.wait_event(ready)
+            out = kernel(A_dev[b], qB, s, z)
+            done = torch.cuda.Event()
+            done.record(compute)
+            buf_free[b] = done
+            if prev_out is not None:
+                with torch.cuda.stream(copy_out):
+                    copy_out.wait_event(prev_done)
+                    C_pin.copy_(prev_out, non_blocking=True)
+                    prev_out.record_stream(copy_out)
+            prev_out, prev_done = out, done
+        with torch.cuda.stream(copy_out):
+            copy_out.wait_event(prev_done)
+            C_pin.copy_(prev_out, non_blocking=True)
+            prev_out.record_stream(copy_out)
+        copy_out.synchronize()
+        return float(C_pin[0, 0])         # the host reads the result
+
+    e2e_steps(2)
+    barrier()
+    t0 = time.perf_counter()
+    e2e_steps(args.steps)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    t = torch.tensor([e2e_s], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = flops * args.steps / t.item() / 1e12
+
+    if rank != 0:
+        return
+
+    # ---- the rest of the configuration's M sweep, single GPU numbers -----------------
+    sweep = {}
+    if world == 1 and not args.no_sweep:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        for m in SWEEP_M:
+            a = torch.randn(m, K_FULL, device=dev).to(torch.bfloat16)
+            c = torch.empty(m, N_FULL, dtype=torch.bfloat16, device=dev)
+            for _ in range(3):
+                ops.gemm(a, pw, out=c)
+            ms = time_with_flush(lambda: ops.gemm(a, pw, out=c), 15, flush)
+            fl, by = 2.0 * m * N_FULL * K_FULL, algorithmic_bytes(m, N_FULL, K_FULL, GROUP)
+            entry = {"ms": ms, "tflops": fl / ms / 1e9, "gbs": by / ms / 1e6}
+            if m <= 16:
+                entry.update(bound="hbm", frac_of_measured_hbm=entry["gbs"] / peaks["hbm_gbs"])
+            else:
+                entry.update(bound="tensor", frac_of_measured_bf16=entry["tflops"] / peaks["bf16_tflops"])
+            sweep[f"M={m}"] = entry
+        ops.check_status(dev)
+
+    cpu = None
+    if world == 1 and not args.no_cpu_baseline:
+        threads = os.cpu_count() or 1
+        n_rows = 1024
+        v, dt = cpu_reference_tflops(M, n_rows, threads, reps=2)
+        cpu = {"value": v, "unit": "TFLOPS", "cores": threads, "kind": "port",
+               "sample": f"weight rows [0, {n_rows}) of {N_FULL}, M={M}, K={K_FULL}, best of 2, {dt:.2f} s, "
+                         "dequantisation included"}
+
+    traffic = load_traffic_note()
+    out = {
+        "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(M, world, args.allgather),
+        "roofline": {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                     "frac": value / world / peaks["bf16_tflops"], "traffic": traffic.get("dram_bytes_per_launch"),
+                     "peak_source": f"{peaks['source']} burst bf16 (sustained {peaks['bf16_tflops_sustained']})",
+                     "frac_of_sustained": value / world / peaks["bf16_tflops_sustained"],
+                     "kernel": "umma_dequant_gemm_kernel<256, U4_SZ, BF16>; duration = step time (GEMM + fix-up pass)",
+                     "traffic_source": traffic.get("source")},
+        "cpu_baseline": cpu,
+        "e2e": {"value": e2e_value, "unit": "TFLOPS", "h2d_bytes_per_step": M * K_FULL * 2 * world,
+                "d2h_bytes_per_step": M * N_FULL * 2,
+                "note": "activations from pinned host memory and result back to it every step; packed weights resident"},
+        "gpu_launches": launches_per_step * args.steps * world,
+        "clocks": clocks.summary(),
+        "sweep": sweep,
+    }
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=30)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--allgather", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if world > 1:
+            import torch.distributed as dist
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
