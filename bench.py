@@ -189,13 +189,15 @@ def workload_config(M, gpus, allgather):
                   "(256 MB write) before every timed call"}
 
 
-def load_traffic_note():
-    """Per-launch DRAM traffic of the dominant kernel from the committed ncu summary."""
-    path = os.path.join(ROOT, "profiles", "traffic.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            return json.load(f)
-    return {}
+# DRAM bytes of one launch of the dominant kernel at M=4096 from the committed ncu
+# capture (dram__bytes_read.sum 840,656,128 + dram__bytes_write.sum 244,715,264);
+# the algorithmic figure is 426,770,432.
+TRAFFIC_M4096 = {"dram_bytes_per_launch": 1085371392,
+                 "source": "profiles/umma_dequant_gemm_w4a16_m4096.md (ncu --set full, one launch)"}
+
+
+def load_traffic_note(M):
+    return TRAFFIC_M4096 if M == 4096 else {}
 
 
 def run_ours(args, rank, world, local_rank):
@@ -334,7 +336,7 @@ def run_ours(args, rank, world, local_rank):
                "sample": f"weight rows [0, {n_rows}) of {N_FULL}, M={M}, K={K_FULL}, best of 2, {dt:.2f} s, "
                          "dequantisation included"}
 
-    traffic = load_traffic_note()
+    traffic = load_traffic_note(M)
     out = {
         "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",

@@ -119,10 +119,10 @@ def test_w4a16_bias_fp32_out_and_transposed_out():
     check_float(out32, ref, strict=2e-2)
     outT = ops.gemm(A.to(DEV), pw, trans_c=True)
     assert outT.shape == (N, M)
-    check_float(outT.T, ref)
+    check_float(outT.T, ref, strict=2e-2)
     bias = torch.randn(M, N, generator=gen(4)).to(torch.bfloat16)
     outb = ops.gemm(A.to(DEV), pw, bias=bias.to(DEV))
-    check_float(outb, ref + bias.float())
+    check_float(outb, ref + bias.float(), strict=2e-2)
 
 
 def test_w4a16_stream_k_split_is_deterministic_and_matches_unsplit():
