@@ -111,6 +111,27 @@ int b200dq_pack_weights(const void* q_natural, const void* scales, const void* z
                         int32_t K, int32_t group_size, int32_t weight_format, int32_t act_type,
                         void* cuda_stream);
 
+/* No counterpart in the reference. The same GEMM as b200dq_gemm for callers that
+ * cannot allocate device memory at all -- code running where cudaMalloc is off
+ * limits (inside another framework's allocator callbacks, under a memory pool that
+ * owns the whole device, in a process that was handed pre-mapped buffers only). The
+ * stream-K partial tiles go to a fixed 40 MiB array compiled into the library's
+ * device image instead of `workspace` (args->workspace and workspace_bytes are
+ * ignored); every GPU that loads the library holds those 40 MiB until the process
+ * exits. Inputs and the output are still the caller's.
+ *   - A problem whose schedule needs more than 40 MiB of scratch is rejected with an
+ *     error (no schedule on a 148-SM part needs more than 38,797,312 bytes).
+ *   - The first call on a device looks up the array's device address and the
+ *     device's properties; make that first call outside any stream capture.
+ *   - It calls no cudaMalloc, cudaFree or allocating library routine, and it does
+ *     not need b200dq_init. If b200dq_init has run on the device, waits that give
+ *     up are recorded in its status word; otherwise they are bounded but unrecorded.
+ *   - All calls share the one array, which keeps whatever the last call left in it.
+ *     Nothing in it has to start at zero (a launch reads only slots it wrote), but two
+ *     calls that overlap on the GPU -- different streams, or graphs replayed
+ *     concurrently -- race on it: serialise them. */
+int b200dq_gemm_static_scratch(const b200dq_gemm_args* args, void* cuda_stream);
+
 /* Reads the device status word of the current device (synchronises `stream`).
  * Returns 0 if no kernel recorded an error since the last reset, else -1 with a
  * message naming the wait that gave up; resets the word. */

@@ -25,6 +25,7 @@ EXPORTED_SYMBOLS = (
     "b200dq_get_last_error",
     "b200dq_version",
     "b200dq_gemm",
+    "b200dq_gemm_static_scratch",
     "b200dq_gemm_workspace_bytes",
     "b200dq_packed_weight_bytes",
     "b200dq_pack_weights",
@@ -77,6 +78,8 @@ def _declare(lib):
     lib.b200dq_version.argtypes = []
     lib.b200dq_gemm.restype = ctypes.c_int
     lib.b200dq_gemm.argtypes = [ctypes.POINTER(GemmArgs), vp]
+    lib.b200dq_gemm_static_scratch.restype = ctypes.c_int
+    lib.b200dq_gemm_static_scratch.argtypes = [ctypes.POINTER(GemmArgs), vp]
     lib.b200dq_gemm_workspace_bytes.restype = sz
     lib.b200dq_gemm_workspace_bytes.argtypes = [i32, i32, i32, i32, i32, i32, i32]
     lib.b200dq_packed_weight_bytes.restype = sz

@@ -57,6 +57,22 @@ DeviceState g_dev[kMaxDevices];
 unsigned long long* g_prof = nullptr;   // profiling builds: per-CTA phase timers
 EncodeTiledFn g_encode = nullptr;
 
+// ---- state of b200dq_gemm_static_scratch ------------------------------------
+// Scratch for callers that cannot allocate device memory: a fixed array that lives
+// in the library's device image (every GPU that loads the library holds it until
+// the process exits). 40 MiB covers the stream-K partial tiles of every schedule on
+// a part with up to 148 SMs (148 CTAs x 2 slots x 256 tokens x 128 rows x 4 B =
+// 38,797,312 B).
+constexpr size_t kStaticScratchBytes = 40u << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+struct StaticScratchState {
+  bool ready = false;
+  int sm_count = 0;
+  void* scratch = nullptr;   // device address of g_static_scratch on this device
+};
+StaticScratchState g_static_dev[kMaxDevices];
+
 int current_device_state(DeviceState** out) {
   int dev = 0;
   CUDA_OK(cudaGetDevice(&dev));
@@ -365,6 +381,100 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
 // profiling builds only: device buffer of 32 x u64 per CTA for phase timers
 void b200dq_debug_set_profile_buffer(void* buf) { g_prof = static_cast<unsigned long long*>(buf); }
 #endif
+
+int b200dq_gemm_static_scratch(const b200dq_gemm_args* a, void* cuda_stream) {
+  if (a == nullptr) return fail("gemm_static_scratch: null argument struct");
+  int dev = 0;
+  CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return fail("device index %d out of range", dev);
+  StaticScratchState& ss = g_static_dev[dev];
+  if (!ss.ready) {
+    // One-time set-up for this device, with this device current. In host code the
+    // array's name is only a stand-in; the kernels need its device address.
+    std::lock_guard<std::mutex> lock(g_mu);
+    if (!ss.ready) {
+      cudaDeviceProp prop;
+      CUDA_OK(cudaGetDeviceProperties(&prop, dev));
+      if (prop.major != 10) return fail("b200dq needs an sm_100 GPU, device %d is sm_%d%d", dev, prop.major, prop.minor);
+      if (g_encode == nullptr) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+        if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return fail("driver has no cuTensorMapEncodeTiled");
+        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+      }
+      void* ptr = nullptr;
+      CUDA_OK(cudaGetSymbolAddress(&ptr, g_static_scratch));
+      if (ptr == nullptr) return fail("gemm_static_scratch: no device address for the static scratch array");
+      ss.scratch = ptr;
+      ss.sm_count = prop.multiProcessorCount;
+      ss.ready = true;
+    }
+  }
+  if (a->a == nullptr || a->wp == nullptr || a->c == nullptr) return fail("gemm_static_scratch: null tensor pointer");
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0)
+    return fail("gemm_static_scratch: M, N, K must be positive (got %d, %d, %d)", a->M, a->N, a->K);
+  Schedule s;
+  if (make_schedule(a->M, a->N, a->K, a->act_type, a->token_tile, a->max_ctas, ss.sm_count, &s) != 0) return -1;
+  if (s.workspace_bytes > kStaticScratchBytes)
+    return fail("gemm_static_scratch: this problem needs %zu bytes of scratch, the static array holds %zu; "
+                "lower max_ctas or use b200dq_gemm with a caller-provided workspace",
+                s.workspace_bytes, kStaticScratchBytes);
+  // Same checks, schedule and launch as b200dq_gemm, with the scratch pointer replaced.
+  const int wf = a->weight_format, act = a->act_type;
+  const bool int_act = (act == ACT_I8);
+  const bool wf_int = (wf == WF_I2_I8 || wf == WF_I4_I8);
+  if (wf < WF_U4_SZ || wf > WF_I4_I8) return fail("gemm_static_scratch: unknown weight format %d", wf);
+  if (act < ACT_F16 || act > ACT_I8) return fail("gemm_static_scratch: unknown activation type %d", act);
+  if (a->out_type < OUT_F16 || a->out_type > OUT_I32) return fail("gemm_static_scratch: unknown output type %d", a->out_type);
+  if (wf_int != int_act) return fail("gemm_static_scratch: weight format %d and activation type %d do not go together", wf, act);
+  if (wf == WF_FP4_E8M0 && act != ACT_BF16) return fail("gemm_static_scratch: e2m1 weights need bf16 activations");
+  if (wf == WF_U4_SZ && (a->group_size <= 0 || a->K % a->group_size != 0))
+    return fail("gemm_static_scratch: group_size=%d must divide K=%d", a->group_size, a->K);
+  if ((a->flags & GF_HAS_BIAS) && a->bias == nullptr) return fail("gemm_static_scratch: HAS_BIAS set but bias is null");
+  if ((a->flags & GF_ROW_SCALE) && a->row_scale == nullptr) return fail("gemm_static_scratch: ROW_SCALE set but row_scale is null");
+  if ((reinterpret_cast<uintptr_t>(a->wp) & 15) != 0) return fail("gemm_static_scratch: packed weights must be 16-byte aligned");
+
+  CUtensorMap tmap;
+  if (encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn) != 0) return -1;
+  int flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
+  if (output_takes_vector_stores(a->c, a->N, a->out_type, flags)) flags |= GF_VEC_STORE;
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.wp = static_cast<const uint8_t*>(a->wp);
+  p.c = a->c;
+  p.partial = static_cast<uint32_t*>(ss.scratch);
+  p.bias = a->bias;
+  p.row_scale = a->row_scale;
+  p.tensor_scale = a->tensor_scale;
+  p.code_bias = a->code_bias;
+  p.fp4_exp_bias = a->fp4_exp_bias;
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  p.n_tiles = s.n_tiles; p.m_tiles = s.m_tiles; p.st_total = s.st_total;
+  p.span = s.span; p.units = s.units;
+  p.stage_bytes = stage_bytes_for(wf, a->group_size);
+  p.sz_per_kb = (wf == WF_U4_SZ && a->group_size == 64) ? 1 : 0;
+  p.ldc = (a->flags & GF_TRANS_C) ? a->M : a->N;
+  p.flags = flags;
+  p.out_type = a->out_type;
+  // device-side status reporting needs the word b200dq_init allocates; without it the
+  // kernels still bound every wait, they just have nowhere to record one that gave up
+  p.status = g_dev[dev].ready ? g_dev[dev].status : nullptr;
+  p.prof = nullptr;
+
+  auto stream = static_cast<cudaStream_t>(cuda_stream);
+  if (wf == WF_U4_SZ && act == ACT_F16) return dispatch_tn<WF_U4_SZ, ACT_F16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_U4_SZ && act == ACT_BF16) return dispatch_tn<WF_U4_SZ, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_U4_RAW && act == ACT_F16) return dispatch_tn<WF_U4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_U4_RAW && act == ACT_BF16) return dispatch_tn<WF_U4_RAW, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_S4_RAW && act == ACT_F16) return dispatch_tn<WF_S4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_S4_RAW && act == ACT_BF16) return dispatch_tn<WF_S4_RAW, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_FP4_E8M0) return dispatch_tn<WF_FP4_E8M0, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_I2_I8) return dispatch_tn<WF_I2_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
+  if (wf == WF_I4_I8) return dispatch_tn<WF_I4_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
+  return fail("gemm_static_scratch: no kernel for weight format %d with activation type %d", wf, act);
+}
 
 int b200dq_check_status(void* cuda_stream) {
   DeviceState* ds = nullptr;
