@@ -136,25 +136,40 @@ int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_cta
   return 0;
 }
 
-int encode_activation_map(CUtensorMap* map, const void* a, int M, int K, int act_type, int tn) {
+// Tensor map of the activations. With `group` > 1 k-blocks per load the map is 3-D,
+// {k-block element, token row, k-block index}, so one TMA lands `group` consecutive
+// k-blocks as separate [row][128 B] slabs; that view needs K to be a whole number of
+// k-blocks. Returns the group size actually encoded (1 = plain 2-D map) or -1.
+int encode_activation_map(CUtensorMap* map, const void* a, int M, int K, int act_type, int tn, int group) {
   if (g_encode == nullptr) return fail("tensor-map encoder not resolved (b200dq_init not run?)");
   const int esize = (act_type == ACT_I8) ? 1 : 2;
   const int bke = k_elems_per_kblock(act_type);
   if ((reinterpret_cast<uintptr_t>(a) & 15) != 0) return fail("activation pointer must be 16-byte aligned");
   if ((static_cast<long long>(K) * esize) % 16 != 0) return fail("activation row pitch must be a multiple of 16 bytes");
+  const CUtensorMapDataType dt = act_type == ACT_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : act_type == ACT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  if (group > 1 && K % bke == 0) {
+    cuuint64_t dims[3] = {static_cast<cuuint64_t>(bke), static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(K / bke)};
+    cuuint64_t strides[2] = {static_cast<cuuint64_t>(K) * esize, static_cast<cuuint64_t>(bke) * esize};
+    cuuint32_t box[3] = {static_cast<cuuint32_t>(bke), static_cast<cuuint32_t>(tn), static_cast<cuuint32_t>(group)};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = g_encode(map, dt, 3, const_cast<void*>(a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) return group;
+    // fall through to the 2-D map
+  }
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
   cuuint64_t strides[1] = {static_cast<cuuint64_t>(K) * esize};
   cuuint32_t box[2] = {static_cast<cuuint32_t>(bke), static_cast<cuuint32_t>(tn)};
   cuuint32_t estr[2] = {1, 1};
-  const CUtensorMapDataType dt = act_type == ACT_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                                 : act_type == ACT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   CUresult r = g_encode(map, dt, 2, const_cast<void*>(a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with CUresult %d (M=%d K=%d box=%dx%d)",
                                      static_cast<int>(r), M, K, bke, tn);
-  return 0;
+  return 1;
 }
 
 int out_elem_size(int out_type) { return (out_type == OUT_F16 || out_type == OUT_BF16) ? 2 : 4; }
@@ -180,16 +195,15 @@ int launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStre
   }
   kernel<<<grid, kThreads, Ring::kSmemBytes, stream>>>(tmap, p);
   CUDA_OK(cudaGetLastError());
-  // stream-K second pass: only tiles cut between CTAs do any work
-  const long long tiles = static_cast<long long>(p.m_tiles) * p.n_tiles;
+  // stream-K second pass: one block column per cut between neighbouring CTAs
   if (p.span % p.st_total != 0 && grid > 1) {
     constexpr bool kInt = (ACT == ACT_I8);
-    const int t = static_cast<int>(tiles);
+    const dim3 fgrid(grid - 1, TN >= 32 ? TN / 32 : 1);
     switch (p.out_type) {
-      case OUT_F16: streamk_fixup_kernel<__half, TN, kInt><<<t, kTileRows, 0, stream>>>(p); break;
-      case OUT_BF16: streamk_fixup_kernel<__nv_bfloat16, TN, kInt><<<t, kTileRows, 0, stream>>>(p); break;
-      case OUT_F32: streamk_fixup_kernel<float, TN, kInt><<<t, kTileRows, 0, stream>>>(p); break;
-      default: streamk_fixup_kernel<int, TN, kInt><<<t, kTileRows, 0, stream>>>(p); break;
+      case OUT_F16: streamk_fixup_kernel<__half, TN, kInt><<<fgrid, kTileRows, 0, stream>>>(p); break;
+      case OUT_BF16: streamk_fixup_kernel<__nv_bfloat16, TN, kInt><<<fgrid, kTileRows, 0, stream>>>(p); break;
+      case OUT_F32: streamk_fixup_kernel<float, TN, kInt><<<fgrid, kTileRows, 0, stream>>>(p); break;
+      default: streamk_fixup_kernel<int, TN, kInt><<<fgrid, kTileRows, 0, stream>>>(p); break;
     }
     CUDA_OK(cudaGetLastError());
   }
@@ -339,12 +353,14 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
   }
 
   CUtensorMap tmap;
-  if (encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn) != 0) return -1;
+  const int b_group = encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn, group_kblocks_for(s.tn));
+  if (b_group < 0) return -1;
   int flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
   if (output_takes_vector_stores(a->c, a->N, a->out_type, flags)) flags |= GF_VEC_STORE;
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
+  p.b_group = b_group;
   p.wp = static_cast<const uint8_t*>(a->wp);
   p.c = a->c;
   p.partial = static_cast<uint32_t*>(a->workspace);
@@ -436,12 +452,14 @@ int b200dq_gemm_static_scratch(const b200dq_gemm_args* a, void* cuda_stream) {
   if ((reinterpret_cast<uintptr_t>(a->wp) & 15) != 0) return fail("gemm_static_scratch: packed weights must be 16-byte aligned");
 
   CUtensorMap tmap;
-  if (encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn) != 0) return -1;
+  const int b_group = encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn, group_kblocks_for(s.tn));
+  if (b_group < 0) return -1;
   int flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
   if (output_takes_vector_stores(a->c, a->N, a->out_type, flags)) flags |= GF_VEC_STORE;
 
   GemmParams p;
   memset(&p, 0, sizeof(p));
+  p.b_group = b_group;
   p.wp = static_cast<const uint8_t*>(a->wp);
   p.c = a->c;
   p.partial = static_cast<uint32_t*>(ss.scratch);

@@ -94,6 +94,7 @@ struct GemmParams {
   long long units;           // m_tiles * n_tiles * st_total
   int stage_bytes;           // bytes of one packed stage in global memory
   int sz_per_kb;             // 1 if each k-block of a stage has its own scale word (group 64)
+  int b_group;               // k-blocks per activation TMA: the tile's group size, or 1 (2-D map only)
   int ldc;                   // leading dimension of the output
   int flags;
   int out_type;
@@ -104,40 +105,50 @@ struct GemmParams {
 constexpr int kTileRows = 128;        // weight rows per CTA tile (= TMEM lanes)
 constexpr int kThreads = 512;
 constexpr int kStageBufBytes = 2048;                    // one epilogue staging buffer: 32 n x 32 m x 2 B
-constexpr int kStagingBytesPerWarp = 2 * kStageBufBytes;   // double-buffered
+constexpr int kStagingBytesPerWarp = kStageBufBytes;      // one 32 x 32 x 2-byte transpose buffer per epilogue warp
 constexpr int kMaxSlots = 16;
 
 __host__ __device__ constexpr int codes_per_kblock_bytes(int wf) { return wf == WF_I4_I8 ? 8192 : 4096; }
 // scale words carried by one stage in shared memory (upper bound, bytes)
 __host__ __device__ constexpr int sz_smem_bytes(int wf) { return wf == WF_U4_SZ ? 1024 : (wf == WF_FP4_E8M0 ? 512 : 0); }
-__host__ __device__ constexpr int issuers_for(int tn) { return tn >= 256 ? 1 : (tn >= 128 ? 2 : 3); }
 
 // TMEM plan: accumulators of the NI issuers in columns [0, kAccCols), then a ring
-// of kSlots dequantised k-blocks (32 columns each). The activation ring in shared
-// memory has at most as many stages, so one "consumed" barrier per slot serves both.
+// of kSlots dequantised k-blocks (32 columns each).
+// Shared memory: an activation ring of kNBG groups (one TMA each, kGB k-blocks), a
+// weight ring of kNWP slots holding a *pair* of packed stages (one bulk copy
+// each), and 4 KiB of epilogue staging per epilogue warp.
+__host__ __device__ constexpr int issuers_for(int tn) { return tn >= 256 ? 1 : 2; }
+__host__ __device__ constexpr int group_kblocks_for(int tn) { return tn >= 256 ? 1 : (tn >= 128 ? 2 : 4); }
+
 template <int TN, int WF>
 struct RingConfig {
   static constexpr int kNI = issuers_for(TN);
+  static constexpr int kGB = group_kblocks_for(TN);
   static constexpr int kAccCols = ((kNI * TN + 31) / 32) * 32;
   static constexpr int kSlots = (512 - kAccCols) / 32 > 14 ? 14 : (512 - kAccCols) / 32;
-  static constexpr int kBStageBytes = TN * 128;
-  static constexpr int kCodeBytes = 2 * codes_per_kblock_bytes(WF);          // per stage
-  static constexpr int kWStageSmem = kCodeBytes + sz_smem_bytes(WF);         // smem stride
-  static constexpr int kNB = TN >= 256 ? 5 : kSlots;
-  static constexpr int kWBudget = TN >= 256 ? 37 * 1024 : (TN >= 128 ? 74 * 1024 : 110 * 1024);
-  static constexpr int kNW = kWBudget / kWStageSmem;
+  static constexpr int kBSlabBytes = TN * 128;                                // one k-block of activations
+  static constexpr int kBGroupBytes = kGB * kBSlabBytes;
+  static constexpr int kNBG = TN >= 256 ? (WF == WF_I4_I8 ? 5 : 6) : (TN >= 128 ? 4 : (TN >= 64 ? 3 : 4));
+  static constexpr int kCodeBytes = 2 * codes_per_kblock_bytes(WF);           // per stage
+  static constexpr int kWStageMax = kCodeBytes + sz_smem_bytes(WF);           // largest packed stage
+  static constexpr int kWPairSmem = 2 * kWStageMax;                           // ring slot: two stages back to back
   static constexpr int kStaging = 4 * kStagingBytesPerWarp;
-  static constexpr int kSmemBytes = kNB * kBStageBytes + kNW * kWStageSmem + kStaging + 1024 /*align*/ + 1024 /*ctl*/;
-  static_assert(kSlots >= 8 && kSlots <= kMaxSlots && kNB <= kSlots, "ring depths");
-  static_assert(kNW >= 2 && kNW <= 32, "weight ring depth");
-  static_assert(kWStageSmem % 128 == 0, "stage stride keeps 128 B alignment");
+  static constexpr int kFixed = kNBG * kBGroupBytes + kStaging + 1024 /*align*/ + 1024 /*ctl*/;
+  static constexpr int kNWPfit = (232448 - kFixed) / kWPairSmem;
+  static constexpr int kNWP = kNWPfit > 8 ? 8 : kNWPfit;
+  static constexpr int kSmemBytes = kFixed + kNWP * kWPairSmem;
+  static_assert(kSlots >= 8 && kSlots <= kMaxSlots, "TMEM ring depth");
+  static_assert(kGB > 1 || (kNI == 1 && kNBG <= kSlots), "single-k-block groups reuse the cons barriers");
+  static_assert(kNWP >= 1, "weight ring depth");
+  static_assert(kWStageMax % 128 == 0, "stage keeps 128 B alignment");
   static_assert(kSmemBytes <= 232448, "over the 227 KiB shared-memory limit");
 };
 
 struct SharedCtl {
-  uint64_t full_w[32];
-  uint64_t empty_w[32];
-  uint64_t full_b[kMaxSlots];
+  uint64_t full_w[8];
+  uint64_t empty_w[8];
+  uint64_t full_b[8];
+  uint64_t empty_b[8];
   uint64_t a_full[kMaxSlots];
   uint64_t cons[kMaxSlots];
   uint64_t acc_full;
@@ -277,9 +288,10 @@ template <int TN, int WF, int ACT>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
   using Ring = RingConfig<TN, WF>;
-  constexpr int NB = Ring::kNB;
-  constexpr int NW = Ring::kNW;
-  constexpr int WSS = Ring::kWStageSmem;
+  constexpr int NBG = Ring::kNBG;        // activation groups in the ring
+  constexpr int GB = Ring::kGB;          // k-blocks per activation group (compile-time maximum)
+  constexpr int NWP = Ring::kNWP;        // weight-stage pairs in the ring
+  constexpr int WPS = Ring::kWPairSmem;
   constexpr int CPK = codes_per_kblock_bytes(WF);   // code bytes per k-block
   constexpr int NI = Ring::kNI;
   constexpr int NS = Ring::kSlots;       // dequantised TMEM ring slots
@@ -290,23 +302,26 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
   constexpr int NV = TN >= 32 ? 32 : 16; // accumulator columns per tcgen05.ld
 
 #ifdef B200DQ_PROFILE
-  __shared__ long long prof_ts_b[kMaxSlots];   // issue time of the activation load in each stage
+  __shared__ long long prof_ts_b[8];   // issue time of the activation load in each ring slot
 #endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* smem_b = smem;                                   // NB x (TN x 128 B), 1024-aligned stages
-  uint8_t* smem_w = smem_b + NB * Ring::kBStageBytes;       // NW x stage
-  uint8_t* smem_o = smem_w + NW * WSS;                      // epilogue staging, 8 KiB per warp
+  uint8_t* smem_b = smem;                                   // NBG x (GB x TN x 128 B), 1024-aligned slabs
+  uint8_t* smem_w = smem_b + NBG * Ring::kBGroupBytes;      // NWP x pair of stages
+  uint8_t* smem_o = smem_w + NWP * WPS;                     // epilogue staging, 4 KiB per warp
   SharedCtl* ctl = reinterpret_cast<SharedCtl*>(smem_o + Ring::kStaging);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   volatile int* abort_flag = &ctl->abort_flag;
   DeviceStatus* st = p.status;
+  // k-blocks per activation group at run time: GB, or 1 when K is not a whole number
+  // of k-blocks per row (then only the 2-D tensor map is valid)
+  const int gsz = p.b_group;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < NW; ++i) { mbar_init(&ctl->full_w[i], 1); mbar_init(&ctl->empty_w[i], 4); }
-    for (int i = 0; i < NB; ++i) mbar_init(&ctl->full_b[i], 1);
+    for (int i = 0; i < NWP; ++i) { mbar_init(&ctl->full_w[i], 1); mbar_init(&ctl->empty_w[i], 8); }
+    for (int i = 0; i < NBG; ++i) { mbar_init(&ctl->full_b[i], 1); mbar_init(&ctl->empty_b[i], NI); }
     for (int i = 0; i < NS; ++i) { mbar_init(&ctl->a_full[i], 4); mbar_init(&ctl->cons[i], 1); }
     mbar_init(&ctl->acc_full, NI);
     mbar_init(&ctl->acc_empty, 4);
@@ -317,102 +332,82 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
     tmem_alloc(&ctl->tmem_base, 512);
     tmem_relinquish();
   }
-  if (warp == 0 && lane == 0) {
-    tma_prefetch_desc(&tmap_a);
-  }
+  if (warp == 3 && lane == 0) tma_prefetch_desc(&tmap_a);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = ctl->tmem_base;
 
   if (warp == 0) {
-    // ---------------- producer: two independent streams (weight stages and
-    // activation k-blocks) served by one thread; each is issued as soon as its
-    // ring has room, polled without blocking so neither delays the other ----
+    // ---------------- weight producer: one bulk copy per pair of packed stages ----
     if (lane == 0) {
-      SegmentWalk walk_w(p), walk_b(p);
-      Segment sw_seg, sb_seg;
-      bool have_w = walk_w.next(p, sw_seg), have_b = walk_b.next(p, sb_seg);
-      int st_w = have_w ? sw_seg.st_begin : 0, kb_b = have_b ? sb_seg.st_begin * 2 : 0;
-      uint32_t wc = 0;   // weight stages issued
-      uint32_t bc = 0;   // k-blocks of activations issued
-      uint64_t t_idle = 0;
-      uint32_t idle = 0;
-      PROF_DECL(pp_w); PROF_DECL(pp_b); PROF_DECL(pp_idle); PROF_DECL(pp_iters);
-      PROF_T0(tp);
-      while (have_w || have_b) {
-        bool progressed = false;
-
-        if (have_w) {
-          const uint32_t s = wc % NW;
-          if (mbar_test_wait(&ctl->empty_w[s], ((wc / NW) & 1) ^ 1)) {
-            mbar_arrive_expect_tx(&ctl->full_w[s], p.stage_bytes);
-            const uint8_t* src = p.wp + (static_cast<size_t>(sw_seg.n_tile) * p.st_total + st_w) * p.stage_bytes;
-            tma_bulk_g2s(smem_w + s * WSS, src, p.stage_bytes, &ctl->full_w[s]);
-            ++wc;
-            if (++st_w >= sw_seg.st_end) { have_w = walk_w.next(p, sw_seg); st_w = sw_seg.st_begin; }
-            progressed = true;
-            PROF_ADD(pp_iters, tp);
-          }
-        }
-        if (have_b) {
-          const uint32_t s = bc % NB;
-          bool room = bc < static_cast<uint32_t>(NB);
-          if (!room) {
-            const uint32_t prev = bc - NB;   // k-block that used this stage before
-            room = mbar_test_wait(&ctl->cons[prev % NS], (prev / NS) & 1);
-          }
-          PROF_ADD(pp_idle, tp);
-          if (room) {
-#ifdef B200DQ_PROFILE
-            prof_ts_b[s] = clock64();
-#endif
-            mbar_arrive_expect_tx(&ctl->full_b[s], Ring::kBStageBytes);
-            tma_load_2d(smem_b + s * Ring::kBStageBytes, &tmap_a, kb_b * BKE, sb_seg.m_tile * TN, &ctl->full_b[s]);
-            PROF_ADD(pp_w, tp);
-            ++bc;
-            if (++kb_b >= sb_seg.st_end * 2) { have_b = walk_b.next(p, sb_seg); kb_b = sb_seg.st_begin * 2; }
-            progressed = true;
-            PROF_ADD(pp_b, tp);
-          }
-        }
-
-        if (progressed) {
-          idle = 0;
-        } else if (((++idle) & 0x3f) == 0) {
-          // bounded: give up if nothing moved for the wait limit
-          if (*abort_flag) break;
-          const uint64_t now = globaltimer_ns();
-          if (idle == 0x40) t_idle = now;
-          else if (now - t_idle > B200DQ_WAIT_LIMIT_NS) { mbar_wait_failed(abort_flag, st, 1); break; }
+      uint32_t wc = 0;   // pairs issued
+      SegmentWalk walk(p);
+      Segment w;
+      while (walk.next(p, w)) {
+        for (int sti = w.st_begin; sti < w.st_end; sti += 2, ++wc) {
+          const int n = min(2, w.st_end - sti);
+          const uint32_t s = wc % NWP;
+          mbar_wait(&ctl->empty_w[s], ((wc / NWP) & 1) ^ 1, abort_flag, st, 1);
+          const uint32_t bytes = static_cast<uint32_t>(n) * p.stage_bytes;
+          mbar_arrive_expect_tx(&ctl->full_w[s], bytes);
+          const uint8_t* src = p.wp + (static_cast<size_t>(w.n_tile) * p.st_total + sti) * p.stage_bytes;
+          tma_bulk_g2s(smem_w + s * WPS, src, bytes, &ctl->full_w[s]);
         }
       }
-#ifdef B200DQ_PROFILE
-      if (p.prof) { unsigned long long* o = p.prof + blockIdx.x * 32 + 28; o[0] = pp_w; o[1] = pp_b; o[2] = pp_idle; o[3] = pp_iters; }
-#endif
     }
-  } else if (warp >= 1 && warp <= 3) {
+  } else if (warp == 3) {
+    // ---------------- activation producer: one TMA per group of k-blocks ----
+    if (lane == 0) {
+      uint32_t gc = 0;   // groups issued
+      SegmentWalk walk(p);
+      Segment w;
+      while (walk.next(p, w)) {
+        const int kb_end = w.st_end * 2;
+        for (int kb = w.st_begin * 2; kb < kb_end; kb += gsz, ++gc) {
+          const uint32_t s = gc % NBG;
+          if constexpr (GB == 1) {
+            // one k-block per group: the MMA's `cons` commit of the k-block that used
+            // this stage before also frees the stage (no second commit per k-block)
+            if (gc >= static_cast<uint32_t>(NBG)) {
+              const uint32_t prev = gc - NBG;
+              mbar_wait(&ctl->cons[prev % NS], (prev / NS) & 1, abort_flag, st, 2);
+            }
+          } else {
+            mbar_wait(&ctl->empty_b[s], ((gc / NBG) & 1) ^ 1, abort_flag, st, 2);
+          }
+#ifdef B200DQ_PROFILE
+          prof_ts_b[s] = clock64();
+#endif
+          mbar_arrive_expect_tx(&ctl->full_b[s], static_cast<uint32_t>(gsz) * Ring::kBSlabBytes);
+          if (GB == 1 || gsz == 1)
+            tma_load_2d(smem_b + s * Ring::kBGroupBytes, &tmap_a, kb * BKE, w.m_tile * TN, &ctl->full_b[s]);
+          else
+            tma_load_3d(smem_b + s * Ring::kBGroupBytes, &tmap_a, 0, w.m_tile * TN, kb, &ctl->full_b[s]);
+        }
+      }
+    }
+  } else if (warp == 1 || warp == 2) {
     // ---------------- MMA issuers ----------------
-    // The tensor pipe queues only a couple of MMAs, so the issuer must never be
-    // away from it for long: the barriers of its next k-block are checked between
-    // the second and third MMA of the current one, and ring positions are stepped
-    // without divisions.
+    // The tensor pipe queues only a few MMAs, so the issuer must never be away from
+    // it for long: the barriers of its next k-block are checked between the second
+    // and third MMA of the current one, and ring positions are stepped without
+    // divisions. With NI = 2 the issuers take alternate k-blocks, each into its own
+    // accumulator.
     const int me = warp - 1;
     if (me < NI && lane == 0) {
       constexpr uint32_t idesc =
           kInt ? make_idesc(2u, 1u, 1u, 128u, TN) : make_idesc(1u, kBf16 ? 1u : 0u, kBf16 ? 1u : 0u, 128u, TN);
       const uint32_t acc_tmem = tmem_base + me * TN;
       const uint32_t b_base = smem_u32(smem_b);
-      // ring state of this issuer's next k-block (global k-block counter kc = me, me+NI, ...)
-      uint32_t sa = me % NS, pa = 0;   // dequantised slot and its a_full parity
-      uint32_t sb = me % NB, pb = 0;   // activation stage and its full_b parity
-      uint32_t mine = me;              // global index of this issuer's next k-block
-      uint32_t kc_seg = 0;             // global index of the segment's first k-block
+      uint32_t sa = me % NS, pa = 0;   // TMEM slot of my next k-block and its a_full parity
+      uint32_t sg = 0, pg = 0;         // ring slot of the current activation group and its full_b parity
       uint32_t tc = 0;
       bool ok = true;
       SegmentWalk walk(p);
       Segment w;
       PROF_DECL(pm_acc); PROF_DECL(pm_a); PROF_DECL(pm_b); PROF_DECL(pm_issue); PROF_DECL(pm_commit); PROF_DECL(pm_lat);
+      PROF_DECL(pm_n);
 #ifdef B200DQ_PROFILE
       long long pm_latmin = 1ll << 40;
 #endif
@@ -421,24 +416,38 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
         ok &= mbar_wait(&ctl->acc_empty, (tc & 1) ^ 1, abort_flag, st, 3);
         tc_fence_after_sync();
         PROF_ADD(pm_acc, tm);
-        const uint32_t kc_end = kc_seg + static_cast<uint32_t>(w.st_end - w.st_begin) * 2;
+        const int nkb = (w.st_end - w.st_begin) * 2;
+        // j: k-block index inside the segment; mine are j = me, me + NI, ... (segments
+        // hold an even number of k-blocks, so the global parity equals the local one)
+        int j = me;
+        int jg = 0;                     // first k-block of the current group
         bool fresh = true;
-        bool ready = false;   // barriers of k-block `mine` already passed
-        while (mine < kc_end) {
-          if (!ready) {
+        bool group_ready = false, slot_ready = false;
+        while (j < nkb) {
+          if (!group_ready) {
+            ok &= mbar_wait(&ctl->full_b[sg], pg, abort_flag, st, 5);
+            PROF_ADD(pm_b, tm);
+#ifdef B200DQ_PROFILE
+            { const long long lat = clock64() - prof_ts_b[sg]; pm_lat += lat; if (lat < pm_latmin) pm_latmin = lat; ++pm_n; }
+#endif
+            group_ready = true;
+          }
+          if (!slot_ready) {
             ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
             PROF_ADD(pm_a, tm);
-            ok &= mbar_wait(&ctl->full_b[sb], pb, abort_flag, st, 5);
-            PROF_ADD(pm_b, tm);
-            tc_fence_after_sync();
           }
+          tc_fence_after_sync();
           const uint32_t a_tmem = tmem_base + kAccCols + sa * 32;
-          const uint64_t b_desc = make_smem_desc_sw128(b_base + sb * Ring::kBStageBytes);
-          const uint32_t sa_cur = sa;
-          // advance ring state to this issuer's next k-block
-          mine += NI;
+          const uint64_t b_desc =
+              make_smem_desc_sw128(b_base + sg * Ring::kBGroupBytes + static_cast<uint32_t>(j - jg) * Ring::kBSlabBytes);
+          const uint32_t sa_cur = sa, sg_cur = sg;
+          // advance to my next k-block
+          j += NI;
           sa += NI; if (sa >= static_cast<uint32_t>(NS)) { sa -= NS; pa ^= 1; }
-          sb += NI; if (sb >= static_cast<uint32_t>(NB)) { sb -= NB; pb ^= 1; }
+          bool group_done = false;      // was that my last k-block in the group?
+          if (j >= jg + gsz || j >= nkb) {
+            group_done = true;
+          }
           if (ok) {
             if constexpr (kInt) {
               umma_ts_i8(acc_tmem, a_tmem, b_desc, idesc, fresh ? 0u : 1u);
@@ -448,18 +457,35 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
               umma_ts_f16(acc_tmem, a_tmem + 8, b_desc + 2, idesc, 1u);
             }
           }
-          ready = false;
-          if (mine < kc_end) {
+          // look ahead: the barriers of my next k-block, while the pipe works
+          slot_ready = false;
+          if (group_done) {
+            // groups between the one just used and the one holding j (only when a group
+            // is narrower than the issuer stride) are not mine: release them unused
+            jg += gsz;
+            sg += 1; if (sg >= static_cast<uint32_t>(NBG)) { sg = 0; pg ^= 1; }
+            while (GB > 1 && jg < nkb && j >= jg + gsz) {
+              ok &= mbar_wait(&ctl->full_b[sg], pg, abort_flag, st, 5);
+              mbar_arrive(&ctl->empty_b[sg]);
+              jg += gsz;
+              sg += 1; if (sg >= static_cast<uint32_t>(NBG)) { sg = 0; pg ^= 1; }
+            }
+            group_ready = false;
+          }
+          if (j < nkb) {
             PROF_ADD(pm_issue, tm);
-            ok &= mbar_wait(&ctl->full_b[sb], pb, abort_flag, st, 5);
-            PROF_ADD(pm_b, tm);
+            if (!group_ready) {
+              ok &= mbar_wait(&ctl->full_b[sg], pg, abort_flag, st, 5);
+              PROF_ADD(pm_b, tm);
 #ifdef B200DQ_PROFILE
-            { const long long lat = clock64() - prof_ts_b[sb]; pm_lat += lat; if (lat < pm_latmin) pm_latmin = lat; }
+              { const long long lat = clock64() - prof_ts_b[sg]; pm_lat += lat; if (lat < pm_latmin) pm_latmin = lat; ++pm_n; }
 #endif
+              group_ready = true;
+            }
             ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
             PROF_ADD(pm_a, tm);
             tc_fence_after_sync();
-            ready = true;
+            slot_ready = true;
           }
           if (ok) {
             if constexpr (kInt) {
@@ -473,115 +499,113 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
           fresh = false;
           PROF_ADD(pm_issue, tm);
           tc_commit(&ctl->cons[sa_cur]);
+          if (GB > 1 && group_done) tc_commit(&ctl->empty_b[sg_cur]);
           PROF_ADD(pm_commit, tm);
+        }
+        // groups of this segment that hold none of my k-blocks at its end
+        while (GB > 1 && jg < nkb) {
+          ok &= mbar_wait(&ctl->full_b[sg], pg, abort_flag, st, 5);
+          mbar_arrive(&ctl->empty_b[sg]);
+          jg += gsz;
+          sg += 1; if (sg >= static_cast<uint32_t>(NBG)) { sg = 0; pg ^= 1; }
         }
         if (!fresh) tc_commit(&ctl->acc_full);
         else mbar_arrive(&ctl->acc_full);
-        kc_seg = kc_end;
+        // TMEM slots of k-blocks that were the other issuer's: skip over them
+        // (sa already points at my next global k-block because segments are even)
         ++tc;
       }
 #ifdef B200DQ_PROFILE
-      if (p.prof && me == 0) { unsigned long long* o = p.prof + blockIdx.x * 32; o[0] = pm_acc; o[1] = pm_a; o[2] = pm_b; o[3] = pm_issue; o[4] = kc_seg; o[5] = pm_commit; o[6] = pm_lat; o[7] = pm_latmin; }
+      if (p.prof && me == 0) { unsigned long long* o = p.prof + blockIdx.x * 32; o[0] = pm_acc; o[1] = pm_a; o[2] = pm_b; o[3] = pm_issue; o[4] = pm_n; o[5] = pm_commit; o[6] = pm_lat; o[7] = pm_latmin; }
 #endif
     }
   } else if (warp >= 4 && warp < 12) {
-    // ---------------- dequant warpgroups ----------------
+    // ---------------- dequant warpgroups: group d takes stage d of every pair ----
     const int dg = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
-    uint32_t sc = 0;   // weight stages seen by this CTA
+    uint32_t wc = 0;   // weight pairs seen by this CTA
+    uint32_t kc0 = 0;  // global index of the first k-block of the current pair
     bool ok = true;
     SegmentWalk walk(p);
     Segment w;
     PROF_DECL(pd_w); PROF_DECL(pd_dec); PROF_DECL(pd_a); PROF_DECL(pd_st); PROF_DECL(pd_n);
     PROF_T0(td);
     while (walk.next(p, w)) {
-      for (int sti = w.st_begin; sti < w.st_end; ++sti, ++sc) {
-        if ((sc & 1) != static_cast<uint32_t>(dg)) continue;
-        const uint32_t sw = sc % NW;
+      for (int sti = w.st_begin; sti < w.st_end; sti += 2, ++wc) {
+        const int n = min(2, w.st_end - sti);
+        const uint32_t sw = wc % NWP;
         PROF_ADD(pd_dec, td);
-        ok &= mbar_wait(&ctl->full_w[sw], (sc / NW) & 1, abort_flag, st, 6);
+        ok &= mbar_wait(&ctl->full_w[sw], (wc / NWP) & 1, abort_flag, st, 6);
         PROF_ADD(pd_w, td);
-        const uint8_t* stage = smem_w + sw * WSS;
-        const uint4* codes = reinterpret_cast<const uint4*>(stage);
-        constexpr int CH = CPK / 2048;   // 16-byte chunks per row and k-block
-        uint4 c[2][CH];
+        const bool mine = dg < n;
+        const uint8_t* stage = smem_w + sw * WPS + dg * p.stage_bytes;
+        constexpr int CH = CPK / 2048;            // 16-byte chunks per row and k-block
+        constexpr int RPC = 32 / CH;              // TMEM columns produced by one chunk
+        if (mine) {
+          uint32_t sz0 = 0, sz1 = 0;
+          if constexpr (WF == WF_U4_SZ) {
+            const uint32_t* szp = reinterpret_cast<const uint32_t*>(stage + Ring::kCodeBytes);
+            sz0 = szp[row_in_tile];
+            sz1 = p.sz_per_kb ? szp[128 + row_in_tile] : sz0;
+          } else if constexpr (WF == WF_FP4_E8M0) {
+            sz0 = reinterpret_cast<const uint32_t*>(stage + Ring::kCodeBytes)[row_in_tile];
+          }
+          const uint4* codes = reinterpret_cast<const uint4*>(stage);
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-          for (int q = 0; q < CH; ++q) c[h][q] = codes[(h * CH + q) * 128 + row_in_tile];
-        uint32_t sz0 = 0, sz1 = 0;
-        if constexpr (WF == WF_U4_SZ) {
-          const uint32_t* szp = reinterpret_cast<const uint32_t*>(stage + Ring::kCodeBytes);
-          sz0 = szp[row_in_tile];
-          sz1 = p.sz_per_kb ? szp[128 + row_in_tile] : sz0;
-        } else if constexpr (WF == WF_FP4_E8M0) {
-          sz0 = reinterpret_cast<const uint32_t*>(stage + Ring::kCodeBytes)[row_in_tile];
-          sz1 = sz0 >> 16;
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&ctl->empty_w[sw]);
-
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const uint32_t szv = h == 0 ? sz0 : sz1;
-          uint32_t regs[32];
-#ifdef B200DQ_EXP_NODECODE
-#pragma unroll
-          for (int q = 0; q < 32; ++q) regs[q] = c[h][q & 1].x + szv + q;
-          if (true) {} else if (false) {
-#else
-          if constexpr (WF == WF_I4_I8) {
-#endif
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              decode_i4_chunk(c[h][q], p.code_bias, *reinterpret_cast<uint32_t (*)[8]>(&regs[8 * q]));
-          } else {
-            uint32_t (&lo)[16] = *reinterpret_cast<uint32_t (*)[16]>(&regs[0]);
-            uint32_t (&hi)[16] = *reinterpret_cast<uint32_t (*)[16]>(&regs[16]);
-            if constexpr (WF == WF_U4_SZ) {
-              decode_u4_chunk<kBf16>(c[h][0], szv, lo);
-              decode_u4_chunk<kBf16>(c[h][1], szv, hi);
+          for (int it = 0; it < 2 * CH; ++it) {
+            const int h = it / CH, q = it % CH;
+            const uint32_t kc = kc0 + dg * 2 + h;
+            const uint32_t sa = kc % NS;
+            const uint4 cq = codes[it * 128 + row_in_tile];
+            if (it == 2 * CH - 1) {
+              // every thread of this warp has issued its last read of the stage
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&ctl->empty_w[sw]);
+            }
+            uint32_t regs[RPC];
+            if constexpr (WF == WF_I4_I8) {
+              decode_i4_chunk(cq, p.code_bias, regs);
+            } else if constexpr (WF == WF_U4_SZ) {
+              decode_u4_chunk<kBf16>(cq, h == 0 ? sz0 : sz1, regs);
             } else if constexpr (WF == WF_U4_RAW) {
-              decode_u4_chunk_noscale<kBf16, false>(c[h][0], lo);
-              decode_u4_chunk_noscale<kBf16, false>(c[h][1], hi);
+              decode_u4_chunk_noscale<kBf16, false>(cq, regs);
             } else if constexpr (WF == WF_S4_RAW) {
-              decode_u4_chunk_noscale<kBf16, true>(c[h][0], lo);
-              decode_u4_chunk_noscale<kBf16, true>(c[h][1], hi);
+              decode_u4_chunk_noscale<kBf16, true>(cq, regs);
             } else if constexpr (WF == WF_FP4_E8M0) {
-              decode_fp4_chunk(c[h][0], 126 + static_cast<int>(szv & 0xff) - p.fp4_exp_bias, lo);
-              decode_fp4_chunk(c[h][1], 126 + static_cast<int>((szv >> 8) & 0xff) - p.fp4_exp_bias, hi);
+              decode_fp4_chunk(cq, 126 + static_cast<int>((sz0 >> (8 * it)) & 0xff) - p.fp4_exp_bias, regs);
             } else {
-              decode_i2_chunk(c[h][0], p.code_bias, lo);
-              decode_i2_chunk(c[h][1], p.code_bias, hi);
+              decode_i2_chunk(cq, p.code_bias, regs);
+            }
+            PROF_ADD(pd_dec, td);
+            if (q == 0) {
+              if (kc >= static_cast<uint32_t>(NS)) {
+                const uint32_t prev = kc - NS;
+                ok &= mbar_wait(&ctl->cons[sa], (prev / NS) & 1, abort_flag, st, 7);
+              }
+              tc_fence_after_sync();
+              PROF_ADD(pd_a, td);
+            }
+            const uint32_t dst = tmem_base + lane_addr + kAccCols + sa * 32 + q * RPC;
+            if constexpr (RPC == 16) tmem_st_32x32b_x16(dst, regs);
+            else tmem_st_32x32b_x8(dst, regs);
+            if (q == CH - 1) {
+              tc_wait_st();
+              tc_fence_before_sync();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&ctl->a_full[sa]);
+              PROF_ADD(pd_st, td);
             }
           }
-          const uint32_t kc = sc * 2 + h;
-          const uint32_t sa = kc % NS;
-          PROF_ADD(pd_dec, td);
-          if (kc >= static_cast<uint32_t>(NS)) {
-            const uint32_t prev = kc - NS;
-#ifndef B200DQ_EXP_NO_CONS
-            ok &= mbar_wait(&ctl->cons[sa], (prev / NS) & 1, abort_flag, st, 7);
-#endif
-          }
-          PROF_ADD(pd_a, td);
-          tc_fence_after_sync();
-#ifndef B200DQ_EXP_NOST
-          tmem_st_32x32b_x32(tmem_base + lane_addr + kAccCols + sa * 32, regs);
-          tc_wait_st();
-#else
-          if (regs[0] == 0x12345678u && regs[17] == 0x9abcdef0u) tmem_st_32x32b_x32(tmem_base + lane_addr + kAccCols + sa * 32, regs);
-#endif
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&ctl->a_full[sa]);
-          PROF_ADD(pd_st, td);
-        }
 #ifdef B200DQ_PROFILE
-        ++pd_n;
+          ++pd_n;
 #endif
+        } else {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&ctl->empty_w[sw]);
+        }
+        kc0 += 2 * n;
       }
     }
 #ifdef B200DQ_PROFILE
@@ -596,7 +620,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
     uint8_t* my_stage = smem_o + quarter * kStagingBytesPerWarp;
     const bool use_vec = (p.flags & GF_VEC_STORE) != 0;
     const bool plain = (p.flags & (GF_HAS_BIAS | GF_ROW_SCALE)) == 0;
-    uint32_t tc = 0, kc = 0;
+    uint32_t tc = 0;
     bool ok = true;
     SegmentWalk walk(p);
     Segment w;
@@ -606,12 +630,9 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
       const int n0_warp = w.n_tile * kTileRows + quarter * 32;
       const int n = n0_warp + lane;
       const int nkb = (w.st_end - w.st_begin) * 2;
-      // accumulators that received at least one k-block in this segment
-      uint32_t valid = 0;
-#pragma unroll
-      for (int i = 0; i < NI; ++i)
-        if (i < nkb) valid |= 1u << ((kc + i) % NI);
-      kc += nkb;
+      // every issuer has at least one k-block in every segment (segments hold >= 2)
+      const uint32_t valid = (1u << NI) - 1u;
+      (void)nkb;
       ok &= mbar_wait(&ctl->acc_full, tc & 1, abort_flag, st, 8);
       tc_fence_after_sync();
       PROF_ADD(pe_wait, te);
@@ -688,18 +709,25 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
   if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
-// Second pass of stream-K: for every tile that was cut between CTAs, add its
-// partial tiles in ascending CTA order and write the result. One block per tile,
-// one thread per weight row. Integer partials are added as integers (exact).
+// Second pass of stream-K: every tile that was cut between CTAs gets its partial
+// tiles added in ascending CTA order. blockIdx.x names the boundary between CTA b
+// and CTA b+1; the first boundary that falls strictly inside a tile owns that tile,
+// the others return at once, so only split tiles cost anything. blockIdx.y picks a
+// chunk of 32 tokens; one thread per weight row. Integer partials are added as
+// integers (exact).
 template <typename OutT, int TN, bool kIntAcc>
 __global__ void __launch_bounds__(kTileRows)
 streamk_fixup_kernel(const GemmParams p) {
-  const long long tile = blockIdx.x;
+  constexpr int TCH = TN >= 32 ? 32 : TN;   // tokens per block
+  const long long pos = static_cast<long long>(blockIdx.x + 1) * p.span;
+  if (pos >= p.units) return;
+  const long long tile = pos / p.st_total;
   const long long t_begin = tile * p.st_total;
   const long long t_end = t_begin + p.st_total;
+  if (pos == t_begin) return;                               // the cut is a tile boundary
   const int c_first = static_cast<int>(t_begin / p.span);
+  if (static_cast<int>(blockIdx.x) != c_first) return;      // an earlier cut owns this tile
   const int c_last = static_cast<int>((t_end - 1) / p.span);
-  if (c_first == c_last) return;   // whole tile done by one CTA
   const int n_tile = static_cast<int>(tile % p.n_tiles);
   const int m_tile = static_cast<int>(tile / p.n_tiles);
   const int row = threadIdx.x;
@@ -707,7 +735,10 @@ streamk_fixup_kernel(const GemmParams p) {
   if (n >= p.N) return;
   OutT* c = reinterpret_cast<OutT*>(p.c);
   const bool trans = (p.flags & GF_TRANS_C) != 0;
-  for (int j = 0; j < TN; ++j) {
+  const int j0 = blockIdx.y * TCH;
+#pragma unroll 4
+  for (int jj = 0; jj < TCH; ++jj) {
+    const int j = j0 + jj;
     const int m = m_tile * TN + j;
     if (m >= p.M) break;
     float facc = 0.f;
