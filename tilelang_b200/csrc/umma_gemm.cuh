@@ -32,8 +32,9 @@
 //   full_w/empty_w : packed weight ring, per stage      (TMA -> dequant warps)
 //   full_b         : activation ring, per k-block       (TMA -> MMA)
 //   a_full         : dequantised TMEM ring, per k-block (dequant warps -> MMA)
-//   cons           : k-block consumed by the MMA (tcgen05.commit); frees both the
-//                    TMEM slot and the activation stage
+//   cons           : a stage (two k-blocks) consumed by the MMA (tcgen05.commit);
+//                    frees its two TMEM slots (and, with one k-block per
+//                    activation group, the activation stages)
 //   acc_full/acc_empty : accumulators                   (MMA -> epilogue)
 // Every wait is bounded (ptx.cuh); a wait that gives up sets a status word.
 //
@@ -137,7 +138,7 @@ struct RingConfig {
   static constexpr int kNWPfit = (232448 - kFixed) / kWPairSmem;
   static constexpr int kNWP = kNWPfit > 8 ? 8 : kNWPfit;
   static constexpr int kSmemBytes = kFixed + kNWP * kWPairSmem;
-  static_assert(kSlots >= 8 && kSlots <= kMaxSlots, "TMEM ring depth");
+  static_assert(kSlots >= 8 && kSlots <= kMaxSlots && kSlots % 2 == 0, "TMEM ring depth");
   static_assert(kGB > 1 || (kNI == 1 && kNBG <= kSlots), "single-k-block groups reuse the cons barriers");
   static_assert(kNWP >= 1, "weight ring depth");
   static_assert(kWStageMax % 128 == 0, "stage keeps 128 B alignment");
@@ -322,7 +323,8 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
   if (threadIdx.x == 0) {
     for (int i = 0; i < NWP; ++i) { mbar_init(&ctl->full_w[i], 1); mbar_init(&ctl->empty_w[i], 8); }
     for (int i = 0; i < NBG; ++i) { mbar_init(&ctl->full_b[i], 1); mbar_init(&ctl->empty_b[i], NI); }
-    for (int i = 0; i < NS; ++i) { mbar_init(&ctl->a_full[i], 4); mbar_init(&ctl->cons[i], 1); }
+    for (int i = 0; i < NS; ++i) mbar_init(&ctl->a_full[i], 4);
+    for (int i = 0; i < NS / 2; ++i) mbar_init(&ctl->cons[i], NI);
     mbar_init(&ctl->acc_full, NI);
     mbar_init(&ctl->acc_empty, 4);
     ctl->abort_flag = 0;
@@ -371,7 +373,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
             // this stage before also frees the stage (no second commit per k-block)
             if (gc >= static_cast<uint32_t>(NBG)) {
               const uint32_t prev = gc - NBG;
-              mbar_wait(&ctl->cons[prev % NS], (prev / NS) & 1, abort_flag, st, 2);
+              mbar_wait(&ctl->cons[(prev % NS) >> 1], (prev / NS) & 1, abort_flag, st, 2);
             }
           } else {
             mbar_wait(&ctl->empty_b[s], ((gc / NBG) & 1) ^ 1, abort_flag, st, 2);
@@ -498,7 +500,9 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
           }
           fresh = false;
           PROF_ADD(pm_issue, tm);
-          tc_commit(&ctl->cons[sa_cur]);
+          // one `cons` barrier per stage (two TMEM slots): each issuer commits it after
+          // its last k-block of the stage
+          if (NI == 2 || (sa_cur & 1)) tc_commit(&ctl->cons[sa_cur >> 1]);
           if (GB > 1 && group_done) tc_commit(&ctl->empty_b[sg_cur]);
           PROF_ADD(pm_commit, tm);
         }
@@ -580,9 +584,9 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
             }
             PROF_ADD(pd_dec, td);
             if (q == 0) {
-              if (kc >= static_cast<uint32_t>(NS)) {
-                const uint32_t prev = kc - NS;
-                ok &= mbar_wait(&ctl->cons[sa], (prev / NS) & 1, abort_flag, st, 7);
+              if (h == 0 && kc >= static_cast<uint32_t>(NS)) {
+                const uint32_t prev = kc - NS;   // first k-block of the stage that used these two slots
+                ok &= mbar_wait(&ctl->cons[sa >> 1], (prev / NS) & 1, abort_flag, st, 7);
               }
               tc_fence_after_sync();
               PROF_ADD(pd_a, td);
