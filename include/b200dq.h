@@ -75,6 +75,18 @@ typedef struct b200dq_gemm_args {
   int32_t fp4_exp_bias;     /* 127: OCP e8m0 exponent bytes; 0: raw power-of-two exponents */
   int32_t token_tile;       /* 0 = choose; else 16, 32, 64, 128 or 256 tokens per CTA tile */
   int32_t max_ctas;         /* 0 = one per SM; else an upper bound on the grid */
+  /* Grouped mode (mixture of experts; num_groups = 0 for one dense GEMM). Rows of A and C
+   * are sorted by group; group g owns rows [group_row_prefix[g], group_row_prefix[g+1]) and
+   * the packed image at wp + g * group_weight_stride (all groups share N, K and format).
+   * group_tile_prefix[g] = sum over earlier groups of ceil(rows / token_tile) * ceil(N / 128);
+   * total_tiles is its last entry. Both prefix arrays are int32 device arrays of
+   * num_groups + 1 entries; M is the total number of rows. Same semantics as the grouped
+   * GEMM of examples/grouped_gemm/example_grouped_gemm_fwd.py:8-36 with dequantised weights. */
+  const int32_t* group_row_prefix;
+  const int32_t* group_tile_prefix;
+  int64_t group_weight_stride;
+  int32_t num_groups;
+  int32_t total_tiles;
 } b200dq_gemm_args;
 
 /* Replaces call(...) of the kernels generated from
@@ -110,6 +122,17 @@ size_t b200dq_packed_weight_bytes(int32_t N, int32_t K, int32_t group_size, int3
 int b200dq_pack_weights(const void* q_natural, const void* scales, const void* zeros, void* wp, int32_t N,
                         int32_t K, int32_t group_size, int32_t weight_format, int32_t act_type,
                         void* cuda_stream);
+
+/* Per-token absmax int8 quantisation of (M, K) f16/bf16 activations: scale[m] =
+ * 127 / max|x[m,:]| (max clamped at 1e-5), q = round(x * scale) clamped to [-128, 127].
+ * Replaces BitLinear.activation_quant, examples/bitnet-1.58b/utils_quant.py:156-163. */
+int b200dq_absmax_quant_int8(const void* x, void* q, float* scale, int32_t M, int32_t K, int32_t act_type,
+                             void* cuda_stream);
+
+/* out[r, c] = silu(h[r, c]) * h[r, H + c] for h of shape (rows, 2H), f16/bf16, fp32 math.
+ * The activation between the two expert GEMMs,
+ * examples/fusedmoe/example_fusedmoe_torch.py:8-23. */
+int b200dq_silu_mul(const void* h, void* out, int64_t rows, int32_t H, int32_t act_type, void* cuda_stream);
 
 /* No counterpart in the reference. The same GEMM as b200dq_gemm for callers that
  * cannot allocate device memory at all -- code running where cudaMalloc is off

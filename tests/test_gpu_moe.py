@@ -1,0 +1,81 @@
+"""GPU: grouped W4A16 GEMM, the activation kernels and the MoE layer against the oracle."""
+import numpy as np
+import pytest
+import torch
+
+import tilelang_b200 as tb
+from tilelang_b200 import moe, ops
+from oracle import ref_programs as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def gen(seed):
+    g = torch.Generator()
+    g.manual_seed(seed)
+    return g
+
+
+def experts(E, N, K, group, seed):
+    q = torch.randint(0, 256, (E, N, K // 2), generator=gen(seed), dtype=torch.uint8)
+    s = (torch.rand(E, N, K // group, generator=gen(seed + 1)) * 0.015 + 0.005).to(torch.bfloat16)
+    packed = ops.stack_packed([ops.pack_w4a16(q[e].to(DEV), s[e].to(DEV), None, N, K, group, torch.bfloat16)
+                               for e in range(E)])
+    return q, s, packed
+
+
+@pytest.mark.parametrize("counts,N,K,tile", [
+    ([300, 0, 17, 256, 1], 256, 256, 256),       # empty, ragged and exact groups
+    ([40, 90, 33], 200, 384, 128),               # N tail, K = 3 groups, 128-token tiles
+    ([5, 9, 2, 7], 128, 128, 16),
+])
+def test_grouped_w4a16_matches_per_group_oracle(counts, N, K, tile):
+    E, group = len(counts), 128
+    q, s, packed = experts(E, N, K, group, seed=3)
+    A = torch.randn(sum(counts), K, generator=gen(9)).to(torch.bfloat16)
+    out = ops.gemm_grouped(A.to(DEV), packed, counts, token_tile=tile)
+    torch.cuda.synchronize()
+    tb.check_status()
+    start = 0
+    for e, c in enumerate(counts):
+        if c:
+            ref = R.ref_w4a16(A[start:start + c], q[e], s[e], None, group, torch.bfloat16)
+            got = out[start:start + c].cpu()
+            assert R.mismatch_ratio(got, ref) <= 0.01
+            assert R.max_rel_error(got, ref) <= 1e-2
+        start += c
+
+
+def test_silu_mul_matches_fp32_reference():
+    h = torch.randn(77, 2 * 1408, generator=gen(1)).to(torch.bfloat16)
+    out = ops.silu_mul(h.to(DEV)).cpu()
+    ref = (torch.nn.functional.silu(h[:, :1408].float()) * h[:, 1408:].float()).to(torch.bfloat16)
+    # expf on the device vs the host's exp: allow one bf16 ulp
+    assert (out.float() - ref.float()).abs().max() <= 2.0 ** -7 * ref.float().abs().max()
+    assert (out != ref).float().mean() < 0.01
+
+
+@pytest.mark.parametrize("M,K,dtype", [(1, 3200, torch.bfloat16), (64, 8640, torch.bfloat16), (33, 3200, torch.float16)])
+def test_absmax_quant_int8_bit_exact(M, K, dtype):
+    x = torch.randn(M, K, generator=gen(2)).to(dtype)
+    q, s = ops.absmax_quant_int8(x.to(DEV))
+    q_ref, s_ref = R.bitnet_activation_quant(x)
+    assert torch.equal(s.cpu(), s_ref.reshape(-1))
+    assert torch.equal(q.cpu(), q_ref)
+
+
+def test_moe_layer_matches_oracle():
+    """64-expert layout scaled down: 8 experts, top-2, W1 (2F, H) and W2 (H, F), group 128,
+    fp16-range scales, zero-point 8."""
+    E, k, T, H, F, group = 8, 2, 96, 256, 128, 128
+    x = torch.randn(T, H, generator=gen(1)).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=gen(2))
+    w1_q, w1_s, w1_p = experts(E, 2 * F, H, group, seed=10)
+    w2_q, w2_s, w2_p = experts(E, H, F, group, seed=20)
+    mlp = moe.make_gpu_expert_mlp(w1_p, w2_p, token_tile=32)
+    out = moe.moe_forward(x.to(DEV), logits.to(DEV), k, E, mlp).cpu()
+    tb.check_status()
+    ref = R.ref_moe_w4a16(x, logits, k, w1_q, w1_s, w2_q, w2_s, group)
+    assert R.mismatch_ratio(out, ref) <= 0.01
+    assert R.max_rel_error(out, ref) <= 2e-2     # two chained GEMMs and a bf16 intermediate

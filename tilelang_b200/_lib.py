@@ -30,6 +30,8 @@ EXPORTED_SYMBOLS = (
     "b200dq_packed_weight_bytes",
     "b200dq_pack_weights",
     "b200dq_check_status",
+    "b200dq_absmax_quant_int8",
+    "b200dq_silu_mul",
 )
 
 
@@ -57,6 +59,11 @@ class GemmArgs(ctypes.Structure):
         ("fp4_exp_bias", ctypes.c_int32),
         ("token_tile", ctypes.c_int32),
         ("max_ctas", ctypes.c_int32),
+        ("group_row_prefix", ctypes.c_void_p),
+        ("group_tile_prefix", ctypes.c_void_p),
+        ("group_weight_stride", ctypes.c_int64),
+        ("num_groups", ctypes.c_int32),
+        ("total_tiles", ctypes.c_int32),
     ]
 
 
@@ -86,6 +93,10 @@ def _declare(lib):
     lib.b200dq_packed_weight_bytes.argtypes = [i32, i32, i32, i32]
     lib.b200dq_pack_weights.restype = ctypes.c_int
     lib.b200dq_pack_weights.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    lib.b200dq_absmax_quant_int8.restype = ctypes.c_int
+    lib.b200dq_absmax_quant_int8.argtypes = [vp, vp, vp, i32, i32, i32, vp]
+    lib.b200dq_silu_mul.restype = ctypes.c_int
+    lib.b200dq_silu_mul.argtypes = [vp, vp, ctypes.c_int64, i32, i32, vp]
     lib.b200dq_check_status.restype = ctypes.c_int
     lib.b200dq_check_status.argtypes = [vp]
 

@@ -11,9 +11,11 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <algorithm>
 #include <mutex>
 
 #include "../../include/b200dq.h"
+#include "elementwise.cuh"
 #include "pack_kernels.cuh"
 #include "umma_gemm.cuh"
 
@@ -22,7 +24,7 @@ namespace {
 using namespace b200dq;
 
 constexpr int kMaxDevices = 32;
-constexpr int kAbiVersion = 1;
+constexpr int kAbiVersion = 2;
 constexpr int kMinSpan = 8;   // fewest k-blocks worth giving a CTA of its own
 
 thread_local char g_err[1024] = "";
@@ -117,14 +119,17 @@ int stage_bytes_for(int weight_format, int group_size) {
   return 2 * codes_per_kblock_bytes(weight_format) + 512 * nsz_for(weight_format, group_size);
 }
 
-int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_ctas, int sm_count, Schedule* s) {
+int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_ctas, int sm_count, Schedule* s,
+                  long long grouped_tiles = -1) {
   s->tn = token_tile > 0 ? token_tile : token_tile_for(M);
   if (s->tn != 16 && s->tn != 32 && s->tn != 64 && s->tn != 128 && s->tn != 256)
     return fail("token_tile must be 16, 32, 64, 128 or 256 (got %d)", s->tn);
   s->m_tiles = (M + s->tn - 1) / s->tn;
   s->n_tiles = (N + kTileRows - 1) / kTileRows;
   s->st_total = stages_for(K, act_type);
-  s->units = static_cast<long long>(s->m_tiles) * s->n_tiles * s->st_total;
+  const long long tiles = grouped_tiles >= 0 ? grouped_tiles : static_cast<long long>(s->m_tiles) * s->n_tiles;
+  if (tiles <= 0) return fail("no tiles to compute");
+  s->units = tiles * s->st_total;
   int cap = sm_count;
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   long long g = s->units / kMinSpan;
@@ -258,6 +263,7 @@ size_t b200dq_gemm_workspace_bytes(int32_t M, int32_t N, int32_t K, int32_t weig
                                    int32_t token_tile, int32_t max_ctas) {
   (void)weight_format;
   Schedule s;
+  // grouped calls are bounded by the same figure: at most one CTA per SM, two slots each
   // an upper bound that does not need a device: assume at most 256 SMs
   int sm = 256;
   int dev = 0;
@@ -343,8 +349,17 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
 
   DeviceState* ds = nullptr;
   if (current_device_state(&ds) != 0) return -1;
+  const bool grouped = a->num_groups > 0;
+  if (grouped) {
+    if (a->group_row_prefix == nullptr || a->group_tile_prefix == nullptr)
+      return fail("gemm: grouped mode needs group_row_prefix and group_tile_prefix");
+    if (a->total_tiles <= 0) return fail("gemm: grouped mode needs total_tiles > 0");
+    if (a->token_tile == 0) return fail("gemm: grouped mode needs an explicit token_tile (the prefix arrays depend on it)");
+    if (a->flags & (GF_TRANS_C | GF_HAS_BIAS)) return fail("gemm: grouped mode supports neither TRANS_C nor bias");
+  }
   Schedule s;
-  if (make_schedule(a->M, a->N, a->K, act, a->token_tile, a->max_ctas, ds->sm_count, &s) != 0) return -1;
+  if (make_schedule(a->M, a->N, a->K, act, a->token_tile, a->max_ctas, ds->sm_count, &s,
+                    grouped ? a->total_tiles : -1) != 0) return -1;
   const bool needs_ws = (s.span % s.st_total != 0) && s.grid > 1;
   if (needs_ws) {
     if (a->workspace == nullptr || a->workspace_bytes < s.workspace_bytes)
@@ -377,6 +392,11 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
   p.ldc = (a->flags & GF_TRANS_C) ? a->M : a->N;
   p.flags = flags;
   p.out_type = a->out_type;
+  p.tn = s.tn;
+  p.num_groups = grouped ? a->num_groups : 0;
+  p.grp_row_prefix = grouped ? a->group_row_prefix : nullptr;
+  p.grp_tile_prefix = grouped ? a->group_tile_prefix : nullptr;
+  p.grp_w_stride = grouped ? a->group_weight_stride : 0;
   p.status = ds->status;
   p.prof = g_prof;
 
@@ -428,6 +448,7 @@ int b200dq_gemm_static_scratch(const b200dq_gemm_args* a, void* cuda_stream) {
     }
   }
   if (a->a == nullptr || a->wp == nullptr || a->c == nullptr) return fail("gemm_static_scratch: null tensor pointer");
+  if (a->num_groups > 0) return fail("gemm_static_scratch: grouped mode is not offered by this entry point");
   if (a->M <= 0 || a->N <= 0 || a->K <= 0)
     return fail("gemm_static_scratch: M, N, K must be positive (got %d, %d, %d)", a->M, a->N, a->K);
   Schedule s;
@@ -480,6 +501,7 @@ int b200dq_gemm_static_scratch(const b200dq_gemm_args* a, void* cuda_stream) {
   // kernels still bound every wait, they just have nowhere to record one that gave up
   p.status = g_dev[dev].ready ? g_dev[dev].status : nullptr;
   p.prof = nullptr;
+  p.tn = s.tn;
 
   auto stream = static_cast<cudaStream_t>(cuda_stream);
   if (wf == WF_U4_SZ && act == ACT_F16) return dispatch_tn<WF_U4_SZ, ACT_F16>(s.tn, tmap, p, s.grid, stream);
@@ -492,6 +514,42 @@ int b200dq_gemm_static_scratch(const b200dq_gemm_args* a, void* cuda_stream) {
   if (wf == WF_I2_I8) return dispatch_tn<WF_I2_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
   if (wf == WF_I4_I8) return dispatch_tn<WF_I4_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
   return fail("gemm_static_scratch: no kernel for weight format %d with activation type %d", wf, act);
+}
+
+int b200dq_absmax_quant_int8(const void* x, void* q, float* scale, int32_t M, int32_t K, int32_t act_type,
+                             void* cuda_stream) {
+  if (x == nullptr || q == nullptr || scale == nullptr) return fail("absmax_quant_int8: null pointer");
+  if (M <= 0 || K <= 0 || K % 8 != 0) return fail("absmax_quant_int8: M=%d, K=%d (K must be a positive multiple of 8)", M, K);
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(q) & 7) != 0)
+    return fail("absmax_quant_int8: x must be 16-byte and q 8-byte aligned");
+  auto stream = static_cast<cudaStream_t>(cuda_stream);
+  if (act_type == ACT_BF16)
+    absmax_quant_int8_kernel<__nv_bfloat16><<<M, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x), static_cast<int8_t*>(q), scale, K);
+  else if (act_type == ACT_F16)
+    absmax_quant_int8_kernel<__half><<<M, 256, 0, stream>>>(static_cast<const __half*>(x), static_cast<int8_t*>(q), scale, K);
+  else
+    return fail("absmax_quant_int8: input must be f16 or bf16");
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int b200dq_silu_mul(const void* h, void* out, int64_t rows, int32_t H, int32_t act_type, void* cuda_stream) {
+  if (h == nullptr || out == nullptr) return fail("silu_mul: null pointer");
+  if (rows < 0 || H <= 0 || H % 8 != 0) return fail("silu_mul: rows=%lld, H=%d (H must be a positive multiple of 8)", static_cast<long long>(rows), H);
+  if (rows == 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(h) & 15) != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0)
+    return fail("silu_mul: pointers must be 16-byte aligned");
+  auto stream = static_cast<cudaStream_t>(cuda_stream);
+  const long long total = rows * (H / 8);
+  const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
+  if (act_type == ACT_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(h), static_cast<__nv_bfloat16*>(out), rows, H);
+  else if (act_type == ACT_F16)
+    silu_mul_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half*>(h), static_cast<__half*>(out), rows, H);
+  else
+    return fail("silu_mul: input must be f16 or bf16");
+  CUDA_OK(cudaGetLastError());
+  return 0;
 }
 
 int b200dq_check_status(void* cuda_stream) {

@@ -1,0 +1,92 @@
+// Small HBM-bound kernels that sit directly in front of / between the GEMMs.
+//
+//  * absmax_quant_int8: per-token absmax int8 quantisation of the activations,
+//    the reference's BitLinear.activation_quant
+//    (examples/bitnet-1.58b/utils_quant.py:156-163): s = 127 / max|x| (max clamped
+//    at 1e-5; evaluated as reciprocal-then-multiply, as torch does for a scalar numerator), q = round(x * s) clamped to [-128, 127], round half to even as
+//    torch.round does.
+//  * silu_mul: act = silu(h[:, :H]) * h[:, H:] between the two expert GEMMs of a
+//    mixture-of-experts MLP (examples/fusedmoe/example_fusedmoe_torch.py:8-23),
+//    computed in fp32 and rounded once to the activation dtype.
+#pragma once
+#include <cstdint>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+namespace b200dq {
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// one CTA per row; K % 8 == 0; 16-byte loads
+template <typename T>
+__global__ void __launch_bounds__(256) absmax_quant_int8_kernel(const T* __restrict__ x, int8_t* __restrict__ q,
+                                                                float* __restrict__ scale, int K) {
+  const int row = blockIdx.x;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(row) * K);
+  const int nvec = K / 8;
+  float amax = 0.f;
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const uint4 v = xr[i];
+    const T* e = reinterpret_cast<const T*>(&v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(to_f32<T>(e[j])));
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+  __shared__ float warp_max[8];
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = warp_max[0];
+#pragma unroll
+  for (int w = 1; w < 8; ++w) amax = fmaxf(amax, warp_max[w]);
+  // torch evaluates `127 / t` for a Python scalar numerator as t.reciprocal() * 127
+  // (two roundings); the reference's scale is that value, so the same two steps here
+  const float s = __frcp_rn(fmaxf(amax, 1e-5f)) * 127.0f;
+  if (threadIdx.x == 0) scale[row] = s;
+  uint2* qr = reinterpret_cast<uint2*>(q + static_cast<size_t>(row) * K);
+  for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const uint4 v = xr[i];     // second read of the row comes from L2
+    const T* e = reinterpret_cast<const T*>(&v);
+    uint32_t packed[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float r = rintf(to_f32<T>(e[j]) * s);
+      r = fminf(fmaxf(r, -128.f), 127.f);
+      packed[j >> 2] |= (static_cast<uint32_t>(static_cast<int>(r)) & 0xffu) << (8 * (j & 3));
+    }
+    qr[i] = make_uint2(packed[0], packed[1]);
+  }
+}
+
+// h: (rows, 2H); out: (rows, H); H % 8 == 0
+template <typename T>
+__global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ h, T* __restrict__ out, long long rows,
+                                                       int H) {
+  const int vec_per_row = H / 8;
+  const long long total = rows * vec_per_row;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long r = idx / vec_per_row;
+    const int c = static_cast<int>(idx - r * vec_per_row);
+    const uint4 g = reinterpret_cast<const uint4*>(h + r * 2 * H)[c];
+    const uint4 u = reinterpret_cast<const uint4*>(h + r * 2 * H + H)[c];
+    const T* ge = reinterpret_cast<const T*>(&g);
+    const T* ue = reinterpret_cast<const T*>(&u);
+    uint4 o;
+    T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gv = to_f32<T>(ge[j]);
+      const float sv = gv / (1.0f + expf(-gv));
+      oe[j] = from_f32<T>(sv * to_f32<T>(ue[j]));
+    }
+    reinterpret_cast<uint4*>(out + r * H)[c] = o;
+  }
+}
+
+}  // namespace b200dq

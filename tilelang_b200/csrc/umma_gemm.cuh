@@ -99,6 +99,14 @@ struct GemmParams {
   int ldc;                   // leading dimension of the output
   int flags;
   int out_type;
+  // grouped (mixture-of-experts) mode: the rows of A and C are sorted by group,
+  // group g owns rows [grp_row_prefix[g], grp_row_prefix[g+1]) and its own packed
+  // image at wp + g * grp_w_stride; its tiles are numbered from grp_tile_prefix[g]
+  const int* grp_row_prefix;     // num_groups + 1 entries, device memory (nullptr: one dense GEMM)
+  const int* grp_tile_prefix;    // num_groups + 1 entries, device memory
+  long long grp_w_stride;
+  int num_groups;
+  int tn;                        // tokens per tile (the kernel's TN)
   DeviceStatus* status;
   unsigned long long* prof;  // optional per-CTA phase timers (profiling builds only)
 };
@@ -161,9 +169,35 @@ static_assert(sizeof(SharedCtl) <= 1024, "control block must fit its slot");
 
 // One contiguous run of weight stages inside one tile.
 struct Segment {
-  int m_tile, n_tile, st_begin, st_end;
-  int slot;   // -1: the segment is a whole tile and stores to C; else scratch slot index
+  int n_tile, st_begin, st_end;
+  int row0;      // first row of A / C of the tile
+  int row_end;   // one past the last valid row (M, or the end of the tile's group)
+  size_t wp_off; // byte offset of the tile's packed image (group) inside wp
+  int slot;      // -1: the segment is a whole tile and stores to C; else scratch slot index
 };
+
+// Tile index -> rows, weight tile and image. Dense: tiles are ordered n-fastest so
+// the CTAs working at the same time share a few token slabs (which stay in L2) and
+// stream different weight tiles. Grouped: the same inside each group, groups in order.
+__device__ __forceinline__ void locate_tile(const GemmParams& p, long long tile, Segment& s) {
+  if (p.num_groups > 0) {
+    int lo = 0, hi = p.num_groups;
+    while (hi - lo > 1) {
+      const int mid = (lo + hi) >> 1;
+      if (p.grp_tile_prefix[mid] <= tile) lo = mid; else hi = mid;
+    }
+    const int local = static_cast<int>(tile - p.grp_tile_prefix[lo]);
+    s.n_tile = local % p.n_tiles;
+    s.row0 = p.grp_row_prefix[lo] + (local / p.n_tiles) * p.tn;
+    s.row_end = p.grp_row_prefix[lo + 1];
+    s.wp_off = static_cast<size_t>(lo) * static_cast<size_t>(p.grp_w_stride);
+  } else {
+    s.n_tile = static_cast<int>(tile % p.n_tiles);
+    s.row0 = static_cast<int>(tile / p.n_tiles) * p.tn;
+    s.row_end = p.M;
+    s.wp_off = 0;
+  }
+}
 
 // Walks the segments of this CTA's span; every warp role runs the same walk.
 struct SegmentWalk {
@@ -181,10 +215,7 @@ struct SegmentWalk {
     s.st_begin = static_cast<int>(pos - tile * p.st_total);
     const long long left = end - pos;
     s.st_end = static_cast<int>(min(static_cast<long long>(p.st_total), s.st_begin + left));
-    // n fastest: the CTAs working at the same time share a few token slabs (which
-    // stay in L2) and stream different weight tiles
-    s.n_tile = static_cast<int>(tile % p.n_tiles);
-    s.m_tile = static_cast<int>(tile / p.n_tiles);
+    locate_tile(p, tile, s);
     const bool whole = (s.st_begin == 0 && s.st_end == p.st_total);
     s.slot = whole ? -1 : (static_cast<int>(blockIdx.x) * 2 + (first ? 0 : 1));
     first = false;
@@ -225,13 +256,13 @@ __device__ __forceinline__ OutT finish_value(const GemmParams& p, uint32_t raw, 
 
 // Slow path: direct, predicated global stores (unaligned pitch or transposed output).
 template <typename OutT, bool kIntAcc, int NV>
-__device__ __forceinline__ void store_values_direct(const GemmParams& p, const uint32_t* acc, int m0, int n) {
+__device__ __forceinline__ void store_values_direct(const GemmParams& p, const uint32_t* acc, int m0, int m_end, int n) {
   OutT* c = reinterpret_cast<OutT*>(p.c);
   const bool trans = (p.flags & GF_TRANS_C) != 0;
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int m = m0 + j;
-    if (m < p.M) {
+    if (m < m_end) {
       const size_t idx = trans ? static_cast<size_t>(n) * p.ldc + m : static_cast<size_t>(m) * p.ldc + n;
       c[idx] = finish_value<OutT, kIntAcc>(p, acc[j], m, n);
     }
@@ -243,7 +274,7 @@ __device__ __forceinline__ void store_values_direct(const GemmParams& p, const u
 // covering 8 (or 4) consecutive n of one output row. Needs a 16-byte aligned
 // base and row pitch; rows beyond M and 16-byte groups beyond N are skipped.
 template <typename OutT, bool kIntAcc, int NV>
-__device__ __forceinline__ void store_values_vec(const GemmParams& p, const uint32_t* acc, int m0, int n,
+__device__ __forceinline__ void store_values_vec(const GemmParams& p, const uint32_t* acc, int m0, int m_end, int n,
                                                  int n0_warp, uint8_t* sbuf, int lane, bool plain) {
   constexpr int ES = static_cast<int>(sizeof(OutT));
   constexpr int RPP = (kStagingBytesPerWarp / (32 * ES)) < NV ? (kStagingBytesPerWarp / (32 * ES)) : NV;   // rows per pass
@@ -267,7 +298,7 @@ __device__ __forceinline__ void store_values_vec(const GemmParams& p, const uint
 #pragma unroll
       for (int j = 0; j < RPP; ++j) {
         const int m = m0 + pass * RPP + j;
-        if (n_ok && m < p.M) s[j * 32 + lane] = finish_value<OutT, kIntAcc>(p, acc[pass * RPP + j], m, n);
+        if (n_ok && m < m_end) s[j * 32 + lane] = finish_value<OutT, kIntAcc>(p, acc[pass * RPP + j], m, n);
       }
     }
     __syncwarp();
@@ -277,7 +308,7 @@ __device__ __forceinline__ void store_values_vec(const GemmParams& p, const uint
     for (int it = 0; it < RPP / RPI; ++it) {
       const int r = it * RPI + lane / VPR;
       const int m = m0 + pass * RPP + r;
-      if (m < p.M && ncol < p.N) {
+      if (m < m_end && ncol < p.N) {
         const uint4 v = *reinterpret_cast<const uint4*>(sbuf + r * 32 * ES + vcol * 16);
         *reinterpret_cast<uint4*>(c + static_cast<size_t>(m) * p.ldc + ncol) = v;
       }
@@ -353,7 +384,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
           mbar_wait(&ctl->empty_w[s], ((wc / NWP) & 1) ^ 1, abort_flag, st, 1);
           const uint32_t bytes = static_cast<uint32_t>(n) * p.stage_bytes;
           mbar_arrive_expect_tx(&ctl->full_w[s], bytes);
-          const uint8_t* src = p.wp + (static_cast<size_t>(w.n_tile) * p.st_total + sti) * p.stage_bytes;
+          const uint8_t* src = p.wp + w.wp_off + (static_cast<size_t>(w.n_tile) * p.st_total + sti) * p.stage_bytes;
           tma_bulk_g2s(smem_w + s * WPS, src, bytes, &ctl->full_w[s]);
         }
       }
@@ -383,9 +414,9 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
 #endif
           mbar_arrive_expect_tx(&ctl->full_b[s], static_cast<uint32_t>(gsz) * Ring::kBSlabBytes);
           if (GB == 1 || gsz == 1)
-            tma_load_2d(smem_b + s * Ring::kBGroupBytes, &tmap_a, kb * BKE, w.m_tile * TN, &ctl->full_b[s]);
+            tma_load_2d(smem_b + s * Ring::kBGroupBytes, &tmap_a, kb * BKE, w.row0, &ctl->full_b[s]);
           else
-            tma_load_3d(smem_b + s * Ring::kBGroupBytes, &tmap_a, 0, w.m_tile * TN, kb, &ctl->full_b[s]);
+            tma_load_3d(smem_b + s * Ring::kBGroupBytes, &tmap_a, 0, w.row0, kb, &ctl->full_b[s]);
         }
       }
     }
@@ -664,27 +695,27 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
           }
         }
         PROF_ADD(pe_ld, te);
-        const int m0 = w.m_tile * TN + c * NV;
+        const int m0 = w.row0 + c * NV;
         if (w.slot >= 0) {
           // partial tile: raw accumulator values, [token][row] so lanes coalesce
           uint32_t* dst = p.partial + (static_cast<size_t>(w.slot) * TN + c * NV) * kTileRows + row_in_tile;
 #pragma unroll
           for (int j = 0; j < NV; ++j) dst[j * kTileRows] = acc[j];
         } else if (use_vec) {
-          if (m0 < p.M && n0_warp < p.N) {
+          if (m0 < w.row_end && n0_warp < p.N) {
             switch (p.out_type) {
-              case OUT_F16: store_values_vec<__half, kInt, NV>(p, acc, m0, n, n0_warp, my_stage, lane, plain); break;
-              case OUT_BF16: store_values_vec<__nv_bfloat16, kInt, NV>(p, acc, m0, n, n0_warp, my_stage, lane, plain); break;
-              case OUT_F32: store_values_vec<float, kInt, NV>(p, acc, m0, n, n0_warp, my_stage, lane, plain); break;
-              default: store_values_vec<int, kInt, NV>(p, acc, m0, n, n0_warp, my_stage, lane, plain); break;
+              case OUT_F16: store_values_vec<__half, kInt, NV>(p, acc, m0, w.row_end, n, n0_warp, my_stage, lane, plain); break;
+              case OUT_BF16: store_values_vec<__nv_bfloat16, kInt, NV>(p, acc, m0, w.row_end, n, n0_warp, my_stage, lane, plain); break;
+              case OUT_F32: store_values_vec<float, kInt, NV>(p, acc, m0, w.row_end, n, n0_warp, my_stage, lane, plain); break;
+              default: store_values_vec<int, kInt, NV>(p, acc, m0, w.row_end, n, n0_warp, my_stage, lane, plain); break;
             }
           }
         } else if (n < p.N) {
           switch (p.out_type) {
-            case OUT_F16: store_values_direct<__half, kInt, NV>(p, acc, m0, n); break;
-            case OUT_BF16: store_values_direct<__nv_bfloat16, kInt, NV>(p, acc, m0, n); break;
-            case OUT_F32: store_values_direct<float, kInt, NV>(p, acc, m0, n); break;
-            default: store_values_direct<int, kInt, NV>(p, acc, m0, n); break;
+            case OUT_F16: store_values_direct<__half, kInt, NV>(p, acc, m0, w.row_end, n); break;
+            case OUT_BF16: store_values_direct<__nv_bfloat16, kInt, NV>(p, acc, m0, w.row_end, n); break;
+            case OUT_F32: store_values_direct<float, kInt, NV>(p, acc, m0, w.row_end, n); break;
+            default: store_values_direct<int, kInt, NV>(p, acc, m0, w.row_end, n); break;
           }
         }
         PROF_ADD(pe_store, te);
@@ -732,10 +763,10 @@ streamk_fixup_kernel(const GemmParams p) {
   const int c_first = static_cast<int>(t_begin / p.span);
   if (static_cast<int>(blockIdx.x) != c_first) return;      // an earlier cut owns this tile
   const int c_last = static_cast<int>((t_end - 1) / p.span);
-  const int n_tile = static_cast<int>(tile % p.n_tiles);
-  const int m_tile = static_cast<int>(tile / p.n_tiles);
+  Segment seg;
+  locate_tile(p, tile, seg);
   const int row = threadIdx.x;
-  const int n = n_tile * kTileRows + row;
+  const int n = seg.n_tile * kTileRows + row;
   if (n >= p.N) return;
   OutT* c = reinterpret_cast<OutT*>(p.c);
   const bool trans = (p.flags & GF_TRANS_C) != 0;
@@ -743,8 +774,8 @@ streamk_fixup_kernel(const GemmParams p) {
 #pragma unroll 4
   for (int jj = 0; jj < TCH; ++jj) {
     const int j = j0 + jj;
-    const int m = m_tile * TN + j;
-    if (m >= p.M) break;
+    const int m = seg.row0 + j;
+    if (m >= seg.row_end) break;
     float facc = 0.f;
     int iacc = 0;
     for (int cta = c_first; cta <= c_last; ++cta) {

@@ -1,0 +1,119 @@
+"""Mixture-of-experts MLP on grouped W4A16 dequantize-GEMMs, single GPU and expert-parallel.
+
+The reference has no W4A16 MoE kernel; its semantics come from
+examples/fusedmoe/example_fusedmoe_torch.py (routing :26-40: softmax then
+``topk(sorted=False)``; expert MLP :8-23: ``down(silu(gate(x)) * up(x))``; dispatch by
+argsort/bincount and score-weighted combine :65-91) and from its grouped GEMM
+(examples/grouped_gemm/example_grouped_gemm_fwd.py:8-36: rows sorted by expert, one
+weight per expert). Here the two grouped GEMMs and the activation between them are this
+library's kernels; routing, the row gather and the weighted scatter-add are torch
+tensor plumbing around them.
+
+Expert parallelism: experts are split contiguously over the ranks, tokens start out
+partitioned by rank; one all-to-all sends every (token, expert) row to the rank that
+owns the expert, the local grouped GEMMs run, a second all-to-all returns the rows, and
+the token's home rank does the weighted sum. ``torch.distributed`` (NCCL over NVLink on
+GPUs, gloo in CPU tests) carries both exchanges.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+
+def route(logits: torch.Tensor, top_k: int):
+    scores = torch.softmax(logits.float(), dim=-1)
+    weights, experts = torch.topk(scores, top_k, dim=-1, sorted=False)
+    return weights, experts
+
+
+def sort_by_expert(experts: torch.Tensor, num_experts: int):
+    """Flatten (token, slot) pairs and order them by expert (stable). Returns the
+    permutation, the token of every sorted row and the per-expert counts."""
+    flat = experts.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    token_of_row = order // experts.shape[1]
+    counts = torch.bincount(flat, minlength=num_experts)
+    return order, token_of_row, counts
+
+
+class ExpertMLP:
+    """``y = W2( silu(g) * u )`` with ``[g, u] = W1(x)`` for rows sorted by expert.
+
+    ``gemm1`` / ``gemm2`` map (rows sorted by expert, per-expert counts) to outputs and
+    ``act`` maps the (rows, 2H) intermediate to (rows, H); on a GPU they are
+    ``ops.gemm_grouped`` and ``ops.silu_mul``, CPU tests inject stand-ins."""
+
+    def __init__(self, gemm1: Callable, gemm2: Callable, act: Callable):
+        self.gemm1, self.gemm2, self.act = gemm1, gemm2, act
+
+    def __call__(self, x_sorted: torch.Tensor, counts: Sequence[int]) -> torch.Tensor:
+        h = self.gemm1(x_sorted, counts)
+        return self.gemm2(self.act(h), counts)
+
+
+def make_gpu_expert_mlp(w1_packed, w2_packed, token_tile: int = 256) -> ExpertMLP:
+    from . import ops
+    return ExpertMLP(lambda x, c: ops.gemm_grouped(x, w1_packed, c, token_tile=token_tile),
+                     lambda a, c: ops.gemm_grouped(a, w2_packed, c, token_tile=token_tile),
+                     ops.silu_mul)
+
+
+def moe_forward(x: torch.Tensor, logits: torch.Tensor, top_k: int, num_experts: int, mlp: ExpertMLP) -> torch.Tensor:
+    """Single-device MoE layer: route, gather rows by expert, expert MLP, weighted combine."""
+    weights, experts = route(logits, top_k)
+    order, token_of_row, counts = sort_by_expert(experts, num_experts)
+    x_sorted = x.index_select(0, token_of_row)
+    y = mlp(x_sorted, counts.tolist())
+    w_sorted = weights.reshape(-1).index_select(0, order)
+    out = torch.zeros(x.shape[0], y.shape[1], dtype=torch.float32, device=x.device)
+    out.index_add_(0, token_of_row, y.float() * w_sorted.unsqueeze(1))
+    return out.to(x.dtype)
+
+
+def expert_ranges(num_experts: int, world_size: int) -> List[range]:
+    per = (num_experts + world_size - 1) // world_size
+    return [range(min(r * per, num_experts), min((r + 1) * per, num_experts)) for r in range(world_size)]
+
+
+def moe_forward_ep(x_local: torch.Tensor, logits_local: torch.Tensor, top_k: int, num_experts: int,
+                   local_mlp: ExpertMLP, group: Optional[dist.ProcessGroup] = None) -> torch.Tensor:
+    """Expert-parallel MoE layer. ``x_local`` are this rank's tokens; ``local_mlp`` runs this
+    rank's experts (counts are given for the local experts only, in order)."""
+    world = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    ranges = expert_ranges(num_experts, world)
+    weights, experts = route(logits_local, top_k)
+    order, token_of_row, counts = sort_by_expert(experts, num_experts)     # rows sorted by global expert id
+    x_sorted = x_local.index_select(0, token_of_row)
+
+    # rows per destination rank and the full count matrix (every rank learns what it will receive)
+    gathered = [torch.zeros_like(counts) for _ in range(world)]
+    dist.all_gather(gathered, counts, group=group)
+    all_counts = [c.cpu() for c in gathered]
+    counts_cpu = all_counts[rank]
+    send_rows = [int(counts_cpu[list(r)].sum()) if len(r) else 0 for r in ranges]
+    my = ranges[rank]
+    recv_rows = [int(c[list(my)].sum()) if len(my) else 0 for c in all_counts]
+
+    recv = x_sorted.new_empty((sum(recv_rows), x_sorted.shape[1]))
+    dist.all_to_all_single(recv, x_sorted.contiguous(), recv_rows, send_rows, group=group)
+
+    # received rows are ordered (source rank, expert); regroup them by expert for the grouped GEMM
+    src_expert = torch.cat([torch.repeat_interleave(torch.arange(len(my)), c[list(my)]) if len(my) else
+                            torch.zeros(0, dtype=torch.long) for c in all_counts]).to(recv.device)
+    regroup = torch.argsort(src_expert, stable=True)
+    local_counts = torch.stack([c[list(my)] for c in all_counts]).sum(0).tolist() if len(my) else []
+    y_grouped = local_mlp(recv.index_select(0, regroup), local_counts)
+    y = torch.empty_like(y_grouped)
+    y.index_copy_(0, regroup, y_grouped)                                   # back to (source rank, expert) order
+
+    back = y.new_empty((x_sorted.shape[0], y.shape[1]))
+    dist.all_to_all_single(back, y.contiguous(), send_rows, recv_rows, group=group)
+
+    w_sorted = weights.reshape(-1).index_select(0, order)
+    out = torch.zeros(x_local.shape[0], back.shape[1], dtype=torch.float32, device=x_local.device)
+    out.index_add_(0, token_of_row, back.float() * w_sorted.unsqueeze(1))
+    return out.to(x_local.dtype)

@@ -61,6 +61,8 @@ class PackedWeight:
     group_size: int = 0
     code_bias: int = 0
     fp4_exp_bias: int = 127
+    num_groups: int = 0          # > 0: a stack of per-group images (stack_packed)
+    group_stride: int = 0        # bytes between consecutive group images
 
     @property
     def device(self) -> torch.device:
@@ -214,6 +216,104 @@ def gemm(A: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None,
         fp4_exp_bias=w.fp4_exp_bias, token_tile=token_tile, max_ctas=max_ctas)
     with torch.cuda.device(dev):
         _lib.check(lib.b200dq_gemm(ctypes.byref(args), _stream_ptr(dev)), "b200dq_gemm")
+    return out
+
+
+def stack_packed(weights: list) -> PackedWeight:
+    """Concatenate per-group packed weights (same N, K, format) into one image; group g
+    lives at byte offset ``g * stride`` (``stride`` = size of one image)."""
+    w0 = weights[0]
+    for w in weights:
+        if (w.N, w.K, w.weight_format, w.act_type, w.group_size) != (w0.N, w0.K, w0.weight_format, w0.act_type, w0.group_size):
+            raise ValueError("all groups must share N, K, format and group size")
+    wp = torch.stack([w.wp for w in weights]).contiguous()
+    out = PackedWeight(wp.view(-1), w0.N, w0.K, w0.weight_format, w0.act_type, w0.group_size, w0.code_bias,
+                       w0.fp4_exp_bias)
+    out.num_groups = len(weights)
+    out.group_stride = w0.wp.numel()
+    return out
+
+
+def grouped_prefixes(counts, N: int, token_tile: int):
+    """Host-side row and tile prefixes of a grouped GEMM from per-group row counts."""
+    n_tiles = (N + 127) // 128
+    rows, tiles = [0], [0]
+    for c in counts:
+        rows.append(rows[-1] + int(c))
+        tiles.append(tiles[-1] + ((int(c) + token_tile - 1) // token_tile) * n_tiles)
+    return rows, tiles
+
+
+def gemm_grouped(A: torch.Tensor, w: PackedWeight, counts, out: Optional[torch.Tensor] = None,
+                 out_dtype: Optional[torch.dtype] = None, token_tile: int = 256) -> torch.Tensor:
+    """Grouped GEMM: rows of ``A`` are sorted by group, group g has ``counts[g]`` rows and
+    multiplies its own weight ``w`` (from :func:`stack_packed`). ``counts`` is a host
+    sequence (the schedule is planned on the host)."""
+    lib = _lib.load()
+    _check_cuda_contig("A", A)
+    dev = A.device
+    G = getattr(w, "num_groups", 0)
+    if G <= 0 or len(counts) != G:
+        raise ValueError(f"counts must have one entry per group ({G})")
+    M = A.shape[0]
+    rows, tiles = grouped_prefixes(counts, w.N, token_tile)
+    if rows[-1] != M:
+        raise ValueError(f"counts sum to {rows[-1]}, A has {M} rows")
+    if A.shape[1] != w.K or _ACT_OF.get(A.dtype) != w.act_type:
+        raise ValueError("A does not match the packed weights")
+    if out is None:
+        out = torch.empty((M, w.N), dtype=out_dtype or A.dtype, device=dev)
+    if M == 0 or tiles[-1] == 0:
+        return out
+    _ensure_init(dev)
+    prefix = torch.tensor(rows + tiles, dtype=torch.int32).to(dev, non_blocking=True)
+    need = lib.b200dq_gemm_workspace_bytes(M, w.N, w.K, w.weight_format, w.act_type, token_tile, 0)
+    workspace = workspace_for(dev, need)
+    args = _lib.GemmArgs(
+        a=A.data_ptr(), wp=w.wp.data_ptr(), bias=None, row_scale=None, c=out.data_ptr(),
+        workspace=workspace.data_ptr(), workspace_bytes=workspace.numel(),
+        M=M, N=w.N, K=w.K, group_size=w.group_size, weight_format=w.weight_format, act_type=w.act_type,
+        out_type=_OUT_OF[out.dtype], flags=0, tensor_scale=1.0, code_bias=w.code_bias, fp4_exp_bias=w.fp4_exp_bias,
+        token_tile=token_tile, max_ctas=0,
+        group_row_prefix=prefix.data_ptr(), group_tile_prefix=prefix.data_ptr() + 4 * (G + 1),
+        group_weight_stride=w.group_stride, num_groups=G, total_tiles=tiles[-1])
+    with torch.cuda.device(dev):
+        _lib.check(lib.b200dq_gemm(ctypes.byref(args), _stream_ptr(dev)), "b200dq_gemm (grouped)")
+    # the prefix tensor must outlive the launch that reads it
+    prefix.record_stream(torch.cuda.current_stream(dev))
+    return out
+
+
+def absmax_quant_int8(x: torch.Tensor):
+    """Per-token absmax int8 quantisation; returns (q int8 (M, K), scale fp32 (M,))."""
+    lib = _lib.load()
+    _check_cuda_contig("x", x)
+    if x.dim() != 2 or x.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("x must be a 2-D float16/bfloat16 tensor")
+    M, K = x.shape
+    q = torch.empty((M, K), dtype=torch.int8, device=x.device)
+    s = torch.empty((M,), dtype=torch.float32, device=x.device)
+    if M:
+        _ensure_init(x.device)
+        with torch.cuda.device(x.device):
+            _lib.check(lib.b200dq_absmax_quant_int8(x.data_ptr(), q.data_ptr(), s.data_ptr(), M, K, _ACT_OF[x.dtype],
+                                                    _stream_ptr(x.device)), "b200dq_absmax_quant_int8")
+    return q, s
+
+
+def silu_mul(h: torch.Tensor) -> torch.Tensor:
+    """silu(h[:, :H]) * h[:, H:] for h of shape (rows, 2H)."""
+    lib = _lib.load()
+    _check_cuda_contig("h", h)
+    if h.dim() != 2 or h.shape[1] % 2 or h.dtype not in (torch.float16, torch.bfloat16):
+        raise ValueError("h must be a 2-D float16/bfloat16 tensor with an even number of columns")
+    rows, H = h.shape[0], h.shape[1] // 2
+    out = torch.empty((rows, H), dtype=h.dtype, device=h.device)
+    if rows:
+        _ensure_init(h.device)
+        with torch.cuda.device(h.device):
+            _lib.check(lib.b200dq_silu_mul(h.data_ptr(), out.data_ptr(), rows, H, _ACT_OF[h.dtype],
+                                           _stream_ptr(h.device)), "b200dq_silu_mul")
     return out
 
 
