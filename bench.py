@@ -359,8 +359,101 @@ def run_ours(args, rank, world, local_rank):
     print(json.dumps(out))
 
 
+# ---- secondary workload: the grouped W4A16 MoE layer, expert-parallel ------------------
+MOE = dict(experts=64, top_k=6, tokens=16384, hidden=2048, ffn=1408, group=128)
+
+
+def run_moe(args, rank, world, local_rank):
+    """64 experts of W1 (2*1408, 2048) and W2 (2048, 1408), uint4 g=128, 16384 tokens, top-6.
+    Experts are split over the ranks, every rank starts with tokens/world tokens; one step
+    is route + dispatch all-to-all + two grouped GEMMs with silu_mul between + combine
+    all-to-all + weighted sum. Strong scaling: the token count is the whole job's."""
+    import torch.distributed as dist
+    from tilelang_b200 import moe, ops
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    c = MOE
+    E, H, F, g = c["experts"], c["hidden"], c["ffn"], c["group"]
+    mine = moe.expert_ranges(E, world)[rank]
+
+    def pack_experts(n, k, seed):
+        packs = []
+        for e in mine:
+            gen = torch.Generator().manual_seed(seed * 1000 + e)
+            q = torch.randint(0, 256, (n, k // 2), generator=gen, dtype=torch.uint8).to(dev)
+            sc = (torch.rand(n, k // g, generator=gen) * 0.015 + 0.005).to(torch.bfloat16).to(dev)
+            z = torch.full((n, k // g), 8.0, dtype=torch.bfloat16, device=dev)
+            packs.append(ops.pack_w4a16(q, sc, z, n, k, g, torch.bfloat16))
+        return ops.stack_packed(packs)
+
+    mlp = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1), pack_experts(H, F, 2), token_tile=256)
+    t_local = c["tokens"] // world
+    gen = torch.Generator().manual_seed(77 + rank)
+    x = torch.randn(t_local, H, generator=gen).to(torch.bfloat16).to(dev)
+    logits = torch.randn(t_local, E, generator=gen).to(dev)
+
+    def step():
+        if world == 1:
+            return moe.moe_forward(x, logits, c["top_k"], E, mlp)
+        return moe.moe_forward_ep(x, logits, c["top_k"], E, mlp)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    with ClockSampler(local_rank) as clocks:
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            out = step()
+        e1.record()
+        barrier()
+        ms_total = e0.elapsed_time(e1)
+        time.sleep(0.25)
+    ops.check_status(dev)
+
+    # the two grouped GEMMs alone, on this rank's share of evenly routed rows
+    rows = c["tokens"] * c["top_k"] // world
+    counts = [rows // len(mine)] * len(mine)
+    xs = torch.randn(sum(counts), H, device=dev).to(torch.bfloat16)
+    for _ in range(3):
+        mlp(xs, counts)
+    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize()
+    k0.record()
+    for _ in range(args.steps):
+        mlp(xs, counts)
+    k1.record()
+    torch.cuda.synchronize()
+    t = torch.tensor([ms_total, k0.elapsed_time(k1)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank != 0:
+        return
+    ms_step, ms_gemm = t[0].item() / args.steps, t[1].item() / args.steps
+    flops = 2.0 * c["tokens"] * c["top_k"] * (2 * F * H + H * F)
+    peaks = measured_peaks()
+    print(json.dumps({
+        "metric": "moe_w4a16_layer_tflops", "value": flops / ms_step / 1e9, "unit": "TFLOPS", "n_gpus": world,
+        "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "MoE W4A16: 64 experts, W1 2816x2048, W2 2048x1408, uint4 g=128, 16384 tokens, top-6",
+                   "parallelism": f"ep{world}", "l2": "working set (weights 348 MB + rows) exceeds L2"},
+        "grouped_gemms_only": {"ms": ms_gemm, "tflops": flops / ms_gemm / 1e9,
+                               "frac_of_measured_bf16": flops / ms_gemm / 1e9 / world / peaks["bf16_tflops"],
+                               "note": "W1 grouped GEMM + silu_mul + W2 grouped GEMM on evenly routed rows"},
+        "gpu_launches": 5 * args.steps * world, "clocks": clocks.summary(),
+    }))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
@@ -382,7 +475,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
     try:
-        run_ours(args, rank, world, local_rank)
+        (run_moe if args.workload == "moe" else run_ours)(args, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist

@@ -129,6 +129,18 @@ int b200dq_pack_weights(const void* q_natural, const void* scales, const void* z
 int b200dq_absmax_quant_int8(const void* x, void* q, float* scale, int32_t M, int32_t K, int32_t act_type,
                              void* cuda_stream);
 
+/* Mixture-of-experts combine: out[t, :] = sum over s < top_k of weights[t*top_k + s] *
+ * y[row_of[t*top_k + s], :], fp32 accumulation in slot order, one rounding to the row type.
+ * Deterministic stand-in for the scatter-add of
+ * examples/fusedmoe/example_fusedmoe_torch.py:83-91. H % 8 == 0. */
+int b200dq_moe_combine(const void* y, const int64_t* row_of, const float* weights, void* out, int64_t tokens,
+                       int32_t top_k, int32_t H, int32_t act_type, void* cuda_stream);
+
+/* Signed int4 values, two per byte with the even index in the low nibble (pack_int4,
+ * examples/gemm_int4/example_tilelang_gemm_int4.py:59-67) -> one int8 each. Puts packed
+ * int4 activations in front of the int8 tensor-core GEMM (tcgen05 has no int4 kind). */
+int b200dq_unpack_int4_to_int8(const void* packed, void* out, int64_t num_elems, void* cuda_stream);
+
 /* out[r, c] = silu(h[r, c]) * h[r, H + c] for h of shape (rows, 2H), f16/bf16, fp32 math.
  * The activation between the two expert GEMMs,
  * examples/fusedmoe/example_fusedmoe_torch.py:8-23. */

@@ -79,3 +79,20 @@ def test_moe_layer_matches_oracle():
     ref = R.ref_moe_w4a16(x, logits, k, w1_q, w1_s, w2_q, w2_s, group)
     assert R.mismatch_ratio(out, ref) <= 0.01
     assert R.max_rel_error(out, ref) <= 2e-2     # two chained GEMMs and a bf16 intermediate
+
+
+def test_moe_expert_parallel_two_gpus_equals_single_gpu():
+    """Experts split over two ranks with NCCL all-to-all dispatch/combine: every rank's
+    tokens must come out bit-equal to the single-GPU layer holding all experts."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import os
+    import subprocess
+    import sys
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ep_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29533", worker],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    assert res.stdout.count("EP_OK") == 2, res.stdout[-2000:]

@@ -85,9 +85,9 @@ def test_w4a16_dequant_is_bit_exact_for_fixed_zero_point():
         assert torch.equal(C, W[:, :64].T.contiguous())
 
 
-def test_w4a16_no_scale_matches_fine_grained_reference():
+@pytest.mark.parametrize("M,N,K", [(64, 256, 512), (48, 256, 352), (200, 130, 96)])   # K not a whole k-block: 2-D activation map
+def test_w4a16_no_scale_matches_fine_grained_reference(M, N, K):
     # example_dequant_gemm_fine_grained.py:125-131: C = A @ unpack(qB)^T
-    M, N, K = 64, 256, 512
     A = torch.randn(M, K, generator=gen(1)).to(torch.float16)
     qB = torch.randint(0, 256, (N, K // 2), generator=gen(2), dtype=torch.uint8)
     kernel = tb.matmul(M, N, K, "float16", "float16", "float32", num_bits=4)
@@ -256,6 +256,19 @@ def test_bitnet_decode_reference_flow():
     C = torch.zeros(M, N, dtype=torch.int32, device=DEV)
     kernel(A.to(DEV), torch.from_numpy(qw).to(DEV), C)
     assert torch.equal(C.cpu(), R.ref_bitnet_int32(A, B))
+
+
+@pytest.mark.parametrize("M,N,K", [(16, 128, 64), (1024, 1024, 1024), (100, 300, 352)])
+def test_int4_gemm_bit_exact(M, N, K):
+    # examples/gemm_int4/example_tilelang_gemm_int4.py:82-103: logical int4 in [-8, 7], rtol = atol = 0
+    A = torch.randint(-8, 8, (M, K), generator=gen(1), dtype=torch.int8)
+    B = torch.randint(-8, 8, (N, K), generator=gen(2), dtype=torch.int8)
+    A_p, B_p = torch.from_numpy(R.pack_int4(A.numpy())), torch.from_numpy(R.pack_int4(B.numpy()))
+    kernel = tb.matmul_nt_int4(M, N, K, 128, 128, 64)
+    C = kernel(A_p.to(DEV), B_p.to(DEV))
+    assert C.dtype == torch.int32 and C.shape == (M, N)
+    assert torch.equal(C.cpu(), torch.matmul(A.to(torch.int32), B.to(torch.int32).T))
+    assert torch.equal(C.cpu(), R.ref_int4_gemm(A_p, B_p))
 
 
 # ------------------------------- C ABI error paths ---------------------------

@@ -32,6 +32,8 @@ EXPORTED_SYMBOLS = (
     "b200dq_check_status",
     "b200dq_absmax_quant_int8",
     "b200dq_silu_mul",
+    "b200dq_unpack_int4_to_int8",
+    "b200dq_moe_combine",
 )
 
 
@@ -97,6 +99,10 @@ def _declare(lib):
     lib.b200dq_absmax_quant_int8.argtypes = [vp, vp, vp, i32, i32, i32, vp]
     lib.b200dq_silu_mul.restype = ctypes.c_int
     lib.b200dq_silu_mul.argtypes = [vp, vp, ctypes.c_int64, i32, i32, vp]
+    lib.b200dq_unpack_int4_to_int8.restype = ctypes.c_int
+    lib.b200dq_unpack_int4_to_int8.argtypes = [vp, vp, ctypes.c_int64, vp]
+    lib.b200dq_moe_combine.restype = ctypes.c_int
+    lib.b200dq_moe_combine.argtypes = [vp, vp, vp, vp, ctypes.c_int64, i32, i32, i32, vp]
     lib.b200dq_check_status.restype = ctypes.c_int
     lib.b200dq_check_status.argtypes = [vp]
 

@@ -533,6 +533,42 @@ int b200dq_absmax_quant_int8(const void* x, void* q, float* scale, int32_t M, in
   return 0;
 }
 
+int b200dq_moe_combine(const void* y, const int64_t* row_of, const float* weights, void* out, int64_t tokens,
+                       int32_t top_k, int32_t H, int32_t act_type, void* cuda_stream) {
+  if (y == nullptr || row_of == nullptr || weights == nullptr || out == nullptr) return fail("moe_combine: null pointer");
+  if (tokens < 0 || top_k <= 0 || H <= 0 || H % 8 != 0)
+    return fail("moe_combine: tokens=%lld, top_k=%d, H=%d (H must be a positive multiple of 8)", static_cast<long long>(tokens), top_k, H);
+  if (tokens == 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(y) & 15) != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0)
+    return fail("moe_combine: pointers must be 16-byte aligned");
+  cudaStream_t stream = static_cast<cudaStream_t>(cuda_stream);
+  const long long total = tokens * (H / 8);
+  const int blocks = static_cast<int>(std::min<long long>((total + 255) / 256, 148 * 16));
+  const long long* rows = reinterpret_cast<const long long*>(row_of);
+  if (act_type == ACT_BF16)
+    moe_combine_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(y), rows, weights, static_cast<__nv_bfloat16*>(out), tokens, top_k, H);
+  else if (act_type == ACT_F16)
+    moe_combine_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half*>(y), rows, weights, static_cast<__half*>(out), tokens, top_k, H);
+  else
+    return fail("moe_combine: rows must be f16 or bf16");
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int b200dq_unpack_int4_to_int8(const void* packed, void* out, int64_t num_elems, void* cuda_stream) {
+  if (packed == nullptr || out == nullptr) return fail("unpack_int4_to_int8: null pointer");
+  if (num_elems < 0 || num_elems % 16 != 0) return fail("unpack_int4_to_int8: element count must be a multiple of 16");
+  if (num_elems == 0) return 0;
+  if ((reinterpret_cast<uintptr_t>(packed) & 7) != 0 || (reinterpret_cast<uintptr_t>(out) & 15) != 0)
+    return fail("unpack_int4_to_int8: input must be 8-byte and output 16-byte aligned");
+  const long long nvec = num_elems / 16;
+  const int blocks = static_cast<int>(std::min<long long>((nvec + 255) / 256, 148 * 16));
+  unpack_int4_to_int8_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      static_cast<const uint2*>(packed), static_cast<uint4*>(out), nvec);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 int b200dq_silu_mul(const void* h, void* out, int64_t rows, int32_t H, int32_t act_type, void* cuda_stream) {
   if (h == nullptr || out == nullptr) return fail("silu_mul: null pointer");
   if (rows < 0 || H <= 0 || H % 8 != 0) return fail("silu_mul: rows=%lld, H=%d (H must be a positive multiple of 8)", static_cast<long long>(rows), H);

@@ -89,4 +89,59 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const T* __restrict__ h, 
   }
 }
 
+// Score-weighted combine of a mixture-of-experts layer: out[t] = sum_s w[t, s] * y[row_of[t, s]]
+// over the token's top_k expert rows, accumulated in fp32 in slot order (deterministic,
+// unlike an atomic scatter-add) and rounded once (the reference's combine,
+// examples/fusedmoe/example_fusedmoe_torch.py:83-91, is a scatter_reduce sum).
+template <typename T>
+__global__ void __launch_bounds__(256) moe_combine_kernel(const T* __restrict__ y, const long long* __restrict__ row_of,
+                                                          const float* __restrict__ w, T* __restrict__ out,
+                                                          long long tokens, int top_k, int H) {
+  const int vec_per_row = H / 8;
+  const long long total = tokens * vec_per_row;
+  for (long long idx = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; idx < total;
+       idx += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const long long t = idx / vec_per_row;
+    const int c = static_cast<int>(idx - t * vec_per_row);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int s = 0; s < top_k; ++s) {
+      const long long r = row_of[t * top_k + s];
+      const float ws = w[t * top_k + s];
+      const uint4 v = reinterpret_cast<const uint4*>(y + r * H)[c];
+      const T* ve = reinterpret_cast<const T*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(ws, to_f32<T>(ve[j]), acc[j]);
+    }
+    uint4 o;
+    T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) oe[j] = from_f32<T>(acc[j]);
+    reinterpret_cast<uint4*>(out + t * H)[c] = o;
+  }
+}
+
+// Signed int4 pairs (low nibble = even index) -> int8, 8 packed bytes per thread.
+// Feeds the int8 tensor-core path for the reference's int4 x int4 GEMM
+// (examples/gemm_int4/example_tilelang_gemm_int4.py:17-38, pack rule :59-67); tcgen05
+// has no 4-bit integer kind.
+__global__ void __launch_bounds__(256) unpack_int4_to_int8_kernel(const uint2* __restrict__ packed,
+                                                                  uint4* __restrict__ out, long long nvec) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < nvec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint2 v = packed[i];
+    const uint32_t w[2] = {v.x, v.y};
+    uint32_t o[4];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      // bytes b0..b3 of w[h] hold elements (2b, 2b+1); sign-extend each nibble
+      const uint32_t lo = w[h] & 0x0f0f0f0fu, hi = (w[h] >> 4) & 0x0f0f0f0fu;
+      const uint32_t slo = __vsub4(lo ^ 0x08080808u, 0x08080808u);   // (x ^ 8) - 8
+      const uint32_t shi = __vsub4(hi ^ 0x08080808u, 0x08080808u);
+      o[2 * h] = __byte_perm(slo, shi, 0x5140);       // e0 e1 e2 e3
+      o[2 * h + 1] = __byte_perm(slo, shi, 0x7362);   // e4 e5 e6 e7
+    }
+    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+  }
+}
+
 }  // namespace b200dq

@@ -458,6 +458,14 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
         bool group_ready = false, slot_ready = false;
         while (j < nkb) {
           if (!group_ready) {
+            // first k-block of the segment: with one-k-block groups the second issuer's
+            // k-block lies past group 0, which it releases unused
+            while (GB > 1 && j >= jg + gsz) {
+              ok &= mbar_wait(&ctl->full_b[sg], pg, abort_flag, st, 5);
+              mbar_arrive(&ctl->empty_b[sg]);
+              jg += gsz;
+              sg += 1; if (sg >= static_cast<uint32_t>(NBG)) { sg = 0; pg ^= 1; }
+            }
             ok &= mbar_wait(&ctl->full_b[sg], pg, abort_flag, st, 5);
             PROF_ADD(pm_b, tm);
 #ifdef B200DQ_PROFILE

@@ -262,6 +262,27 @@ def matmul_int8xint4(M: int, N: int, K: int, in_dtype="int8", out_dtype="int32",
     return DequantKernel("matmul_int8xint4", params, [2], impl, pack_fn, f"b200dq kind::i8 W4A8: M={M} N={N} K={K}")
 
 
+def matmul_nt_int4(M: int, N: int, K: int, block_M=None, block_N=None, block_K=None, threads=None) -> DequantKernel:
+    """``C[M, N] int32 = A @ B^T`` with both operands signed int4, two per byte
+    (examples/gemm_int4/example_tilelang_gemm_int4.py:17-38, compiled there with
+    ``out_idx=-1``; check :92-103 is ``rtol=0, atol=0``). A is unpacked to int8 by a
+    small kernel, B takes the 4-bit-weights-into-int8-MMA path."""
+    if K % 32 != 0:
+        raise ValueError("matmul_nt_int4: K must be a multiple of 32")
+    params = [Param("A", (M, K // 2), torch.int8), Param("B", (N, K // 2), torch.int8), Param("C", (M, N), torch.int32)]
+
+    def pack_fn(qB):
+        return ops.pack_int4_for_int8(qB.view(torch.uint8) ^ 0x88, N, K, code_offset=8)
+
+    def impl(kernel: DequantKernel, A, qB):
+        _check(A, params[0], any_int8=True)
+        _check(qB, params[1], any_int8=True)
+        A8 = ops.unpack_int4_to_int8(A.view(torch.uint8))
+        return ops.gemm(A8, kernel._packed(qB), out_dtype=torch.int32)
+
+    return DequantKernel("matmul_nt_int4", params, [-1], impl, pack_fn, f"b200dq kind::i8 int4 x int4: M={M} N={N} K={K}")
+
+
 # ---------------------------------------------------------------------------
 # BitNet b1.58: int8 activations x 2-bit weights -> int32
 # ---------------------------------------------------------------------------

@@ -44,21 +44,35 @@ class ExpertMLP:
 
     ``gemm1`` / ``gemm2`` map (rows sorted by expert, per-expert counts) to outputs and
     ``act`` maps the (rows, 2H) intermediate to (rows, H); on a GPU they are
-    ``ops.gemm_grouped`` and ``ops.silu_mul``, CPU tests inject stand-ins."""
+    ``ops.gemm_grouped`` and ``ops.silu_mul``, CPU tests inject stand-ins. ``combine``
+    maps (rows, (T, k) row indices, (T, k) weights) to the (T, H) weighted sums
+    (``ops.moe_combine`` on a GPU, a torch gather-and-sum otherwise)."""
 
-    def __init__(self, gemm1: Callable, gemm2: Callable, act: Callable):
+    def __init__(self, gemm1: Callable, gemm2: Callable, act: Callable, combine: Optional[Callable] = None):
         self.gemm1, self.gemm2, self.act = gemm1, gemm2, act
+        self.combine = combine or torch_combine
 
     def __call__(self, x_sorted: torch.Tensor, counts: Sequence[int]) -> torch.Tensor:
         h = self.gemm1(x_sorted, counts)
         return self.gemm2(self.act(h), counts)
 
 
+def torch_combine(y: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    return (y[row_of].float() * weights.unsqueeze(-1)).sum(1).to(y.dtype)
+
+
+def rows_of_tokens(order: torch.Tensor, top_k: int) -> torch.Tensor:
+    """(T, k) index of every (token, slot) pair's row in the expert-sorted order."""
+    inv = torch.empty_like(order)
+    inv[order] = torch.arange(order.numel(), device=order.device)
+    return inv.view(-1, top_k)
+
+
 def make_gpu_expert_mlp(w1_packed, w2_packed, token_tile: int = 256) -> ExpertMLP:
     from . import ops
     return ExpertMLP(lambda x, c: ops.gemm_grouped(x, w1_packed, c, token_tile=token_tile),
                      lambda a, c: ops.gemm_grouped(a, w2_packed, c, token_tile=token_tile),
-                     ops.silu_mul)
+                     ops.silu_mul, ops.moe_combine)
 
 
 def moe_forward(x: torch.Tensor, logits: torch.Tensor, top_k: int, num_experts: int, mlp: ExpertMLP) -> torch.Tensor:
@@ -67,10 +81,7 @@ def moe_forward(x: torch.Tensor, logits: torch.Tensor, top_k: int, num_experts: 
     order, token_of_row, counts = sort_by_expert(experts, num_experts)
     x_sorted = x.index_select(0, token_of_row)
     y = mlp(x_sorted, counts.tolist())
-    w_sorted = weights.reshape(-1).index_select(0, order)
-    out = torch.zeros(x.shape[0], y.shape[1], dtype=torch.float32, device=x.device)
-    out.index_add_(0, token_of_row, y.float() * w_sorted.unsqueeze(1))
-    return out.to(x.dtype)
+    return mlp.combine(y, rows_of_tokens(order, top_k), weights.contiguous())
 
 
 def expert_ranges(num_experts: int, world_size: int) -> List[range]:
@@ -113,7 +124,4 @@ def moe_forward_ep(x_local: torch.Tensor, logits_local: torch.Tensor, top_k: int
     back = y.new_empty((x_sorted.shape[0], y.shape[1]))
     dist.all_to_all_single(back, y.contiguous(), send_rows, recv_rows, group=group)
 
-    w_sorted = weights.reshape(-1).index_select(0, order)
-    out = torch.zeros(x_local.shape[0], back.shape[1], dtype=torch.float32, device=x_local.device)
-    out.index_add_(0, token_of_row, back.float() * w_sorted.unsqueeze(1))
-    return out.to(x_local.dtype)
+    return local_mlp.combine(back, rows_of_tokens(order, top_k), weights.contiguous())

@@ -301,6 +301,39 @@ def absmax_quant_int8(x: torch.Tensor):
     return q, s
 
 
+def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """``out[t] = sum_s weights[t, s] * y[row_of[t, s]]`` (fp32 accumulate, slot order).
+    y (rows, H) f16/bf16; row_of (T, k) int64; weights (T, k) float32."""
+    lib = _lib.load()
+    _check_cuda_contig("y", y)
+    _check_cuda_contig("row_of", row_of)
+    _check_cuda_contig("weights", weights)
+    if row_of.dtype != torch.int64 or weights.dtype != torch.float32 or row_of.shape != weights.shape:
+        raise ValueError("moe_combine: row_of must be int64 and weights float32 of the same (tokens, top_k) shape")
+    T, k = row_of.shape
+    out = torch.empty((T, y.shape[1]), dtype=y.dtype, device=y.device)
+    if T:
+        _ensure_init(y.device)
+        with torch.cuda.device(y.device):
+            _lib.check(lib.b200dq_moe_combine(y.data_ptr(), row_of.data_ptr(), weights.data_ptr(), out.data_ptr(), T, k,
+                                              y.shape[1], _ACT_OF[y.dtype], _stream_ptr(y.device)), "b200dq_moe_combine")
+    return out
+
+
+def unpack_int4_to_int8(packed: torch.Tensor) -> torch.Tensor:
+    """(M, K/2) bytes of signed int4 pairs -> (M, K) int8."""
+    lib = _lib.load()
+    _check_cuda_contig("packed", packed)
+    M, Kb = packed.shape
+    out = torch.empty((M, Kb * 2), dtype=torch.int8, device=packed.device)
+    if out.numel():
+        _ensure_init(packed.device)
+        with torch.cuda.device(packed.device):
+            _lib.check(lib.b200dq_unpack_int4_to_int8(packed.data_ptr(), out.data_ptr(), out.numel(),
+                                                      _stream_ptr(packed.device)), "b200dq_unpack_int4_to_int8")
+    return out
+
+
 def silu_mul(h: torch.Tensor) -> torch.Tensor:
     """silu(h[:, :H]) * h[:, H:] for h of shape (rows, 2H)."""
     lib = _lib.load()
