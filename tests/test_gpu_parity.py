@@ -60,6 +60,14 @@ def check_float(out, ref, strict=1e-2):
     (77, 200, 512, 128, torch.bfloat16, True),       # N tail inside a 128-row tile
     (64, 256, 1408, 128, torch.bfloat16, False),     # K = 11 groups: K padded to a whole stage
     (40, 320, 256, 256, torch.float16, True),        # one group per row (group == K)
+    # small-M kernels: SIMT GEMV (1-2 tokens) and mma.sync (3-16), split tiles, N and K tails
+    (2, 1000, 4096, 128, torch.bfloat16, True),
+    (1, 4096, 4096, 64, torch.bfloat16, True),
+    (2, 200, 1408, 128, torch.float16, False),
+    (3, 1000, 4096, 128, torch.bfloat16, True),
+    (8, 4096, 4096, 64, torch.float16, True),
+    (9, 200, 1408, 128, torch.bfloat16, False),
+    (13, 2048, 8192, 128, torch.bfloat16, True),
 ])
 def test_w4a16_grouped(M, N, K, group, dtype, zeros):
     A, qB, s, z = w4_inputs(M, N, K, group, dtype, zeros)
@@ -70,6 +78,36 @@ def test_w4a16_grouped(M, N, K, group, dtype, zeros):
     tb.check_status()
     assert C.shape == (M, N) and C.dtype == dtype
     check_float(C, R.ref_w4a16(A, qB, s, z, group, dtype))
+
+
+@pytest.mark.parametrize("M", [1, 2, 5, 16])
+def test_small_m_kernels_read_back_dequantised_weights_bit_exact(M):
+    """One-hot activation rows through the small-M kernels: the output is the dequantised
+    weight column, RN((q - 8) * s), bit for bit (every other product is an exact zero)."""
+    N, K, group = 384, 1024, 128
+    for dtype in (torch.float16, torch.bfloat16):
+        _, qB, s, _ = w4_inputs(1, N, K, group, dtype, False, seed=7)
+        cols = [3 + 67 * i for i in range(M)]
+        A = torch.zeros(M, K, dtype=dtype)
+        for i, c in enumerate(cols):
+            A[i, c] = 1.0
+        kernel = tb.matmul(M, N, K, dtype, dtype, "float32", group_size=group)
+        C = kernel(A.to(DEV), qB.to(DEV), s.to(DEV)).cpu()
+        W = R.dequant_w4_group(qB, s, None, group, dtype)
+        assert torch.equal(C, W[:, cols].T.contiguous())
+
+
+def test_small_m_kernel_agrees_with_tcgen05_kernel():
+    """The library picks the small-M kernels when the token tile is left to it; an explicit
+    tile of 16 keeps the tcgen05 kernel. Both dequantise identically, so they differ only
+    by the order of the fp32 additions."""
+    M, N, K, group = 7, 1024, 2048, 128
+    A, qB, s, z = w4_inputs(M, N, K, group, torch.bfloat16, True, seed=11)
+    pw = ops.pack_w4a16(qB.to(DEV), s.to(DEV), z.to(DEV), N, K, group, torch.bfloat16)
+    small = ops.gemm(A.to(DEV), pw, out_dtype=torch.float32)
+    umma = ops.gemm(A.to(DEV), pw, out_dtype=torch.float32, token_tile=16)
+    tb.check_status()
+    assert (small - umma).abs().max() <= 1e-4 * umma.abs().max()
 
 
 def test_w4a16_dequant_is_bit_exact_for_fixed_zero_point():

@@ -18,6 +18,7 @@
 #include "elementwise.cuh"
 #include "pack_kernels.cuh"
 #include "umma_gemm.cuh"
+#include "skinny_gemm.cuh"
 
 namespace {
 
@@ -203,7 +204,7 @@ int launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStre
   // stream-K second pass: one block column per cut between neighbouring CTAs
   if (p.span % p.st_total != 0 && grid > 1) {
     constexpr bool kInt = (ACT == ACT_I8);
-    const dim3 fgrid(grid - 1, TN >= 32 ? TN / 32 : 1);
+    const dim3 fgrid(grid - 1, TN / fixup_tokens_per_block(TN));
     switch (p.out_type) {
       case OUT_F16: streamk_fixup_kernel<__half, TN, kInt><<<fgrid, kTileRows, 0, stream>>>(p); break;
       case OUT_BF16: streamk_fixup_kernel<__nv_bfloat16, TN, kInt><<<fgrid, kTileRows, 0, stream>>>(p); break;
@@ -213,6 +214,49 @@ int launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStre
     CUDA_OK(cudaGetLastError());
   }
   return 0;
+}
+
+// Small-M path on the token-tile-16 schedule, then the same fix-up pass.
+template <typename Kernel>
+int launch_small_m(Kernel kernel, int smem_bytes, bool* attr_set, const GemmParams& p, int grid, cudaStream_t stream) {
+  if (!*attr_set) {
+    CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+    *attr_set = true;
+  }
+  kernel<<<grid, kSkinnyThreads, smem_bytes, stream>>>(p);
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+template <int WF, int ACT>
+int launch_skinny(const GemmParams& p, int grid, cudaStream_t stream) {
+  static bool attr_set[kMaxDevices][4] = {};
+  int dev = 0;
+  CUDA_OK(cudaGetDevice(&dev));
+  int rc;
+  if (p.M <= 8) rc = launch_small_m(skinny_dequant_gemm_kernel<1, WF, ACT>, kSkinnySmemBytes, &attr_set[dev][2], p, grid, stream);
+  else rc = launch_small_m(skinny_dequant_gemm_kernel<2, WF, ACT>, kSkinnySmemBytes, &attr_set[dev][3], p, grid, stream);
+  if (rc != 0) return rc;
+  if (p.span % p.st_total != 0 && grid > 1) {
+    const dim3 fgrid(grid - 1, kSkinnyTokens / fixup_tokens_per_block(kSkinnyTokens));
+    switch (p.out_type) {
+      case OUT_F16: streamk_fixup_kernel<__half, kSkinnyTokens, false><<<fgrid, kTileRows, 0, stream>>>(p); break;
+      case OUT_BF16: streamk_fixup_kernel<__nv_bfloat16, kSkinnyTokens, false><<<fgrid, kTileRows, 0, stream>>>(p); break;
+      default: streamk_fixup_kernel<float, kSkinnyTokens, false><<<fgrid, kTileRows, 0, stream>>>(p); break;
+    }
+    CUDA_OK(cudaGetLastError());
+  }
+  return 0;
+}
+
+// The small-M kernel takes dense problems of at most 16 tokens with 4-bit weights on 16-bit
+// activations when the caller leaves the token tile to the library (an explicit
+// token_tile = 16 keeps the tcgen05 kernel).
+bool takes_skinny_path(const b200dq_gemm_args* a) {
+  if (a->num_groups > 0 || a->M > kSkinnyTokens || a->token_tile != 0) return false;
+  if (a->act_type != ACT_F16 && a->act_type != ACT_BF16) return false;
+  if (a->out_type == OUT_I32) return false;
+  return a->weight_format == WF_U4_SZ || a->weight_format == WF_U4_RAW || a->weight_format == WF_S4_RAW;
 }
 
 template <int WF, int ACT>
@@ -367,9 +411,16 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
     if ((reinterpret_cast<uintptr_t>(a->workspace) & 15) != 0) return fail("gemm: workspace must be 16-byte aligned");
   }
 
+  const bool skinny = takes_skinny_path(a);
   CUtensorMap tmap;
-  const int b_group = encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn, group_kblocks_for(s.tn));
-  if (b_group < 0) return -1;
+  int b_group = 1;
+  if (skinny) {
+    if ((reinterpret_cast<uintptr_t>(a->a) & 15) != 0) return fail("activation pointer must be 16-byte aligned");
+    if (a->K % 8 != 0) return fail("activation row pitch must be a multiple of 16 bytes");
+  } else {
+    b_group = encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn, group_kblocks_for(s.tn));
+    if (b_group < 0) return -1;
+  }
   int flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
   if (output_takes_vector_stores(a->c, a->N, a->out_type, flags)) flags |= GF_VEC_STORE;
 
@@ -377,6 +428,7 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
   memset(&p, 0, sizeof(p));
   p.b_group = b_group;
   p.wp = static_cast<const uint8_t*>(a->wp);
+  p.a = a->a;
   p.c = a->c;
   p.partial = static_cast<uint32_t*>(a->workspace);
   p.bias = a->bias;
@@ -401,6 +453,14 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
   p.prof = g_prof;
 
   auto stream = static_cast<cudaStream_t>(cuda_stream);
+  if (skinny) {
+    if (wf == WF_U4_SZ && act == ACT_F16) return launch_skinny<WF_U4_SZ, ACT_F16>(p, s.grid, stream);
+    if (wf == WF_U4_SZ && act == ACT_BF16) return launch_skinny<WF_U4_SZ, ACT_BF16>(p, s.grid, stream);
+    if (wf == WF_U4_RAW && act == ACT_F16) return launch_skinny<WF_U4_RAW, ACT_F16>(p, s.grid, stream);
+    if (wf == WF_U4_RAW && act == ACT_BF16) return launch_skinny<WF_U4_RAW, ACT_BF16>(p, s.grid, stream);
+    if (wf == WF_S4_RAW && act == ACT_F16) return launch_skinny<WF_S4_RAW, ACT_F16>(p, s.grid, stream);
+    return launch_skinny<WF_S4_RAW, ACT_BF16>(p, s.grid, stream);
+  }
   if (wf == WF_U4_SZ && act == ACT_F16) return dispatch_tn<WF_U4_SZ, ACT_F16>(s.tn, tmap, p, s.grid, stream);
   if (wf == WF_U4_SZ && act == ACT_BF16) return dispatch_tn<WF_U4_SZ, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
   if (wf == WF_U4_RAW && act == ACT_F16) return dispatch_tn<WF_U4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);

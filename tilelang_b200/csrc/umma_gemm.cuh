@@ -82,6 +82,7 @@ enum GemmFlags : int {
 
 struct GemmParams {
   const uint8_t* wp;         // packed image: [n_tiles][st_total][stage_bytes]
+  const void* a;             // activations (M, K) row-major; read directly by the small-M kernel only
   void* c;                   // output
   uint32_t* partial;         // scratch: [grid][2][TN][128] raw fp32/int32 partial tiles
   const void* bias;          // optional bias [M][N]
@@ -440,7 +441,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
       SegmentWalk walk(p);
       Segment w;
       PROF_DECL(pm_acc); PROF_DECL(pm_a); PROF_DECL(pm_b); PROF_DECL(pm_issue); PROF_DECL(pm_commit); PROF_DECL(pm_lat);
-      PROF_DECL(pm_n);
+      PROF_DECL(pm_n); PROF_DECL(pm_x0); PROF_DECL(pm_x1); PROF_DECL(pm_x2);
 #ifdef B200DQ_PROFILE
       long long pm_latmin = 1ll << 40;
 #endif
@@ -477,7 +478,9 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
             ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
             PROF_ADD(pm_a, tm);
           }
+          PROF_ADD(pm_x0, tm);
           tc_fence_after_sync();
+          PROF_ADD(pm_x1, tm);
           const uint32_t a_tmem = tmem_base + kAccCols + sa * 32;
           const uint64_t b_desc =
               make_smem_desc_sw128(b_base + sg * Ring::kBGroupBytes + static_cast<uint32_t>(j - jg) * Ring::kBSlabBytes);
@@ -489,6 +492,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
           if (j >= jg + gsz || j >= nkb) {
             group_done = true;
           }
+          PROF_ADD(pm_x2, tm);
           if (ok) {
             if constexpr (kInt) {
               umma_ts_i8(acc_tmem, a_tmem, b_desc, idesc, fresh ? 0u : 1u);
@@ -559,7 +563,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
         ++tc;
       }
 #ifdef B200DQ_PROFILE
-      if (p.prof && me == 0) { unsigned long long* o = p.prof + blockIdx.x * 32; o[0] = pm_acc; o[1] = pm_a; o[2] = pm_b; o[3] = pm_issue; o[4] = pm_n; o[5] = pm_commit; o[6] = pm_lat; o[7] = pm_latmin; }
+      if (p.prof && me == 0) { unsigned long long* o = p.prof + blockIdx.x * 32; o[0] = pm_acc; o[1] = pm_a; o[2] = pm_b; o[3] = pm_issue; o[4] = pm_n; o[5] = pm_commit; o[6] = pm_lat; o[7] = pm_latmin; o[28] = pm_x0; o[29] = pm_x1; o[30] = pm_x2; }
 #endif
     }
   } else if (warp >= 4 && warp < 12) {
@@ -756,12 +760,14 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
 // tiles added in ascending CTA order. blockIdx.x names the boundary between CTA b
 // and CTA b+1; the first boundary that falls strictly inside a tile owns that tile,
 // the others return at once, so only split tiles cost anything. blockIdx.y picks a
-// chunk of 32 tokens; one thread per weight row. Integer partials are added as
-// integers (exact).
+// few tokens (so the loads of a thread are independent and the pass is not a chain of
+// L2 latencies); one thread per weight row. Integer partials are added as integers (exact).
+__host__ __device__ constexpr int fixup_tokens_per_block(int tn) { return tn >= 64 ? 8 : (tn >= 32 ? 4 : 2); }
+
 template <typename OutT, int TN, bool kIntAcc>
 __global__ void __launch_bounds__(kTileRows)
 streamk_fixup_kernel(const GemmParams p) {
-  constexpr int TCH = TN >= 32 ? 32 : TN;   // tokens per block
+  constexpr int TCH = fixup_tokens_per_block(TN);
   const long long pos = static_cast<long long>(blockIdx.x + 1) * p.span;
   if (pos >= p.units) return;
   const long long tile = pos / p.st_total;
@@ -775,30 +781,38 @@ streamk_fixup_kernel(const GemmParams p) {
   locate_tile(p, tile, seg);
   const int row = threadIdx.x;
   const int n = seg.n_tile * kTileRows + row;
-  if (n >= p.N) return;
+  const int j0 = blockIdx.y * TCH;
+  if (n >= p.N || seg.row0 + j0 >= seg.row_end) return;
+  float facc[TCH];
+  int iacc[TCH];
+#pragma unroll
+  for (int jj = 0; jj < TCH; ++jj) { facc[jj] = 0.f; iacc[jj] = 0; }
+  for (int cta = c_first; cta <= c_last; ++cta) {
+    // slot 0 if this tile holds the first segment of that CTA's span, else slot 1
+    const long long span_begin = static_cast<long long>(cta) * p.span;
+    const int slot = cta * 2 + ((span_begin >= t_begin) ? 0 : 1);
+    const uint32_t* src = p.partial + (static_cast<size_t>(slot) * TN + j0) * kTileRows + row;
+    uint32_t raw[TCH];
+#pragma unroll
+    for (int jj = 0; jj < TCH; ++jj) raw[jj] = src[jj * kTileRows];
+#pragma unroll
+    for (int jj = 0; jj < TCH; ++jj) {
+      if constexpr (kIntAcc) iacc[jj] += static_cast<int>(raw[jj]);
+      else facc[jj] += __uint_as_float(raw[jj]);
+    }
+  }
   OutT* c = reinterpret_cast<OutT*>(p.c);
   const bool trans = (p.flags & GF_TRANS_C) != 0;
-  const int j0 = blockIdx.y * TCH;
-#pragma unroll 4
+#pragma unroll
   for (int jj = 0; jj < TCH; ++jj) {
-    const int j = j0 + jj;
-    const int m = seg.row0 + j;
-    if (m >= seg.row_end) break;
-    float facc = 0.f;
-    int iacc = 0;
-    for (int cta = c_first; cta <= c_last; ++cta) {
-      // slot 0 if this tile holds the first segment of that CTA's span, else slot 1
-      const long long span_begin = static_cast<long long>(cta) * p.span;
-      const int slot = cta * 2 + ((span_begin >= t_begin) ? 0 : 1);
-      const uint32_t raw = p.partial[(static_cast<size_t>(slot) * TN + j) * kTileRows + row];
-      if constexpr (kIntAcc) iacc += static_cast<int>(raw);
-      else facc += __uint_as_float(raw);
+    const int m = seg.row0 + j0 + jj;
+    if (m < seg.row_end) {
+      uint32_t bits;
+      if constexpr (kIntAcc) bits = static_cast<uint32_t>(iacc[jj]);
+      else bits = __float_as_uint(facc[jj]);
+      const size_t idx = trans ? static_cast<size_t>(n) * p.ldc + m : static_cast<size_t>(m) * p.ldc + n;
+      c[idx] = finish_value<OutT, kIntAcc>(p, bits, m, n);
     }
-    uint32_t bits;
-    if constexpr (kIntAcc) bits = static_cast<uint32_t>(iacc);
-    else bits = __float_as_uint(facc);
-    const size_t idx = trans ? static_cast<size_t>(n) * p.ldc + m : static_cast<size_t>(m) * p.ldc + n;
-    c[idx] = finish_value<OutT, kIntAcc>(p, bits, m, n);
   }
 }
 
