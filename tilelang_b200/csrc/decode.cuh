@@ -8,8 +8,10 @@
 // examples/dequantize_gemm/quantize/lop3.py (decode_i4u_to_f16 :6-39, the
 // scale/zeros variants :41-176, decode_i2s_to_i8s / decode_i4s_to_i8s :893-1047)
 // and quantize/mxfp.py:6-49 (fp4 -> bf16 by mask/shift then * 2^126). The
-// reference has fp16 LOP3 decoders only; the bf16 ones here use the same idea
-// with the magic exponent of 128.0 (bf16 has 7 mantissa bits, so 128 + q is exact).
+// reference has fp16 LOP3 decoders only. Here the scaled uint4 decoders read the
+// masked code as a 16-bit subnormal (see decode_u4_chunk); the unscaled ones use the
+// magic-exponent trick (0x6400 | q = 1024 + q in fp16, 0x4300 | q = 128 + q in bf16,
+// which has 7 mantissa bits, so 128 + q is exact).
 //
 // Offline layouts expected in each 32-bit word (produced by pack_weight):
 //   u4 -> 16 bit : element e at bit (e % 2) * 16 + (e / 2) * 4        (8 per word)

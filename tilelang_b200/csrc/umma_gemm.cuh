@@ -413,7 +413,11 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
 #ifdef B200DQ_PROFILE
           prof_ts_b[s] = clock64();
 #endif
+#ifdef B200DQ_EXP_HALF_B
+          mbar_arrive_expect_tx(&ctl->full_b[s], static_cast<uint32_t>(gsz) * Ring::kBSlabBytes / 2);
+#else
           mbar_arrive_expect_tx(&ctl->full_b[s], static_cast<uint32_t>(gsz) * Ring::kBSlabBytes);
+#endif
           if (GB == 1 || gsz == 1)
             tma_load_2d(smem_b + s * Ring::kBGroupBytes, &tmap_a, kb * BKE, w.row0, &ctl->full_b[s]);
           else
