@@ -163,6 +163,7 @@ struct SharedCtl {
   uint64_t cons[kMaxSlots];
   uint64_t acc_full;
   uint64_t acc_empty;
+  uint64_t turn[2];   // TN = 256: the two issuers hand the shared accumulator back and forth
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -359,6 +360,8 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
     for (int i = 0; i < NS / 2; ++i) mbar_init(&ctl->cons[i], NI);
     mbar_init(&ctl->acc_full, NI);
     mbar_init(&ctl->acc_empty, 4);
+    mbar_init(&ctl->turn[0], 1);
+    mbar_init(&ctl->turn[1], 1);
     ctl->abort_flag = 0;
     mbar_fence_init();
   }
@@ -433,7 +436,66 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
     // divisions. With NI = 2 the issuers take alternate k-blocks, each into its own
     // accumulator.
     const int me = warp - 1;
-    if (me < NI && lane == 0) {
+    if constexpr (TN >= 256) {
+      // One accumulator fills all the TMEM the operand ring leaves free, so both issuers
+      // feed the same one and take alternate *stages* (two k-blocks, eight MMAs). While one
+      // issues, the other is already through the waits, the commit and the loop round trip
+      // of its next stage, which a single thread cannot fit under the few MMAs the pipe
+      // queues. `turn` orders the two threads' MMAs: the issuer of stage g arrives on the
+      // other's barrier after its last MMA (fence before, fence after on the waiting side).
+      if (lane == 0) {
+        constexpr uint32_t idesc =
+            kInt ? make_idesc(2u, 1u, 1u, 128u, TN) : make_idesc(1u, kBf16 ? 1u : 0u, kBf16 ? 1u : 0u, 128u, TN);
+        static_assert(GB == 1 && NI == 1, "stage ping-pong assumes one k-block per activation group");
+        const uint32_t acc_tmem = tmem_base;
+        const uint32_t b_base = smem_u32(smem_b);
+        uint32_t g = 0;        // stages seen by this CTA (both issuers count all of them)
+        uint32_t tc = 0;       // segments seen
+        uint32_t my_turns = 0; // waits done on turn[me]
+        bool ok = true;
+        SegmentWalk walk(p);
+        Segment w;
+        while (walk.next(p, w)) {
+          const int nst = w.st_end - w.st_begin;
+          for (int i = 0; i < nst; ++i, ++g) {
+            if ((g & 1u) != static_cast<uint32_t>(me)) continue;
+            const uint32_t kc = 2u * g;                  // first k-block of the stage
+            const uint32_t sa = kc % NS;                 // TMEM slots sa, sa + 1 (NS is even)
+            const uint32_t pa = (kc / NS) & 1u;
+            const uint32_t sb0 = kc % NBG, sb1 = (kc + 1u) % NBG;
+            const uint32_t pb0 = (kc / NBG) & 1u, pb1 = ((kc + 1u) / NBG) & 1u;
+            ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
+            ok &= mbar_wait(&ctl->full_b[sb0], pb0, abort_flag, st, 5);
+            ok &= mbar_wait(&ctl->a_full[sa + 1], pa, abort_flag, st, 4);
+            ok &= mbar_wait(&ctl->full_b[sb1], pb1, abort_flag, st, 5);
+            if (i == 0) ok &= mbar_wait(&ctl->acc_empty, (tc & 1u) ^ 1u, abort_flag, st, 3);
+            if (g > 0) {
+              ok &= mbar_wait(&ctl->turn[me], my_turns & 1u, abort_flag, st, 9);
+              ++my_turns;
+            }
+            tc_fence_after_sync();
+            if (ok) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h) {
+                const uint32_t a_tmem = tmem_base + kAccCols + (sa + h) * 32;
+                const uint64_t b_desc = make_smem_desc_sw128(b_base + (h == 0 ? sb0 : sb1) * Ring::kBGroupBytes);
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                  const uint32_t accum = (i == 0 && h == 0 && m == 0) ? 0u : 1u;
+                  if constexpr (kInt) umma_ts_i8(acc_tmem, a_tmem + 8 * m, b_desc + 2 * m, idesc, accum);
+                  else umma_ts_f16(acc_tmem, a_tmem + 8 * m, b_desc + 2 * m, idesc, accum);
+                }
+              }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&ctl->turn[me ^ 1]);
+            tc_commit(&ctl->cons[sa >> 1]);
+            if (i == nst - 1) tc_commit(&ctl->acc_full);
+          }
+          ++tc;
+        }
+      }
+    } else if (me < NI && lane == 0) {
       constexpr uint32_t idesc =
           kInt ? make_idesc(2u, 1u, 1u, 128u, TN) : make_idesc(1u, kBf16 ? 1u : 0u, kBf16 ? 1u : 0u, 128u, TN);
       const uint32_t acc_tmem = tmem_base + me * TN;
