@@ -127,7 +127,7 @@ __host__ __device__ constexpr int sz_smem_bytes(int wf) { return wf == WF_U4_SZ 
 // Shared memory: an activation ring of kNBG groups (one TMA each, kGB k-blocks), a
 // weight ring of kNWP slots holding a *pair* of packed stages (one bulk copy
 // each), and 4 KiB of epilogue staging per epilogue warp.
-__host__ __device__ constexpr int issuers_for(int tn) { return tn >= 256 ? 1 : 2; }
+__host__ __device__ constexpr int issuers_for(int) { return 1; }   // accumulators per tile
 __host__ __device__ constexpr int group_kblocks_for(int tn) { return tn >= 256 ? 1 : (tn >= 128 ? 2 : 4); }
 
 template <int TN, int WF>
@@ -163,7 +163,7 @@ struct SharedCtl {
   uint64_t cons[kMaxSlots];
   uint64_t acc_full;
   uint64_t acc_empty;
-  uint64_t turn[2];   // TN = 256: the two issuers hand the shared accumulator back and forth
+  uint64_t turn[2];   // the two issuers hand the shared accumulator back and forth
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -355,7 +355,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < NWP; ++i) { mbar_init(&ctl->full_w[i], 1); mbar_init(&ctl->empty_w[i], 8); }
-    for (int i = 0; i < NBG; ++i) { mbar_init(&ctl->full_b[i], 1); mbar_init(&ctl->empty_b[i], NI); }
+    for (int i = 0; i < NBG; ++i) { mbar_init(&ctl->full_b[i], 1); mbar_init(&ctl->empty_b[i], gsz == 4 ? 2 : 1); }
     for (int i = 0; i < NS; ++i) mbar_init(&ctl->a_full[i], 4);
     for (int i = 0; i < NS / 2; ++i) mbar_init(&ctl->cons[i], NI);
     mbar_init(&ctl->acc_full, NI);
@@ -430,207 +430,77 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
     }
   } else if (warp == 1 || warp == 2) {
     // ---------------- MMA issuers ----------------
-    // The tensor pipe queues only a few MMAs, so the issuer must never be away from
-    // it for long: the barriers of its next k-block are checked between the second
-    // and third MMA of the current one, and ring positions are stepped without
-    // divisions. With NI = 2 the issuers take alternate k-blocks, each into its own
-    // accumulator.
+    // Both issuers feed the one accumulator and take alternate *stages* (two k-blocks,
+    // eight MMAs). While one issues, the other is already through the waits, the commits
+    // and the loop round trip of its next stage; a single thread cannot fit those under the
+    // few MMAs the tensor pipe queues (measured: 1085 -> 1381 TFLOP/s at 4096 tokens).
+    // `turn` orders the two threads' MMAs: the issuer of stage g arrives on the other's
+    // barrier after its last MMA (fence before the arrive, fence after the wait).
     const int me = warp - 1;
-    if constexpr (TN >= 256) {
-      // One accumulator fills all the TMEM the operand ring leaves free, so both issuers
-      // feed the same one and take alternate *stages* (two k-blocks, eight MMAs). While one
-      // issues, the other is already through the waits, the commit and the loop round trip
-      // of its next stage, which a single thread cannot fit under the few MMAs the pipe
-      // queues. `turn` orders the two threads' MMAs: the issuer of stage g arrives on the
-      // other's barrier after its last MMA (fence before, fence after on the waiting side).
-      if (lane == 0) {
-        constexpr uint32_t idesc =
-            kInt ? make_idesc(2u, 1u, 1u, 128u, TN) : make_idesc(1u, kBf16 ? 1u : 0u, kBf16 ? 1u : 0u, 128u, TN);
-        static_assert(GB == 1 && NI == 1, "stage ping-pong assumes one k-block per activation group");
-        const uint32_t acc_tmem = tmem_base;
-        const uint32_t b_base = smem_u32(smem_b);
-        uint32_t g = 0;        // stages seen by this CTA (both issuers count all of them)
-        uint32_t tc = 0;       // segments seen
-        uint32_t my_turns = 0; // waits done on turn[me]
-        bool ok = true;
-        SegmentWalk walk(p);
-        Segment w;
-        while (walk.next(p, w)) {
-          const int nst = w.st_end - w.st_begin;
-          for (int i = 0; i < nst; ++i, ++g) {
-            if ((g & 1u) != static_cast<uint32_t>(me)) continue;
-            const uint32_t kc = 2u * g;                  // first k-block of the stage
-            const uint32_t sa = kc % NS;                 // TMEM slots sa, sa + 1 (NS is even)
-            const uint32_t pa = (kc / NS) & 1u;
-            const uint32_t sb0 = kc % NBG, sb1 = (kc + 1u) % NBG;
-            const uint32_t pb0 = (kc / NBG) & 1u, pb1 = ((kc + 1u) / NBG) & 1u;
-            ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
-            ok &= mbar_wait(&ctl->full_b[sb0], pb0, abort_flag, st, 5);
-            ok &= mbar_wait(&ctl->a_full[sa + 1], pa, abort_flag, st, 4);
-            ok &= mbar_wait(&ctl->full_b[sb1], pb1, abort_flag, st, 5);
-            if (i == 0) ok &= mbar_wait(&ctl->acc_empty, (tc & 1u) ^ 1u, abort_flag, st, 3);
-            if (g > 0) {
-              ok &= mbar_wait(&ctl->turn[me], my_turns & 1u, abort_flag, st, 9);
-              ++my_turns;
-            }
-            tc_fence_after_sync();
-            if (ok) {
-#pragma unroll
-              for (int h = 0; h < 2; ++h) {
-                const uint32_t a_tmem = tmem_base + kAccCols + (sa + h) * 32;
-                const uint64_t b_desc = make_smem_desc_sw128(b_base + (h == 0 ? sb0 : sb1) * Ring::kBGroupBytes);
-#pragma unroll
-                for (int m = 0; m < 4; ++m) {
-                  const uint32_t accum = (i == 0 && h == 0 && m == 0) ? 0u : 1u;
-                  if constexpr (kInt) umma_ts_i8(acc_tmem, a_tmem + 8 * m, b_desc + 2 * m, idesc, accum);
-                  else umma_ts_f16(acc_tmem, a_tmem + 8 * m, b_desc + 2 * m, idesc, accum);
-                }
-              }
-            }
-            tc_fence_before_sync();
-            mbar_arrive(&ctl->turn[me ^ 1]);
-            tc_commit(&ctl->cons[sa >> 1]);
-            if (i == nst - 1) tc_commit(&ctl->acc_full);
-          }
-          ++tc;
-        }
-      }
-    } else if (me < NI && lane == 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc =
           kInt ? make_idesc(2u, 1u, 1u, 128u, TN) : make_idesc(1u, kBf16 ? 1u : 0u, kBf16 ? 1u : 0u, 128u, TN);
-      const uint32_t acc_tmem = tmem_base + me * TN;
+      static_assert(NI == 1, "one accumulator");
+      const uint32_t acc_tmem = tmem_base;
       const uint32_t b_base = smem_u32(smem_b);
-      uint32_t sa = me % NS, pa = 0;   // TMEM slot of my next k-block and its a_full parity
-      uint32_t sg = 0, pg = 0;         // ring slot of the current activation group and its full_b parity
-      uint32_t tc = 0;
+      uint32_t g = 0;         // stages seen by this CTA (both issuers count all of them)
+      uint32_t gc0 = 0;       // activation groups issued before this segment
+      uint32_t tc = 0;        // segments seen
+      uint32_t my_turns = 0;  // waits done on turn[me]
       bool ok = true;
       SegmentWalk walk(p);
       Segment w;
-      PROF_DECL(pm_acc); PROF_DECL(pm_a); PROF_DECL(pm_b); PROF_DECL(pm_issue); PROF_DECL(pm_commit); PROF_DECL(pm_lat);
-      PROF_DECL(pm_n); PROF_DECL(pm_x0); PROF_DECL(pm_x1); PROF_DECL(pm_x2);
-#ifdef B200DQ_PROFILE
-      long long pm_latmin = 1ll << 40;
-#endif
-      PROF_T0(tm);
       while (walk.next(p, w)) {
-        ok &= mbar_wait(&ctl->acc_empty, (tc & 1) ^ 1, abort_flag, st, 3);
-        tc_fence_after_sync();
-        PROF_ADD(pm_acc, tm);
-        const int nkb = (w.st_end - w.st_begin) * 2;
-        // j: k-block index inside the segment; mine are j = me, me + NI, ... (segments
-        // hold an even number of k-blocks, so the global parity equals the local one)
-        int j = me;
-        int jg = 0;                     // first k-block of the current group
-        bool fresh = true;
-        bool group_ready = false, slot_ready = false;
-        while (j < nkb) {
-          if (!group_ready) {
-            // first k-block of the segment: with one-k-block groups the second issuer's
-            // k-block lies past group 0, which it releases unused
-            while (GB > 1 && j >= jg + gsz) {
-              ok &= mbar_wait(&ctl->full_b[sg], pg, abort_flag, st, 5);
-              mbar_arrive(&ctl->empty_b[sg]);
-              jg += gsz;
-              sg += 1; if (sg >= static_cast<uint32_t>(NBG)) { sg = 0; pg ^= 1; }
-            }
-            ok &= mbar_wait(&ctl->full_b[sg], pg, abort_flag, st, 5);
-            PROF_ADD(pm_b, tm);
-#ifdef B200DQ_PROFILE
-            { const long long lat = clock64() - prof_ts_b[sg]; pm_lat += lat; if (lat < pm_latmin) pm_latmin = lat; ++pm_n; }
-#endif
-            group_ready = true;
+        const int nst = w.st_end - w.st_begin;
+        for (int i = 0; i < nst; ++i, ++g) {
+          if ((g & 1u) != static_cast<uint32_t>(me)) continue;
+          const uint32_t kc = 2u * g;                  // first k-block of the stage
+          const uint32_t sa = kc % NS;                 // TMEM slots sa, sa + 1 (NS is even)
+          const uint32_t pa = (kc / NS) & 1u;
+          // activation groups of the stage's two k-blocks (segment-relative k-blocks 2i, 2i + 1)
+          const uint32_t grp0 = gc0 + static_cast<uint32_t>(2 * i) / static_cast<uint32_t>(gsz);
+          const uint32_t grp1 = gc0 + static_cast<uint32_t>(2 * i + 1) / static_cast<uint32_t>(gsz);
+          const uint32_t sb0 = grp0 % NBG, sb1 = grp1 % NBG;
+          ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
+          ok &= mbar_wait(&ctl->full_b[sb0], (grp0 / NBG) & 1u, abort_flag, st, 5);
+          ok &= mbar_wait(&ctl->a_full[sa + 1], pa, abort_flag, st, 4);
+          if (grp1 != grp0) ok &= mbar_wait(&ctl->full_b[sb1], (grp1 / NBG) & 1u, abort_flag, st, 5);
+          if (i == 0) ok &= mbar_wait(&ctl->acc_empty, (tc & 1u) ^ 1u, abort_flag, st, 3);
+          if (g > 0) {
+            ok &= mbar_wait(&ctl->turn[me], my_turns & 1u, abort_flag, st, 9);
+            ++my_turns;
           }
-          if (!slot_ready) {
-            ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
-            PROF_ADD(pm_a, tm);
-          }
-          PROF_ADD(pm_x0, tm);
           tc_fence_after_sync();
-          PROF_ADD(pm_x1, tm);
-          const uint32_t a_tmem = tmem_base + kAccCols + sa * 32;
-          const uint64_t b_desc =
-              make_smem_desc_sw128(b_base + sg * Ring::kBGroupBytes + static_cast<uint32_t>(j - jg) * Ring::kBSlabBytes);
-          const uint32_t sa_cur = sa, sg_cur = sg;
-          // advance to my next k-block
-          j += NI;
-          sa += NI; if (sa >= static_cast<uint32_t>(NS)) { sa -= NS; pa ^= 1; }
-          bool group_done = false;      // was that my last k-block in the group?
-          if (j >= jg + gsz || j >= nkb) {
-            group_done = true;
-          }
-          PROF_ADD(pm_x2, tm);
           if (ok) {
-            if constexpr (kInt) {
-              umma_ts_i8(acc_tmem, a_tmem, b_desc, idesc, fresh ? 0u : 1u);
-              umma_ts_i8(acc_tmem, a_tmem + 8, b_desc + 2, idesc, 1u);
-            } else {
-              umma_ts_f16(acc_tmem, a_tmem, b_desc, idesc, fresh ? 0u : 1u);
-              umma_ts_f16(acc_tmem, a_tmem + 8, b_desc + 2, idesc, 1u);
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+              const uint32_t a_tmem = tmem_base + kAccCols + (sa + h) * 32;
+              const uint32_t slab = static_cast<uint32_t>(2 * i + h) % static_cast<uint32_t>(gsz);
+              const uint64_t b_desc = make_smem_desc_sw128(b_base + (h == 0 ? sb0 : sb1) * Ring::kBGroupBytes +
+                                                           slab * Ring::kBSlabBytes);
+#pragma unroll
+              for (int m = 0; m < 4; ++m) {
+                const uint32_t accum = (i == 0 && h == 0 && m == 0) ? 0u : 1u;
+                if constexpr (kInt) umma_ts_i8(acc_tmem, a_tmem + 8 * m, b_desc + 2 * m, idesc, accum);
+                else umma_ts_f16(acc_tmem, a_tmem + 8 * m, b_desc + 2 * m, idesc, accum);
+              }
             }
           }
-          // look ahead: the barriers of my next k-block, while the pipe works
-          slot_ready = false;
-          if (group_done) {
-            // groups between the one just used and the one holding j (only when a group
-            // is narrower than the issuer stride) are not mine: release them unused
-            jg += gsz;
-            sg += 1; if (sg >= static_cast<uint32_t>(NBG)) { sg = 0; pg ^= 1; }
-            while (GB > 1 && jg < nkb && j >= jg + gsz) {
-              ok &= mbar_wait(&ctl->full_b[sg], pg, abort_flag, st, 5);
-              mbar_arrive(&ctl->empty_b[sg]);
-              jg += gsz;
-              sg += 1; if (sg >= static_cast<uint32_t>(NBG)) { sg = 0; pg ^= 1; }
-            }
-            group_ready = false;
+          tc_fence_before_sync();
+          mbar_arrive(&ctl->turn[me ^ 1]);
+          tc_commit(&ctl->cons[sa >> 1]);
+          if constexpr (GB > 1) {
+            // hand the activation groups back: a group of four k-blocks serves two stages and
+            // takes one arrival from each (or both from this one when the segment ends here)
+            tc_commit(&ctl->empty_b[sb0]);
+            if (grp1 != grp0) tc_commit(&ctl->empty_b[sb1]);
+            if (gsz == 4 && (i & 1) == 0 && i == nst - 1) mbar_arrive(&ctl->empty_b[sb0]);
           }
-          if (j < nkb) {
-            PROF_ADD(pm_issue, tm);
-            if (!group_ready) {
-              ok &= mbar_wait(&ctl->full_b[sg], pg, abort_flag, st, 5);
-              PROF_ADD(pm_b, tm);
-#ifdef B200DQ_PROFILE
-              { const long long lat = clock64() - prof_ts_b[sg]; pm_lat += lat; if (lat < pm_latmin) pm_latmin = lat; ++pm_n; }
-#endif
-              group_ready = true;
-            }
-            ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
-            PROF_ADD(pm_a, tm);
-            tc_fence_after_sync();
-            slot_ready = true;
-          }
-          if (ok) {
-            if constexpr (kInt) {
-              umma_ts_i8(acc_tmem, a_tmem + 16, b_desc + 4, idesc, 1u);
-              umma_ts_i8(acc_tmem, a_tmem + 24, b_desc + 6, idesc, 1u);
-            } else {
-              umma_ts_f16(acc_tmem, a_tmem + 16, b_desc + 4, idesc, 1u);
-              umma_ts_f16(acc_tmem, a_tmem + 24, b_desc + 6, idesc, 1u);
-            }
-          }
-          fresh = false;
-          PROF_ADD(pm_issue, tm);
-          // one `cons` barrier per stage (two TMEM slots): each issuer commits it after
-          // its last k-block of the stage
-          if (NI == 2 || (sa_cur & 1)) tc_commit(&ctl->cons[sa_cur >> 1]);
-          if (GB > 1 && group_done) tc_commit(&ctl->empty_b[sg_cur]);
-          PROF_ADD(pm_commit, tm);
+          if (i == nst - 1) tc_commit(&ctl->acc_full);
         }
-        // groups of this segment that hold none of my k-blocks at its end
-        while (GB > 1 && jg < nkb) {
-          ok &= mbar_wait(&ctl->full_b[sg], pg, abort_flag, st, 5);
-          mbar_arrive(&ctl->empty_b[sg]);
-          jg += gsz;
-          sg += 1; if (sg >= static_cast<uint32_t>(NBG)) { sg = 0; pg ^= 1; }
-        }
-        if (!fresh) tc_commit(&ctl->acc_full);
-        else mbar_arrive(&ctl->acc_full);
-        // TMEM slots of k-blocks that were the other issuer's: skip over them
-        // (sa already points at my next global k-block because segments are even)
+        gc0 += (static_cast<uint32_t>(2 * nst) + static_cast<uint32_t>(gsz) - 1u) / static_cast<uint32_t>(gsz);
         ++tc;
       }
-#ifdef B200DQ_PROFILE
-      if (p.prof && me == 0) { unsigned long long* o = p.prof + blockIdx.x * 32; o[0] = pm_acc; o[1] = pm_a; o[2] = pm_b; o[3] = pm_issue; o[4] = pm_n; o[5] = pm_commit; o[6] = pm_lat; o[7] = pm_latmin; o[28] = pm_x0; o[29] = pm_x1; o[30] = pm_x2; }
-#endif
     }
   } else if (warp >= 4 && warp < 12) {
     // ---------------- dequant warpgroups: group d takes stage d of every pair ----
