@@ -443,39 +443,51 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
       static_assert(NI == 1, "one accumulator");
       const uint32_t acc_tmem = tmem_base;
       const uint32_t b_base = smem_u32(smem_b);
-      uint32_t g = 0;         // stages seen by this CTA (both issuers count all of them)
+      uint32_t g0 = 0;        // stages of this CTA before the current segment (both issuers count all)
       uint32_t gc0 = 0;       // activation groups issued before this segment
       uint32_t tc = 0;        // segments seen
       uint32_t my_turns = 0;  // waits done on turn[me]
+      // ring position of my next stage's first k-block (k-block 2 * stage): +4 per own stage
+      uint32_t sa = (2u * static_cast<uint32_t>(me)) % NS, pa = 0;
+      const uint32_t gshift = gsz == 4 ? 2u : (gsz == 2 ? 1u : 0u);   // gsz is 1, 2 or 4
+      const uint32_t gmask = static_cast<uint32_t>(gsz) - 1u;
       bool ok = true;
       SegmentWalk walk(p);
       Segment w;
+      PROF_DECL(pm_loop); PROF_DECL(pm_a); PROF_DECL(pm_b); PROF_DECL(pm_acc); PROF_DECL(pm_turn); PROF_DECL(pm_issue);
+      PROF_DECL(pm_commit); PROF_DECL(pm_n);
+      PROF_T0(tm);
       while (walk.next(p, w)) {
         const int nst = w.st_end - w.st_begin;
-        for (int i = 0; i < nst; ++i, ++g) {
-          if ((g & 1u) != static_cast<uint32_t>(me)) continue;
-          const uint32_t kc = 2u * g;                  // first k-block of the stage
-          const uint32_t sa = kc % NS;                 // TMEM slots sa, sa + 1 (NS is even)
-          const uint32_t pa = (kc / NS) & 1u;
+        // my stages of the segment: those whose CTA-wide index g0 + i has my parity
+        for (int i = static_cast<int>((static_cast<uint32_t>(me) ^ g0) & 1u); i < nst; i += 2) {
+          const bool first_ever = (g0 + static_cast<uint32_t>(i)) == 0u;
           // activation groups of the stage's two k-blocks (segment-relative k-blocks 2i, 2i + 1)
-          const uint32_t grp0 = gc0 + static_cast<uint32_t>(2 * i) / static_cast<uint32_t>(gsz);
-          const uint32_t grp1 = gc0 + static_cast<uint32_t>(2 * i + 1) / static_cast<uint32_t>(gsz);
+          const uint32_t grp0 = gc0 + (static_cast<uint32_t>(2 * i) >> gshift);
+          const uint32_t grp1 = gc0 + (static_cast<uint32_t>(2 * i + 1) >> gshift);
           const uint32_t sb0 = grp0 % NBG, sb1 = grp1 % NBG;
+          PROF_ADD(pm_loop, tm);
           ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
+          PROF_ADD(pm_a, tm);
           ok &= mbar_wait(&ctl->full_b[sb0], (grp0 / NBG) & 1u, abort_flag, st, 5);
+          PROF_ADD(pm_b, tm);
           ok &= mbar_wait(&ctl->a_full[sa + 1], pa, abort_flag, st, 4);
+          PROF_ADD(pm_a, tm);
           if (grp1 != grp0) ok &= mbar_wait(&ctl->full_b[sb1], (grp1 / NBG) & 1u, abort_flag, st, 5);
+          PROF_ADD(pm_b, tm);
           if (i == 0) ok &= mbar_wait(&ctl->acc_empty, (tc & 1u) ^ 1u, abort_flag, st, 3);
-          if (g > 0) {
+          PROF_ADD(pm_acc, tm);
+          if (!first_ever) {
             ok &= mbar_wait(&ctl->turn[me], my_turns & 1u, abort_flag, st, 9);
             ++my_turns;
           }
+          PROF_ADD(pm_turn, tm);
           tc_fence_after_sync();
           if (ok) {
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
               const uint32_t a_tmem = tmem_base + kAccCols + (sa + h) * 32;
-              const uint32_t slab = static_cast<uint32_t>(2 * i + h) % static_cast<uint32_t>(gsz);
+              const uint32_t slab = static_cast<uint32_t>(2 * i + h) & gmask;
               const uint64_t b_desc = make_smem_desc_sw128(b_base + (h == 0 ? sb0 : sb1) * Ring::kBGroupBytes +
                                                            slab * Ring::kBSlabBytes);
 #pragma unroll
@@ -486,6 +498,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
               }
             }
           }
+          PROF_ADD(pm_issue, tm);
           tc_fence_before_sync();
           mbar_arrive(&ctl->turn[me ^ 1]);
           tc_commit(&ctl->cons[sa >> 1]);
@@ -497,10 +510,19 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
             if (gsz == 4 && (i & 1) == 0 && i == nst - 1) mbar_arrive(&ctl->empty_b[sb0]);
           }
           if (i == nst - 1) tc_commit(&ctl->acc_full);
+          PROF_ADD(pm_commit, tm);
+#ifdef B200DQ_PROFILE
+          ++pm_n;
+#endif
+          sa += 4; if (sa >= static_cast<uint32_t>(NS)) { sa -= NS; pa ^= 1u; }
         }
-        gc0 += (static_cast<uint32_t>(2 * nst) + static_cast<uint32_t>(gsz) - 1u) / static_cast<uint32_t>(gsz);
+        g0 += static_cast<uint32_t>(nst);
+        gc0 += (static_cast<uint32_t>(2 * nst) + gmask) >> gshift;
         ++tc;
       }
+#ifdef B200DQ_PROFILE
+      if (p.prof && me == 0) { unsigned long long* o = p.prof + blockIdx.x * 32; o[0] = pm_acc; o[1] = pm_a; o[2] = pm_b; o[3] = pm_issue; o[4] = pm_n; o[5] = pm_commit; o[6] = pm_turn; o[7] = pm_loop; }
+#endif
     }
   } else if (warp >= 4 && warp < 12) {
     // ---------------- dequant warpgroups: group d takes stage d of every pair ----
