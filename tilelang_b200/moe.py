@@ -100,23 +100,25 @@ def moe_forward_ep(x_local: torch.Tensor, logits_local: torch.Tensor, top_k: int
     order, token_of_row, counts = sort_by_expert(experts, num_experts)     # rows sorted by global expert id
     x_sorted = x_local.index_select(0, token_of_row)
 
-    # rows per destination rank and the full count matrix (every rank learns what it will receive)
-    gathered = [torch.zeros_like(counts) for _ in range(world)]
-    dist.all_gather(gathered, counts, group=group)
-    all_counts = [c.cpu() for c in gathered]
-    counts_cpu = all_counts[rank]
-    send_rows = [int(counts_cpu[list(r)].sum()) if len(r) else 0 for r in ranges]
+    # the full count matrix (every rank learns what it will receive): one collective, one sync
+    flat_counts = counts.new_empty(world * num_experts)
+    dist.all_gather_into_tensor(flat_counts, counts.contiguous(), group=group)
+    all_counts_dev = flat_counts.view(world, num_experts)
+    all_counts = all_counts_dev.cpu()                                       # (world, E)
     my = ranges[rank]
-    recv_rows = [int(c[list(my)].sum()) if len(my) else 0 for c in all_counts]
+    send_rows = [int(all_counts[rank, r.start:r.stop].sum()) if len(r) else 0 for r in ranges]
+    mine = all_counts[:, my.start:my.stop] if len(my) else all_counts[:, :0]   # (world, local experts)
+    recv_rows = mine.sum(1).tolist()
 
     recv = x_sorted.new_empty((sum(recv_rows), x_sorted.shape[1]))
     dist.all_to_all_single(recv, x_sorted.contiguous(), recv_rows, send_rows, group=group)
 
     # received rows are ordered (source rank, expert); regroup them by expert for the grouped GEMM
-    src_expert = torch.cat([torch.repeat_interleave(torch.arange(len(my)), c[list(my)]) if len(my) else
-                            torch.zeros(0, dtype=torch.long) for c in all_counts]).to(recv.device)
+    local_ids = torch.arange(len(my), device=recv.device).repeat(world)
+    src_expert = torch.repeat_interleave(local_ids, all_counts_dev[:, my.start:my.stop].reshape(-1),
+                                         output_size=sum(recv_rows))
     regroup = torch.argsort(src_expert, stable=True)
-    local_counts = torch.stack([c[list(my)] for c in all_counts]).sum(0).tolist() if len(my) else []
+    local_counts = mine.sum(0).tolist()
     y_grouped = local_mlp(recv.index_select(0, regroup), local_counts)
     y = torch.empty_like(y_grouped)
     y.index_copy_(0, regroup, y_grouped)                                   # back to (source rank, expert) order
