@@ -19,23 +19,24 @@
 // swizzle) from a TMA-filled shared-memory ring. Accumulators (fp32 or int32)
 // live in TMEM columns [0, 256).
 //
-//   warp 0      : producer: packed weights (cp.async.bulk, one stage = 2 k-blocks
-//                 of codes + their scale words) and activations (tiled TMA)
-//   warps 1-3   : MMA issuers (one elected lane each); warp 1 owns TMEM.
-//                 A single thread issues one tcgen05.mma per ~45 cycles, so for
-//                 narrow token tiles NI = 2 or 3 issuers take k-blocks round-robin,
-//                 each into its own accumulator; the epilogue adds them.
+//   warp 0      : weight producer (cp.async.bulk, one copy per pair of packed stages;
+//                 a stage = 2 k-blocks of codes + their scale words)
+//   warp 3      : activation producer (tiled TMA, one load per group of 1, 2 or 4 k-blocks)
+//   warps 1-2   : MMA issuers (one elected lane each); warp 1 owns TMEM. They take
+//                 alternate stages into the one accumulator, ordered by `turn`.
 //   warps 4-11  : two dequant warpgroups, alternating weight stages
 //   warps 12-15 : epilogue (tcgen05.ld -> convert -> smem transpose -> 16-byte stores)
 //
 // k-block = 64 16-bit (128 8-bit) K elements = one 128 B swizzle atom of activations.
-//   full_w/empty_w : packed weight ring, per stage      (TMA -> dequant warps)
-//   full_b         : activation ring, per k-block       (TMA -> MMA)
-//   a_full         : dequantised TMEM ring, per k-block (dequant warps -> MMA)
+//   full_w/empty_w : packed weight ring, per pair of stages (TMA -> dequant warps)
+//   full_b/empty_b : activation ring, per group             (TMA -> MMA)
+//   a_full         : dequantised TMEM ring, per stage, on the barrier of the stage's
+//                    first slot                              (dequant warps -> MMA)
 //   cons           : a stage (two k-blocks) consumed by the MMA (tcgen05.commit);
 //                    frees its two TMEM slots (and, with one k-block per
 //                    activation group, the activation stages)
-//   acc_full/acc_empty : accumulators                   (MMA -> epilogue)
+//   turn           : hands the accumulator from the issuer of one stage to the other
+//   acc_full/acc_empty : accumulator                        (MMA -> epilogue)
 // Every wait is bounded (ptx.cuh); a wait that gives up sets a status word.
 //
 // Scheduling is stream-K: the (tile, stage) space is cut into equal contiguous
@@ -127,7 +128,9 @@ __host__ __device__ constexpr int sz_smem_bytes(int wf) { return wf == WF_U4_SZ 
 // Shared memory: an activation ring of kNBG groups (one TMA each, kGB k-blocks), a
 // weight ring of kNWP slots holding a *pair* of packed stages (one bulk copy
 // each), and 4 KiB of epilogue staging per epilogue warp.
-__host__ __device__ constexpr int issuers_for(int) { return 1; }   // accumulators per tile
+// accumulators per tile: narrow token tiles give each issuer its own (the epilogue adds
+// them), so the two issue streams do not have to take turns
+__host__ __device__ constexpr int issuers_for(int tn) { return tn <= 128 ? 2 : 1; }
 __host__ __device__ constexpr int group_kblocks_for(int tn) { return tn >= 256 ? 1 : (tn >= 128 ? 2 : 4); }
 
 template <int TN, int WF>
@@ -149,6 +152,7 @@ struct RingConfig {
   static constexpr int kSmemBytes = kFixed + kNWP * kWPairSmem;
   static_assert(kSlots >= 8 && kSlots <= kMaxSlots && kSlots % 2 == 0, "TMEM ring depth");
   static_assert(kGB > 1 || (kNI == 1 && kNBG <= kSlots), "single-k-block groups reuse the cons barriers");
+  static_assert(kGB != 2 || 2 * kNBG <= kSlots, "two-k-block groups reuse the cons barriers");
   static_assert(kNWP >= 1, "weight ring depth");
   static_assert(kWStageMax % 128 == 0, "stage keeps 128 B alignment");
   static_assert(kSmemBytes <= 232448, "over the 227 KiB shared-memory limit");
@@ -357,7 +361,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
     for (int i = 0; i < NWP; ++i) { mbar_init(&ctl->full_w[i], 1); mbar_init(&ctl->empty_w[i], 8); }
     for (int i = 0; i < NBG; ++i) { mbar_init(&ctl->full_b[i], 1); mbar_init(&ctl->empty_b[i], gsz == 4 ? 2 : 1); }
     for (int i = 0; i < NS; ++i) mbar_init(&ctl->a_full[i], 4);
-    for (int i = 0; i < NS / 2; ++i) mbar_init(&ctl->cons[i], NI);
+    for (int i = 0; i < NS / 2; ++i) mbar_init(&ctl->cons[i], 1);
     mbar_init(&ctl->acc_full, NI);
     mbar_init(&ctl->acc_empty, 4);
     mbar_init(&ctl->turn[0], 1);
@@ -403,12 +407,13 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
         const int kb_end = w.st_end * 2;
         for (int kb = w.st_begin * 2; kb < kb_end; kb += gsz, ++gc) {
           const uint32_t s = gc % NBG;
-          if constexpr (GB == 1) {
-            // one k-block per group: the MMA's `cons` commit of the k-block that used
-            // this stage before also frees the stage (no second commit per k-block)
+          if (GB == 1 || (GB == 2 && gsz == 2)) {
+            // groups that lie inside one stage (one or two k-blocks): the MMA's `cons`
+            // commit of the stage that used this slot before also frees the slot (no second
+            // commit); prev_kb = first k-block of that group in CTA-wide counting
             if (gc >= static_cast<uint32_t>(NBG)) {
-              const uint32_t prev = gc - NBG;
-              mbar_wait(&ctl->cons[(prev % NS) >> 1], (prev / NS) & 1, abort_flag, st, 2);
+              const uint32_t prev_kb = (gc - NBG) * static_cast<uint32_t>(GB);
+              mbar_wait(&ctl->cons[(prev_kb % NS) >> 1], (prev_kb / NS) & 1, abort_flag, st, 2);
             }
           } else {
             mbar_wait(&ctl->empty_b[s], ((gc / NBG) & 1) ^ 1, abort_flag, st, 2);
@@ -440,8 +445,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
     if (lane == 0) {
       constexpr uint32_t idesc =
           kInt ? make_idesc(2u, 1u, 1u, 128u, TN) : make_idesc(1u, kBf16 ? 1u : 0u, kBf16 ? 1u : 0u, 128u, TN);
-      static_assert(NI == 1, "one accumulator");
-      const uint32_t acc_tmem = tmem_base;
+      const uint32_t acc_tmem = tmem_base + (NI == 2 ? static_cast<uint32_t>(me) * TN : 0u);
       const uint32_t b_base = smem_u32(smem_b);
       uint32_t g0 = 0;        // stages of this CTA before the current segment (both issuers count all)
       uint32_t gc0 = 0;       // activation groups issued before this segment
@@ -471,13 +475,11 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
           PROF_ADD(pm_a, tm);
           ok &= mbar_wait(&ctl->full_b[sb0], (grp0 / NBG) & 1u, abort_flag, st, 5);
           PROF_ADD(pm_b, tm);
-          ok &= mbar_wait(&ctl->a_full[sa + 1], pa, abort_flag, st, 4);
-          PROF_ADD(pm_a, tm);
           if (grp1 != grp0) ok &= mbar_wait(&ctl->full_b[sb1], (grp1 / NBG) & 1u, abort_flag, st, 5);
           PROF_ADD(pm_b, tm);
-          if (i == 0) ok &= mbar_wait(&ctl->acc_empty, (tc & 1u) ^ 1u, abort_flag, st, 3);
+          if (i < NI) ok &= mbar_wait(&ctl->acc_empty, (tc & 1u) ^ 1u, abort_flag, st, 3);   // my first stage here
           PROF_ADD(pm_acc, tm);
-          if (!first_ever) {
+          if (NI == 1 && !first_ever) {
             ok &= mbar_wait(&ctl->turn[me], my_turns & 1u, abort_flag, st, 9);
             ++my_turns;
           }
@@ -492,29 +494,38 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
                                                            slab * Ring::kBSlabBytes);
 #pragma unroll
               for (int m = 0; m < 4; ++m) {
-                const uint32_t accum = (i == 0 && h == 0 && m == 0) ? 0u : 1u;
+                const uint32_t accum = (i < NI && h == 0 && m == 0) ? 0u : 1u;   // first MMA into this accumulator
                 if constexpr (kInt) umma_ts_i8(acc_tmem, a_tmem + 8 * m, b_desc + 2 * m, idesc, accum);
                 else umma_ts_f16(acc_tmem, a_tmem + 8 * m, b_desc + 2 * m, idesc, accum);
               }
             }
           }
           PROF_ADD(pm_issue, tm);
-          tc_fence_before_sync();
-          mbar_arrive(&ctl->turn[me ^ 1]);
+          if constexpr (NI == 1) {
+            tc_fence_before_sync();
+            mbar_arrive(&ctl->turn[me ^ 1]);
+          }
           tc_commit(&ctl->cons[sa >> 1]);
-          if constexpr (GB > 1) {
-            // hand the activation groups back: a group of four k-blocks serves two stages and
+          if (GB > 1 && !(GB == 2 && gsz == 2)) {
+            // hand the activation groups back (two-k-block groups ride on `cons`): a group of four k-blocks serves two stages and
             // takes one arrival from each (or both from this one when the segment ends here)
             tc_commit(&ctl->empty_b[sb0]);
             if (grp1 != grp0) tc_commit(&ctl->empty_b[sb1]);
             if (gsz == 4 && (i & 1) == 0 && i == nst - 1) mbar_arrive(&ctl->empty_b[sb0]);
           }
-          if (i == nst - 1) tc_commit(&ctl->acc_full);
+          if (NI == 1 ? (i == nst - 1) : (i + 2 >= nst)) tc_commit(&ctl->acc_full);   // my last stage here
           PROF_ADD(pm_commit, tm);
 #ifdef B200DQ_PROFILE
           ++pm_n;
 #endif
           sa += 4; if (sa >= static_cast<uint32_t>(NS)) { sa -= NS; pa ^= 1u; }
+        }
+        // a one-stage segment leaves the other issuer without work: it still owes its arrival
+        // (after the epilogue has drained the previous segment, so it cannot run ahead and put
+        // two arrivals into one phase)
+        if (NI == 2 && nst == 1 && ((static_cast<uint32_t>(me) ^ g0) & 1u) != 0u) {
+          ok &= mbar_wait(&ctl->acc_empty, (tc & 1u) ^ 1u, abort_flag, st, 3);
+          mbar_arrive(&ctl->acc_full);
         }
         g0 += static_cast<uint32_t>(nst);
         gc0 += (static_cast<uint32_t>(2 * nst) + gmask) >> gshift;
@@ -595,11 +606,13 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
             const uint32_t dst = tmem_base + lane_addr + kAccCols + sa * 32 + q * RPC;
             if constexpr (RPC == 16) tmem_st_32x32b_x16(dst, regs);
             else tmem_st_32x32b_x8(dst, regs);
-            if (q == CH - 1) {
+            if (it == 2 * CH - 1) {
+              // both k-blocks of the stage are stored: one hand-off per stage, on the
+              // barrier of the stage's first slot
               tc_wait_st();
               tc_fence_before_sync();
               __syncwarp();
-              if (lane == 0) mbar_arrive(&ctl->a_full[sa]);
+              if (lane == 0) mbar_arrive(&ctl->a_full[sa - 1]);
               PROF_ADD(pd_st, td);
             }
           }
@@ -626,6 +639,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
     const bool use_vec = (p.flags & GF_VEC_STORE) != 0;
     const bool plain = (p.flags & (GF_HAS_BIAS | GF_ROW_SCALE)) == 0;
     uint32_t tc = 0;
+    uint32_t g0_e = 0;   // stages of this CTA before the current segment
     bool ok = true;
     SegmentWalk walk(p);
     Segment w;
@@ -635,8 +649,10 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
       const int n0_warp = w.n_tile * kTileRows + quarter * 32;
       const int n = n0_warp + lane;
       const int nkb = (w.st_end - w.st_begin) * 2;
-      // every issuer has at least one k-block in every segment (segments hold >= 2)
-      const uint32_t valid = (1u << NI) - 1u;
+      // accumulators that hold anything: both, unless the segment is a single stage
+      const int nst_e = w.st_end - w.st_begin;
+      const uint32_t valid = (NI == 2 && nst_e == 1) ? (1u << (g0_e & 1u)) : ((1u << NI) - 1u);
+      g0_e += static_cast<uint32_t>(nst_e);
       (void)nkb;
       ok &= mbar_wait(&ctl->acc_full, tc & 1, abort_flag, st, 8);
       tc_fence_after_sync();
