@@ -192,7 +192,7 @@ def workload_config(M, gpus, allgather):
 # DRAM bytes of one launch of the dominant kernel at M=4096 from the committed ncu
 # capture (dram__bytes_read.sum 840,656,128 + dram__bytes_write.sum 244,715,264);
 # the algorithmic figure is 426,770,432.
-TRAFFIC_M4096 = {"dram_bytes_per_launch": 1160232448,
+TRAFFIC_M4096 = {"dram_bytes_per_launch": 840532480,
                  "source": "profiles/umma_dequant_gemm_w4a16_m4096.md (ncu --set full, one launch)"}
 
 

@@ -60,7 +60,7 @@ def check_float(out, ref, strict=1e-2):
     (77, 200, 512, 128, torch.bfloat16, True),       # N tail inside a 128-row tile
     (64, 256, 1408, 128, torch.bfloat16, False),     # K = 11 groups: K padded to a whole stage
     (40, 320, 256, 256, torch.float16, True),        # one group per row (group == K)
-    (64, 640, 128, 128, torch.bfloat16, True),       # K = one stage: single-stage segments, one issuer idle
+    (64, 640, 128, 128, torch.bfloat16, False),      # K = one stage: single-stage segments, one issuer idle
     (100, 384, 384, 128, torch.float16, False),      # three stages per tile: odd segments
     # small-M kernel (mma.sync, at most 16 tokens): split tiles, N and K tails
     (2, 1000, 4096, 128, torch.bfloat16, True),
