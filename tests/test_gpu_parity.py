@@ -285,6 +285,28 @@ def test_bitnet_int8xint2_bit_exact(M, N, K):
     assert torch.equal(out.cpu(), R.ref_bitnet_linear(A_q, s_act, W.to(torch.int8), s_w, torch.bfloat16))
 
 
+def test_bitnet_ragged_k_64_tokens_repeated_cold_launches():
+    """K = 8640 is 67.5 k-blocks, so the activation ring runs in single-k-block groups, and 64
+    tokens use the two-issuer tile. Many launches with a cold L2 in between (loads then land
+    out of order now and then) must all be exact and leave the device status clean."""
+    M, N, K = 64, 3200, 8640
+    W = torch.multinomial(torch.tensor([0.25, 0.5, 0.25]), N * K, replacement=True, generator=gen(3)).reshape(N, K) - 1
+    A = torch.randint(-127, 128, (M, K), generator=gen(4), dtype=torch.int8)
+    codes = quantize.compress_codes((W + 2).to(torch.uint8), 2)
+    pw = ops.pack_int2(codes.to(DEV), N, K, code_offset=2)
+    ref32 = R.ref_bitnet_int32(A, W.to(torch.int8)).to(DEV)
+    A_d = A.to(DEV)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)
+    outs = [torch.empty(M, N, dtype=torch.int32, device=DEV) for _ in range(8)]
+    for rep in range(25):
+        for C in outs:
+            flush.zero_()
+            ops.gemm(A_d, pw, out=C)
+        ops.check_status(torch.device(DEV))
+        for C in outs:
+            assert torch.equal(C, ref32), f"repetition {rep}"
+
+
 def test_bitnet_decode_reference_flow():
     # tilelang_bitnet_158_int8xint2_decode.py:238-258: A in [0,4), W in {0,1}, unsigned codes,
     # general_compress + interleave_weight(qw, 2, "int8")

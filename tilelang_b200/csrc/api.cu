@@ -147,9 +147,6 @@ int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_cta
 // k-blocks as separate [row][128 B] slabs; that view needs K to be a whole number of
 // k-blocks. Returns the group size actually encoded (1 = plain 2-D map) or -1.
 int encode_activation_map(CUtensorMap* map, const void* a, int M, int K, int act_type, int tn, int group) {
-#ifdef B200DQ_EXP_HALF_B
-  tn /= 2;
-#endif
   if (g_encode == nullptr) return fail("tensor-map encoder not resolved (b200dq_init not run?)");
   const int esize = (act_type == ACT_I8) ? 1 : 2;
   const int bke = k_elems_per_kblock(act_type);

@@ -141,7 +141,12 @@ struct RingConfig {
   static constexpr int kSlots = (512 - kAccCols) / 32 > 14 ? 14 : (512 - kAccCols) / 32;
   static constexpr int kBSlabBytes = TN * 128;                                // one k-block of activations
   static constexpr int kBGroupBytes = kGB * kBSlabBytes;
-  static constexpr int kNBG = TN >= 256 ? (WF == WF_I4_I8 ? 5 : 6) : (TN >= 128 ? 4 : (TN >= 64 ? 3 : 4));
+  // With two independent issuers (kNI == 2) the ring depth is even: when K is ragged the
+  // groups shrink to single k-blocks, stage g then reads slots 2g and 2g + 1 (mod kNBG), and
+  // only an even depth gives every slot to the same issuer each time round. An issuer that
+  // sees a slot's barrier only every other phase can find it one phase behind, where the
+  // parity test answers "complete" for a load that has not landed.
+  static constexpr int kNBG = TN >= 256 ? (WF == WF_I4_I8 ? 5 : 6) : 4;
   static constexpr int kCodeBytes = 2 * codes_per_kblock_bytes(WF);           // per stage
   static constexpr int kWStageMax = kCodeBytes + sz_smem_bytes(WF);           // largest packed stage
   static constexpr int kWPairSmem = 2 * kWStageMax;                           // ring slot: two stages back to back
@@ -153,6 +158,7 @@ struct RingConfig {
   static_assert(kSlots >= 8 && kSlots <= kMaxSlots && kSlots % 2 == 0, "TMEM ring depth");
   static_assert(kGB > 1 || (kNI == 1 && kNBG <= kSlots), "single-k-block groups reuse the cons barriers");
   static_assert(kGB != 2 || 2 * kNBG <= kSlots, "two-k-block groups reuse the cons barriers");
+  static_assert(kNI == 1 || kNBG % 2 == 0, "two issuers need an even activation ring");
   static_assert(kNWP >= 1, "weight ring depth");
   static_assert(kWStageMax % 128 == 0, "stage keeps 128 B alignment");
   static_assert(kSmemBytes <= 232448, "over the 227 KiB shared-memory limit");
@@ -421,11 +427,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
 #ifdef B200DQ_PROFILE
           prof_ts_b[s] = clock64();
 #endif
-#ifdef B200DQ_EXP_HALF_B
-          mbar_arrive_expect_tx(&ctl->full_b[s], static_cast<uint32_t>(gsz) * Ring::kBSlabBytes / 2);
-#else
           mbar_arrive_expect_tx(&ctl->full_b[s], static_cast<uint32_t>(gsz) * Ring::kBSlabBytes);
-#endif
           if (GB == 1 || gsz == 1)
             tma_load_2d(smem_b + s * Ring::kBGroupBytes, &tmap_a, kb * BKE, w.row0, &ctl->full_b[s]);
           else
@@ -657,30 +659,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
       ok &= mbar_wait(&ctl->acc_full, tc & 1, abort_flag, st, 8);
       tc_fence_after_sync();
       PROF_ADD(pe_wait, te);
-#pragma unroll 1
-      for (int c = 0; c < TN / NV; ++c) {
-        uint32_t acc[NV];
-        bool have = false;
-#pragma unroll
-        for (int i = 0; i < NI; ++i) {
-          if (!(valid & (1u << i))) continue;
-          uint32_t part[NV];
-          if constexpr (NV == 32) tmem_ld_32x32b_x32(tmem_base + lane_addr + i * TN + c * NV, part);
-          else tmem_ld_32x32b_x16(tmem_base + lane_addr + i * TN + c * NV, part);
-          tc_wait_ld();
-          if (!have) {
-#pragma unroll
-            for (int j = 0; j < NV; ++j) acc[j] = part[j];
-            have = true;
-          } else {
-#pragma unroll
-            for (int j = 0; j < NV; ++j) {
-              if constexpr (kInt) acc[j] = static_cast<uint32_t>(static_cast<int>(acc[j]) + static_cast<int>(part[j]));
-              else acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __uint_as_float(part[j]));
-            }
-          }
-        }
-        PROF_ADD(pe_ld, te);
+      auto store_chunk = [&](const uint32_t (&acc)[NV], int c) {
         const int m0 = w.row0 + c * NV;
         if (w.slot >= 0) {
           // partial tile: raw accumulator values, [token][row] so lanes coalesce
@@ -704,11 +683,63 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
             default: store_values_direct<int, kInt, NV>(p, acc, m0, w.row_end, n); break;
           }
         }
-        PROF_ADD(pe_store, te);
+      };
+      // The accumulator goes back to the issuers as soon as its last columns are in
+      // registers, before they are stored.
+      auto release_acc = [&]() {
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->acc_empty);
+      };
+      if constexpr (NI == 1 && NV == 32 && (TN / NV) % 2 == 0) {
+        // one accumulator, an even number of 32-column chunks: the load of the next chunk
+        // flies under the stores of the current one (two register buffers, loop unrolled by 2)
+        uint32_t buf_a[NV], buf_b[NV];
+        tmem_ld_32x32b_x32(tmem_base + lane_addr, buf_a);
+#pragma unroll 1
+        for (int c = 0; c < TN / NV; c += 2) {
+          tc_wait_ld();
+          tmem_ld_32x32b_x32(tmem_base + lane_addr + (c + 1) * NV, buf_b);
+          PROF_ADD(pe_ld, te);
+          store_chunk(buf_a, c);
+          PROF_ADD(pe_store, te);
+          tc_wait_ld();
+          if (c + 2 < TN / NV) tmem_ld_32x32b_x32(tmem_base + lane_addr + (c + 2) * NV, buf_a);
+          else release_acc();
+          PROF_ADD(pe_ld, te);
+          store_chunk(buf_b, c + 1);
+          PROF_ADD(pe_store, te);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < TN / NV; ++c) {
+          uint32_t acc[NV];
+          bool have = false;
+#pragma unroll
+          for (int i = 0; i < NI; ++i) {
+            if (!(valid & (1u << i))) continue;
+            uint32_t part[NV];
+            if constexpr (NV == 32) tmem_ld_32x32b_x32(tmem_base + lane_addr + i * TN + c * NV, part);
+            else tmem_ld_32x32b_x16(tmem_base + lane_addr + i * TN + c * NV, part);
+            tc_wait_ld();
+            if (!have) {
+#pragma unroll
+              for (int j = 0; j < NV; ++j) acc[j] = part[j];
+              have = true;
+            } else {
+#pragma unroll
+              for (int j = 0; j < NV; ++j) {
+                if constexpr (kInt) acc[j] = static_cast<uint32_t>(static_cast<int>(acc[j]) + static_cast<int>(part[j]));
+                else acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __uint_as_float(part[j]));
+              }
+            }
+          }
+          PROF_ADD(pe_ld, te);
+          if (c == TN / NV - 1) release_acc();
+          store_chunk(acc, c);
+          PROF_ADD(pe_store, te);
+        }
       }
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&ctl->acc_empty);
       ++tc;
     }
 #ifdef B200DQ_PROFILE
