@@ -240,6 +240,30 @@ def test_mxfp4_dequant_bit_exact_and_all_codes():
     assert torch.equal(C, W[:, :128].T.contiguous())
 
 
+@pytest.mark.parametrize("M", [1, 7, 16])
+def test_mxfp4_small_m_kernel_bit_exact_and_against_oracle(M):
+    """At most 16 tokens take the small-M kernel for e2m1 weights too: one-hot rows read the
+    dequantised weights back bit for bit, random rows meet the oracle, and an explicit token
+    tile of 16 (the tcgen05 kernel) gives the same numbers up to the fp32 summation order."""
+    N, K = 384, 1024
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(21), dtype=torch.uint8)
+    scale = torch.randint(119, 128, (N, K // 32), generator=gen(22)).to(torch.uint8)
+    W = R.dequant_mxfp4(qB, scale, 127, "e2m1")
+    cols = [5 + 61 * i for i in range(M)]
+    A1 = torch.zeros(M, K, dtype=torch.bfloat16)
+    for i, c in enumerate(cols):
+        A1[i, c] = 1.0
+    pw = ops.pack_mxfp4(qB.to(DEV), scale.to(DEV), N, K)
+    C1 = ops.gemm(A1.to(DEV), pw, out_dtype=torch.float32).cpu()
+    assert torch.equal(C1, W[:, cols].T.contiguous().float())
+    A = torch.randn(M, K, generator=gen(23)).to(torch.bfloat16)
+    small = ops.gemm(A.to(DEV), pw, out_dtype=torch.float32)
+    umma = ops.gemm(A.to(DEV), pw, out_dtype=torch.float32, token_tile=16)
+    tb.check_status()
+    assert (small - umma).abs().max() <= 1e-4 * umma.abs().max()
+    check_float(ops.gemm(A.to(DEV), pw), R.ref_mxfp4(A, qB, scale, None, exp_bias=127, fmt="e2m1"))
+
+
 def test_mxfp4_reference_twiddled_bytes_with_raw_exponent_and_bias():
     """Byte-level drop-in for the reference's fast_dequant=True inputs: twiddled codes
     and 2**Scale with no bias (example_dequant_gemm_bf16_mxfp4_hopper.py:381-423)."""

@@ -18,7 +18,7 @@
 #include "elementwise.cuh"
 #include "pack_kernels.cuh"
 #include "umma_gemm.cuh"
-#include "skinny_gemm.cuh"
+#include "skinny_launch.h"
 
 namespace {
 
@@ -216,39 +216,6 @@ int launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStre
   return 0;
 }
 
-// Small-M path on the token-tile-16 schedule, then the same fix-up pass.
-template <typename Kernel>
-int launch_small_m(Kernel kernel, int smem_bytes, bool* attr_set, const GemmParams& p, int grid, cudaStream_t stream) {
-  if (!*attr_set) {
-    CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
-    *attr_set = true;
-  }
-  kernel<<<grid, kSkinnyThreads, smem_bytes, stream>>>(p);
-  CUDA_OK(cudaGetLastError());
-  return 0;
-}
-
-template <int WF, int ACT>
-int launch_skinny(const GemmParams& p, int grid, cudaStream_t stream) {
-  static bool attr_set[kMaxDevices][4] = {};
-  int dev = 0;
-  CUDA_OK(cudaGetDevice(&dev));
-  int rc;
-  if (p.M <= 8) rc = launch_small_m(skinny_dequant_gemm_kernel<1, WF, ACT>, kSkinnySmemBytes, &attr_set[dev][2], p, grid, stream);
-  else rc = launch_small_m(skinny_dequant_gemm_kernel<2, WF, ACT>, kSkinnySmemBytes, &attr_set[dev][3], p, grid, stream);
-  if (rc != 0) return rc;
-  if (p.span % p.st_total != 0 && grid > 1) {
-    const dim3 fgrid(grid - 1, kSkinnyTokens / fixup_tokens_per_block(kSkinnyTokens));
-    switch (p.out_type) {
-      case OUT_F16: streamk_fixup_kernel<__half, kSkinnyTokens, false><<<fgrid, kTileRows, 0, stream>>>(p); break;
-      case OUT_BF16: streamk_fixup_kernel<__nv_bfloat16, kSkinnyTokens, false><<<fgrid, kTileRows, 0, stream>>>(p); break;
-      default: streamk_fixup_kernel<float, kSkinnyTokens, false><<<fgrid, kTileRows, 0, stream>>>(p); break;
-    }
-    CUDA_OK(cudaGetLastError());
-  }
-  return 0;
-}
-
 // The small-M kernel takes dense problems of at most 16 tokens with 4-bit weights on 16-bit
 // activations when the caller leaves the token tile to the library (an explicit
 // token_tile = 16 keeps the tcgen05 kernel).
@@ -256,6 +223,7 @@ bool takes_skinny_path(const b200dq_gemm_args* a) {
   if (a->num_groups > 0 || a->M > kSkinnyTokens || a->token_tile != 0) return false;
   if (a->act_type != ACT_F16 && a->act_type != ACT_BF16) return false;
   if (a->out_type == OUT_I32) return false;
+  if (a->weight_format == WF_FP4_E8M0) return a->act_type == ACT_BF16;
   return a->weight_format == WF_U4_SZ || a->weight_format == WF_U4_RAW || a->weight_format == WF_S4_RAW;
 }
 
@@ -454,12 +422,8 @@ int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
 
   auto stream = static_cast<cudaStream_t>(cuda_stream);
   if (skinny) {
-    if (wf == WF_U4_SZ && act == ACT_F16) return launch_skinny<WF_U4_SZ, ACT_F16>(p, s.grid, stream);
-    if (wf == WF_U4_SZ && act == ACT_BF16) return launch_skinny<WF_U4_SZ, ACT_BF16>(p, s.grid, stream);
-    if (wf == WF_U4_RAW && act == ACT_F16) return launch_skinny<WF_U4_RAW, ACT_F16>(p, s.grid, stream);
-    if (wf == WF_U4_RAW && act == ACT_BF16) return launch_skinny<WF_U4_RAW, ACT_BF16>(p, s.grid, stream);
-    if (wf == WF_S4_RAW && act == ACT_F16) return launch_skinny<WF_S4_RAW, ACT_F16>(p, s.grid, stream);
-    return launch_skinny<WF_S4_RAW, ACT_BF16>(p, s.grid, stream);
+    CUDA_OK(launch_skinny_gemm(wf, act, p, s.grid, stream));
+    return 0;
   }
   if (wf == WF_U4_SZ && act == ACT_F16) return dispatch_tn<WF_U4_SZ, ACT_F16>(s.tn, tmap, p, s.grid, stream);
   if (wf == WF_U4_SZ && act == ACT_BF16) return dispatch_tn<WF_U4_SZ, ACT_BF16>(s.tn, tmap, p, s.grid, stream);

@@ -47,48 +47,64 @@ __device__ __forceinline__ __half2 u32_as_h2(uint32_t v) { return *reinterpret_c
 // s * 2^6 (s * 2^9) lands on the same value the reference's ref_program computes in
 // fp32 and rounds once: RN((q - z) * s). sz word: low 16 bits = s * 2^6 (2^9),
 // high 16 bits = -z * 2^-6 (2^-9), both prepared offline in the activation dtype.
+// Codes 1 and 3 of each 16-bit half stay one nibble up (mask 0x00f0): the pattern is then
+// 16 q in the same units (a bf16 with q >= 8 has exponent field 1, which continues the
+// subnormal scale, so it still reads q * 2^-129 exactly) and the fma's factor is 2^123 (2^11)
+// instead -- one shift and four masks per eight codes.
+// One 32-bit word (8 codes) -> 4 registers; s2 / nz2 are the scale word's halves, each
+// duplicated into both 16-bit lanes.
+template <bool kBf16>
+__device__ __forceinline__ void decode_u4_word(uint32_t w, uint32_t s2, uint32_t nz2, uint32_t* out) {
+  const uint32_t wh = w >> 8;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t src = (i & 2) ? wh : w;
+    const uint32_t x = src & ((i & 1) ? 0x00f000f0u : 0x000f000fu);
+    if constexpr (kBf16) {
+      const uint32_t pw2 = (i & 1) ? 0x7d007d00u : 0x7f007f00u;   // 2^123 : 2^127
+      const __nv_bfloat162 t = __hfma2(u32_as_bf162(x), u32_as_bf162(pw2), u32_as_bf162(nz2));
+      out[i] = bf162_as_u32(__hmul2(t, u32_as_bf162(s2)));
+    } else {
+      const uint32_t pw2 = (i & 1) ? 0x68006800u : 0x78007800u;   // 2^11 : 2^15
+      const __half2 t = __hfma2(u32_as_h2(x), u32_as_h2(pw2), u32_as_h2(nz2));
+      out[i] = h2_as_u32(__hmul2(t, u32_as_h2(s2)));
+    }
+  }
+}
+
 template <bool kBf16>
 __device__ __forceinline__ void decode_u4_chunk(const uint4& packed, uint32_t sz, uint32_t (&out)[16]) {
   const uint32_t s2 = __byte_perm(sz, 0, 0x1010);
   const uint32_t nz2 = __byte_perm(sz, 0, 0x3232);
-  const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t x = (w[j] >> (4 * i)) & 0x000f000fu;
-      if constexpr (kBf16) {
-        const __nv_bfloat162 t = __hfma2(u32_as_bf162(x), u32_as_bf162(0x7f007f00u), u32_as_bf162(nz2));
-        out[4 * j + i] = bf162_as_u32(__hmul2(t, u32_as_bf162(s2)));
-      } else {
-        const __half2 t = __hfma2(u32_as_h2(x), u32_as_h2(0x78007800u), u32_as_h2(nz2));
-        out[4 * j + i] = h2_as_u32(__hmul2(t, u32_as_h2(s2)));
-      }
-    }
-  }
+  decode_u4_word<kBf16>(packed.x, s2, nz2, &out[0]);
+  decode_u4_word<kBf16>(packed.y, s2, nz2, &out[4]);
+  decode_u4_word<kBf16>(packed.z, s2, nz2, &out[8]);
+  decode_u4_word<kBf16>(packed.w, s2, nz2, &out[12]);
 }
 
 // No scale at all: weight = q (unsigned) or q - 8 (signed storage), as in the
 // reference's fine-grained example (example_dequant_gemm_fine_grained.py:11-13).
 template <bool kBf16, bool kSigned>
-__device__ __forceinline__ void decode_u4_chunk_noscale(const uint4& packed, uint32_t (&out)[16]) {
-  const uint32_t w[4] = {packed.x, packed.y, packed.z, packed.w};
+__device__ __forceinline__ void decode_u4_word_noscale(uint32_t w, uint32_t* out) {
 #pragma unroll
-  for (int j = 0; j < 4; ++j) {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t t = w[j] >> (4 * i);
-      if constexpr (kBf16) {
-        const uint32_t x = lop3_and_or(t, 0x000f000fu, 0x43004300u);
-        out[4 * j + i] = bf162_as_u32(
-            __hsub2(u32_as_bf162(x), u32_as_bf162(kSigned ? 0x43084308u : 0x43004300u)));
-      } else {
-        const uint32_t x = lop3_and_or(t, 0x000f000fu, 0x64006400u);
-        out[4 * j + i] =
-            h2_as_u32(__hsub2(u32_as_h2(x), u32_as_h2(kSigned ? 0x64086408u : 0x64006400u)));
-      }
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t t = w >> (4 * i);
+    if constexpr (kBf16) {
+      const uint32_t x = lop3_and_or(t, 0x000f000fu, 0x43004300u);
+      out[i] = bf162_as_u32(__hsub2(u32_as_bf162(x), u32_as_bf162(kSigned ? 0x43084308u : 0x43004300u)));
+    } else {
+      const uint32_t x = lop3_and_or(t, 0x000f000fu, 0x64006400u);
+      out[i] = h2_as_u32(__hsub2(u32_as_h2(x), u32_as_h2(kSigned ? 0x64086408u : 0x64006400u)));
     }
   }
+}
+
+template <bool kBf16, bool kSigned>
+__device__ __forceinline__ void decode_u4_chunk_noscale(const uint4& packed, uint32_t (&out)[16]) {
+  decode_u4_word_noscale<kBf16, kSigned>(packed.x, &out[0]);
+  decode_u4_word_noscale<kBf16, kSigned>(packed.y, &out[4]);
+  decode_u4_word_noscale<kBf16, kSigned>(packed.z, &out[8]);
+  decode_u4_word_noscale<kBf16, kSigned>(packed.w, &out[12]);
 }
 
 // 2-bit codes -> int8. 16 codes per word, word j of the chunk covers K

@@ -95,7 +95,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
 
 // Bounded wait. `abort_flag` lives in shared memory; once set, every wait of the
 // CTA returns at once. Returns false if the wait gave up (or the CTA aborted).
-__device__ __noinline__ void mbar_wait_failed(volatile int* abort_flag, DeviceStatus* st,
+static __device__ __noinline__ void mbar_wait_failed(volatile int* abort_flag, DeviceStatus* st,
                                               uint32_t site) {
   *abort_flag = 1;
   if (st != nullptr) {

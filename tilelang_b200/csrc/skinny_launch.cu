@@ -1,0 +1,62 @@
+// Host side of the small-M path: picks the kernel instance, sets its shared-memory
+// attribute once per device and launches it followed by the stream-K fix-up pass.
+#include "skinny_launch.h"
+
+#include "skinny_gemm.cuh"
+
+namespace b200dq {
+
+namespace {
+
+constexpr int kMaxDevicesSkinny = 32;
+
+#define SKINNY_OK(expr)                    \
+  do {                                     \
+    cudaError_t _e = (expr);               \
+    if (_e != cudaSuccess) return _e;      \
+  } while (0)
+
+template <typename Kernel>
+cudaError_t launch_one(Kernel kernel, bool* attr_set, const GemmParams& p, int grid, cudaStream_t stream) {
+  if (!*attr_set) {
+    SKINNY_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSkinnySmemBytes));
+    *attr_set = true;
+  }
+  kernel<<<grid, kSkinnyThreads, kSkinnySmemBytes, stream>>>(p);
+  return cudaGetLastError();
+}
+
+template <int WF, int ACT>
+cudaError_t launch_format(const GemmParams& p, int grid, cudaStream_t stream) {
+  static bool attr_set[kMaxDevicesSkinny][2] = {};
+  int dev = 0;
+  SKINNY_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevicesSkinny) return cudaErrorInvalidDevice;
+  if (p.M <= 8) SKINNY_OK(launch_one(skinny_dequant_gemm_kernel<1, WF, ACT>, &attr_set[dev][0], p, grid, stream));
+  else SKINNY_OK(launch_one(skinny_dequant_gemm_kernel<2, WF, ACT>, &attr_set[dev][1], p, grid, stream));
+  if (p.span % p.st_total != 0 && grid > 1) {
+    const dim3 fgrid(grid - 1, kSkinnyTokens / fixup_tokens_per_block(kSkinnyTokens));
+    switch (p.out_type) {
+      case OUT_F16: streamk_fixup_kernel<__half, kSkinnyTokens, false><<<fgrid, kTileRows, 0, stream>>>(p); break;
+      case OUT_BF16: streamk_fixup_kernel<__nv_bfloat16, kSkinnyTokens, false><<<fgrid, kTileRows, 0, stream>>>(p); break;
+      default: streamk_fixup_kernel<float, kSkinnyTokens, false><<<fgrid, kTileRows, 0, stream>>>(p); break;
+    }
+    SKINNY_OK(cudaGetLastError());
+  }
+  return cudaSuccess;
+}
+
+}  // namespace
+
+cudaError_t launch_skinny_gemm(int wf, int act, const GemmParams& p, int grid, cudaStream_t stream) {
+  if (wf == WF_FP4_E8M0 && act == ACT_BF16) return launch_format<WF_FP4_E8M0, ACT_BF16>(p, grid, stream);
+  if (wf == WF_U4_SZ && act == ACT_F16) return launch_format<WF_U4_SZ, ACT_F16>(p, grid, stream);
+  if (wf == WF_U4_SZ && act == ACT_BF16) return launch_format<WF_U4_SZ, ACT_BF16>(p, grid, stream);
+  if (wf == WF_U4_RAW && act == ACT_F16) return launch_format<WF_U4_RAW, ACT_F16>(p, grid, stream);
+  if (wf == WF_U4_RAW && act == ACT_BF16) return launch_format<WF_U4_RAW, ACT_BF16>(p, grid, stream);
+  if (wf == WF_S4_RAW && act == ACT_F16) return launch_format<WF_S4_RAW, ACT_F16>(p, grid, stream);
+  if (wf == WF_S4_RAW && act == ACT_BF16) return launch_format<WF_S4_RAW, ACT_BF16>(p, grid, stream);
+  return cudaErrorInvalidValue;
+}
+
+}  // namespace b200dq
