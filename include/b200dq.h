@@ -73,7 +73,7 @@ typedef struct b200dq_gemm_args {
   float tensor_scale;       /* used with ROW_SCALE       */
   uint32_t code_bias;       /* bytewise bias of the integer decoders, e.g. 0x02020202 */
   int32_t fp4_exp_bias;     /* 127: OCP e8m0 exponent bytes; 0: raw power-of-two exponents */
-  int32_t token_tile;       /* 0 = choose (M <= 16 with uint4 weights on 16-bit activations then takes the
+  int32_t token_tile;       /* 0 = choose (M <= 16 with uint4 or e2m1 weights on 16-bit activations then takes the
                              * barrier-free small-M kernel); else 16, 32, 64, 128 or 256 tokens per CTA
                              * tile of the tcgen05 kernel */
   int32_t max_ctas;         /* 0 = one per SM; else an upper bound on the grid */
