@@ -190,9 +190,9 @@ def workload_config(M, gpus, allgather):
 
 
 # DRAM bytes of one launch of the dominant kernel at M=4096 from the committed ncu
-# capture (dram__bytes_read.sum 840,656,128 + dram__bytes_write.sum 244,715,264);
+# capture (dram__bytes_read.sum 631,474,432 + dram__bytes_write.sum 243,267,584);
 # the algorithmic figure is 426,770,432.
-TRAFFIC_M4096 = {"dram_bytes_per_launch": 840532480,
+TRAFFIC_M4096 = {"dram_bytes_per_launch": 874742016,
                  "source": "profiles/umma_dequant_gemm_w4a16_m4096.md (ncu --set full, one launch)"}
 
 
