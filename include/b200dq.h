@@ -73,9 +73,9 @@ typedef struct b200dq_gemm_args {
   float tensor_scale;       /* used with ROW_SCALE       */
   uint32_t code_bias;       /* bytewise bias of the integer decoders, e.g. 0x02020202 */
   int32_t fp4_exp_bias;     /* 127: OCP e8m0 exponent bytes; 0: raw power-of-two exponents */
-  int32_t token_tile;       /* 0 = choose (M <= 16 with uint4 or e2m1 weights on 16-bit activations then takes the
-                             * barrier-free small-M kernel); else 16, 32, 64, 128 or 256 tokens per CTA
-                             * tile of the tcgen05 kernel */
+  int32_t token_tile;       /* 0 = choose (M <= 16 with uint4 or e2m1 weights on 16-bit activations and
+                             * K % 128 == 0 then takes the memory-bound small-M kernel); else 16, 32, 64,
+                             * 128 or 256 tokens per CTA tile of the tcgen05 kernel */
   int32_t max_ctas;         /* 0 = one per SM; else an upper bound on the grid */
   /* Grouped mode (mixture of experts; num_groups = 0 for one dense GEMM). Rows of A and C
    * are sorted by group; group g owns rows [group_row_prefix[g], group_row_prefix[g+1]) and
@@ -101,9 +101,16 @@ typedef struct b200dq_gemm_args {
  * for one B200. */
 int b200dq_gemm(const b200dq_gemm_args* args, void* cuda_stream);
 
-/* Scratch bytes b200dq_gemm needs for these sizes (stream-K partial tiles). */
+/* Scratch bytes b200dq_gemm needs for a dense call of these sizes (stream-K partial
+ * tiles). Before b200dq_init has run on the current device the figure is an upper bound
+ * that holds for any SM count up to 256. */
 size_t b200dq_gemm_workspace_bytes(int32_t M, int32_t N, int32_t K, int32_t weight_format,
                                    int32_t act_type, int32_t token_tile, int32_t max_ctas);
+
+/* The same for a filled-in argument struct; the one to use for grouped calls, whose
+ * schedule follows total_tiles (every group rounds up to whole tiles) and not M. The
+ * pointers in the struct are not read. */
+size_t b200dq_gemm_workspace_bytes_for(const b200dq_gemm_args* args);
 
 /* Bytes of the packed weight image (codes and scale words) for an (N, K) weight. */
 size_t b200dq_packed_weight_bytes(int32_t N, int32_t K, int32_t group_size, int32_t weight_format);
@@ -114,7 +121,9 @@ size_t b200dq_packed_weight_bytes(int32_t N, int32_t K, int32_t group_size, int3
  * plus, per format:
  *   U4_SZ    : scales and zeros (N, K/group_size) in the activation dtype
  *              (zeros may be NULL = fixed zero-point 8); weight = (q - z) * s, the
- *              reference's "original" zeros mode (quantize/lop3.py:684-689);
+ *              reference's "original" zeros mode (quantize/lop3.py:684-689). The image
+ *              keeps s * 2^6 (bf16) or s * 2^9 (fp16) in the activation dtype: fp16
+ *              scales must stay below 128 in magnitude or they overflow to infinity;
  *   FP4_E8M0 : `scales` = (N, K/32) exponent bytes; zeros unused;
  *   others   : scales and zeros unused (NULL).
  * Output: the tiled, pre-interleaved image the GEMM streams with one bulk copy
@@ -148,7 +157,9 @@ int b200dq_unpack_int4_to_int8(const void* packed, void* out, int64_t num_elems,
  * examples/fusedmoe/example_fusedmoe_torch.py:8-23. */
 int b200dq_silu_mul(const void* h, void* out, int64_t rows, int32_t H, int32_t act_type, void* cuda_stream);
 
-/* No counterpart in the reference. The same GEMM as b200dq_gemm for callers that
+/* No counterpart in the reference. The same GEMM as b200dq_gemm (same validation,
+ * schedule and kernel choice, small-M kernel included: both run one internal routine) for
+ * callers that
  * cannot allocate device memory at all -- code running where cudaMalloc is off
  * limits (inside another framework's allocator callbacks, under a memory pool that
  * owns the whole device, in a process that was handed pre-mapped buffers only). The
@@ -168,6 +179,14 @@ int b200dq_silu_mul(const void* h, void* out, int64_t rows, int32_t H, int32_t a
  *     calls that overlap on the GPU -- different streams, or graphs replayed
  *     concurrently -- race on it: serialise them. */
 int b200dq_gemm_static_scratch(const b200dq_gemm_args* args, void* cuda_stream);
+
+/* No counterpart in the reference. The size check of b200dq_gemm_static_scratch alone,
+ * for a part with `sm_count` SMs; needs no GPU and launches nothing. Stores the scratch
+ * bytes the call's schedule needs and the capacity of the static array (either pointer
+ * may be NULL). Returns 0 if the call would fit, -1 (with the same message the entry
+ * point gives) if it would be rejected as too large or the sizes are invalid. */
+int b200dq_static_scratch_check(const b200dq_gemm_args* args, int32_t sm_count, size_t* needed_bytes,
+                                size_t* capacity_bytes);
 
 /* Reads the device status word of the current device (synchronises `stream`).
  * Returns 0 if no kernel recorded an error since the last reset, else -1 with a

@@ -360,12 +360,12 @@ def mismatch_ratio(x: torch.Tensor, ref: torch.Tensor, rtol: float = 1e-2, atol:
     return float((d > atol + rtol * ref.double().abs()).double().mean())
 
 
-def max_rel_error(x: torch.Tensor, ref: torch.Tensor) -> float:
-    """max |x - ref| / max(|ref|, rms(ref)): the relative error, measured against the
-    typical output magnitude for elements that happen to fall near zero (a plain
-    |x - ref| / |ref| is unbounded there for any rounded output)."""
+def max_rel_error(x: torch.Tensor, ref: torch.Tensor, floor_frac: float = 1.0) -> float:
+    """max |x - ref| / max(|ref|, floor_frac * rms(ref)): the relative error, measured against
+    (a fraction of) the typical output magnitude for elements that happen to fall near zero
+    (a plain |x - ref| / |ref| is unbounded there for any rounded output)."""
     r = ref.double()
-    floor = float(r.pow(2).mean().sqrt())
+    floor = floor_frac * float(r.pow(2).mean().sqrt())
     if floor == 0.0:
         return float((x.double() - r).abs().max())
     return float(((x.double() - r).abs() / torch.clamp(r.abs(), min=floor)).max())

@@ -27,6 +27,8 @@ EXPORTED_SYMBOLS = (
     "b200dq_gemm",
     "b200dq_gemm_static_scratch",
     "b200dq_gemm_workspace_bytes",
+    "b200dq_gemm_workspace_bytes_for",
+    "b200dq_static_scratch_check",
     "b200dq_packed_weight_bytes",
     "b200dq_pack_weights",
     "b200dq_check_status",
@@ -91,6 +93,10 @@ def _declare(lib):
     lib.b200dq_gemm_static_scratch.argtypes = [ctypes.POINTER(GemmArgs), vp]
     lib.b200dq_gemm_workspace_bytes.restype = sz
     lib.b200dq_gemm_workspace_bytes.argtypes = [i32, i32, i32, i32, i32, i32, i32]
+    lib.b200dq_gemm_workspace_bytes_for.restype = sz
+    lib.b200dq_gemm_workspace_bytes_for.argtypes = [ctypes.POINTER(GemmArgs)]
+    lib.b200dq_static_scratch_check.restype = ctypes.c_int
+    lib.b200dq_static_scratch_check.argtypes = [ctypes.POINTER(GemmArgs), i32, ctypes.POINTER(sz), ctypes.POINTER(sz)]
     lib.b200dq_packed_weight_bytes.restype = sz
     lib.b200dq_packed_weight_bytes.argtypes = [i32, i32, i32, i32]
     lib.b200dq_pack_weights.restype = ctypes.c_int

@@ -12,6 +12,7 @@
 #include <cstdio>
 #include <cstring>
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 
 #include "../../include/b200dq.h"
@@ -19,13 +20,14 @@
 #include "pack_kernels.cuh"
 #include "umma_gemm.cuh"
 #include "skinny_launch.h"
+#include "umma_launch.h"
 
 namespace {
 
 using namespace b200dq;
 
 constexpr int kMaxDevices = 32;
-constexpr int kAbiVersion = 2;
+constexpr int kAbiVersion = 3;
 constexpr int kMinSpan = 8;   // fewest k-blocks worth giving a CTA of its own
 
 thread_local char g_err[1024] = "";
@@ -50,14 +52,13 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapFloatOOBfill);
 
 struct DeviceState {
-  bool ready = false;
+  std::atomic<bool> ready{false};   // set (release) after the fields below, under g_mu
   int sm_count = 0;
   DeviceStatus* status = nullptr;
 };
 
 std::mutex g_mu;
 DeviceState g_dev[kMaxDevices];
-unsigned long long* g_prof = nullptr;   // profiling builds: per-CTA phase timers
 EncodeTiledFn g_encode = nullptr;
 
 // ---- state of b200dq_gemm_static_scratch ------------------------------------
@@ -70,7 +71,7 @@ constexpr size_t kStaticScratchBytes = 40u << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 struct StaticScratchState {
-  bool ready = false;
+  std::atomic<bool> ready{false};   // set (release) after the two fields below, under g_mu
   int sm_count = 0;
   void* scratch = nullptr;   // device address of g_static_scratch on this device
 };
@@ -80,7 +81,7 @@ int current_device_state(DeviceState** out) {
   int dev = 0;
   CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return fail("device index %d out of range", dev);
-  if (!g_dev[dev].ready) {
+  if (!g_dev[dev].ready.load(std::memory_order_acquire)) {
     if (b200dq_init() != 0) return -1;
   }
   *out = &g_dev[dev];
@@ -99,6 +100,7 @@ struct Schedule {
   int tn, m_tiles, n_tiles, st_total, grid, span;
   long long units;
   size_t workspace_bytes;
+  bool needs_scratch;   // some tile is cut between CTAs
 };
 
 int k_elems_per_kblock(int act_type) { return act_type == ACT_I8 ? 128 : 64; }
@@ -139,22 +141,69 @@ int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_cta
   s->span = static_cast<int>((s->units + g - 1) / g);
   s->grid = static_cast<int>((s->units + s->span - 1) / s->span);
   s->workspace_bytes = static_cast<size_t>(s->grid) * 2 * s->tn * kTileRows * sizeof(uint32_t);
+  s->needs_scratch = (s->span % s->st_total != 0) && s->grid > 1;
   return 0;
 }
 
-// Tensor map of the activations. With `group` > 1 k-blocks per load the map is 3-D,
-// {k-block element, token row, k-block index}, so one TMA lands `group` consecutive
-// k-blocks as separate [row][128 B] slabs; that view needs K to be a whole number of
-// k-blocks. Returns the group size actually encoded (1 = plain 2-D map) or -1.
+// Encoded activation tensor maps of this thread's recent calls. Encoding costs a driver
+// call of a microsecond or two, which matters next to a 20 us small-M kernel; a map depends
+// only on the key below (the descriptor holds the address, not the data).
+struct TensorMapKey {
+  const void* a;
+  int M, K, act_type, box_tokens, kind;   // kind: 0 = tcgen05 kernel (box_tokens x group), 1 = small-M kernel
+  int group;
+  bool operator==(const TensorMapKey& o) const {
+    return a == o.a && M == o.M && K == o.K && act_type == o.act_type && box_tokens == o.box_tokens &&
+           kind == o.kind && group == o.group;
+  }
+};
+struct TensorMapEntry {
+  TensorMapKey key;
+  CUtensorMap map;
+  int group_encoded;
+  bool valid = false;
+};
+constexpr int kTensorMapCache = 16;
+thread_local TensorMapEntry g_tmap_cache[kTensorMapCache];
+thread_local int g_tmap_next = 0;
+
+const TensorMapEntry* tensor_map_lookup(const TensorMapKey& key) {
+  for (int i = 0; i < kTensorMapCache; ++i)
+    if (g_tmap_cache[i].valid && g_tmap_cache[i].key == key) return &g_tmap_cache[i];
+  return nullptr;
+}
+
+void tensor_map_remember(const TensorMapKey& key, const CUtensorMap& map, int group_encoded) {
+  TensorMapEntry& e = g_tmap_cache[g_tmap_next];
+  g_tmap_next = (g_tmap_next + 1) % kTensorMapCache;
+  e.key = key;
+  e.map = map;
+  e.group_encoded = group_encoded;
+  e.valid = true;
+}
+
+CUtensorMapDataType tensor_map_dtype(int act_type) {
+  return act_type == ACT_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+         : act_type == ACT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+}
+
+// Tensor map of the activations for the tcgen05 kernel. With `group` > 1 k-blocks per load
+// the map is 3-D, {k-block element, token row, k-block index}, so one TMA lands `group`
+// consecutive k-blocks as separate [row][128 B] slabs; that view needs K to be a whole
+// number of k-blocks. Returns the group size actually encoded (1 = plain 2-D map) or -1.
 int encode_activation_map(CUtensorMap* map, const void* a, int M, int K, int act_type, int tn, int group) {
   if (g_encode == nullptr) return fail("tensor-map encoder not resolved (b200dq_init not run?)");
   const int esize = (act_type == ACT_I8) ? 1 : 2;
   const int bke = k_elems_per_kblock(act_type);
   if ((reinterpret_cast<uintptr_t>(a) & 15) != 0) return fail("activation pointer must be 16-byte aligned");
   if ((static_cast<long long>(K) * esize) % 16 != 0) return fail("activation row pitch must be a multiple of 16 bytes");
-  const CUtensorMapDataType dt = act_type == ACT_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                                 : act_type == ACT_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
-                                                        : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const TensorMapKey key{a, M, K, act_type, tn, 0, group};
+  if (const TensorMapEntry* hit = tensor_map_lookup(key)) {
+    *map = hit->map;
+    return hit->group_encoded;
+  }
+  const CUtensorMapDataType dt = tensor_map_dtype(act_type);
   if (group > 1 && K % bke == 0) {
     cuuint64_t dims[3] = {static_cast<cuuint64_t>(bke), static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(K / bke)};
     cuuint64_t strides[2] = {static_cast<cuuint64_t>(K) * esize, static_cast<cuuint64_t>(bke) * esize};
@@ -163,7 +212,10 @@ int encode_activation_map(CUtensorMap* map, const void* a, int M, int K, int act
     CUresult r = g_encode(map, dt, 3, const_cast<void*>(a), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r == CUDA_SUCCESS) return group;
+    if (r == CUDA_SUCCESS) {
+      tensor_map_remember(key, *map, group);
+      return group;
+    }
     // fall through to the 2-D map
   }
   cuuint64_t dims[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(M)};
@@ -175,7 +227,35 @@ int encode_activation_map(CUtensorMap* map, const void* a, int M, int K, int act
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail("cuTensorMapEncodeTiled failed with CUresult %d (M=%d K=%d box=%dx%d)",
                                      static_cast<int>(r), M, K, bke, tn);
+  tensor_map_remember(key, *map, 1);
   return 1;
+}
+
+// Tensor map of the activations for the small-M kernel: 16-bit elements viewed as
+// {64 k, k-block parity, token, stage of 128 k}; one load brings the box
+// {64, 2, box_tokens, 1} = one stage of every token, which the 128-byte swizzle lays out
+// as [token][parity][128 B] with bank-conflict-free fragment reads
+// (skinny_gemm.cuh). K must be a multiple of 128. Returns 0 or -1.
+int encode_skinny_activation_map(CUtensorMap* map, const void* a, int M, int K, int act_type, int box_tokens) {
+  if (g_encode == nullptr) return fail("tensor-map encoder not resolved (b200dq_init not run?)");
+  if ((reinterpret_cast<uintptr_t>(a) & 15) != 0) return fail("activation pointer must be 16-byte aligned");
+  if (K % 128 != 0) return fail("the small-M kernel needs K to be a multiple of 128 (got %d)", K);
+  const TensorMapKey key{a, M, K, act_type, box_tokens, 1, 2};
+  if (const TensorMapEntry* hit = tensor_map_lookup(key)) {
+    *map = hit->map;
+    return 0;
+  }
+  cuuint64_t dims[4] = {64, 2, static_cast<cuuint64_t>(M), static_cast<cuuint64_t>(K / 128)};
+  cuuint64_t strides[3] = {128, static_cast<cuuint64_t>(K) * 2, 256};
+  cuuint32_t box[4] = {64, 2, static_cast<cuuint32_t>(box_tokens), 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = g_encode(map, tensor_map_dtype(act_type), 4, const_cast<void*>(a), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail("cuTensorMapEncodeTiled (small-M view) failed with CUresult %d (M=%d K=%d)", static_cast<int>(r), M, K);
+  tensor_map_remember(key, *map, 2);
+  return 0;
 }
 
 int out_elem_size(int out_type) { return (out_type == OUT_F16 || out_type == OUT_BF16) ? 2 : 4; }
@@ -188,54 +268,136 @@ bool output_takes_vector_stores(const void* c, int N, int out_type, int flags) {
   return (static_cast<long long>(N) * out_elem_size(out_type)) % 16 == 0;
 }
 
-template <int TN, int WF, int ACT>
-int launch_gemm(const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStream_t stream) {
-  using Ring = RingConfig<TN, WF>;
-  auto kernel = umma_dequant_gemm_kernel<TN, WF, ACT>;
-  static bool attr_set[kMaxDevices] = {};
-  int dev = 0;
-  CUDA_OK(cudaGetDevice(&dev));
-  if (!attr_set[dev]) {
-    CUDA_OK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Ring::kSmemBytes));
-    attr_set[dev] = true;
-  }
-  kernel<<<grid, kThreads, Ring::kSmemBytes, stream>>>(tmap, p);
-  CUDA_OK(cudaGetLastError());
-  // stream-K second pass: one block column per cut between neighbouring CTAs
-  if (p.span % p.st_total != 0 && grid > 1) {
-    constexpr bool kInt = (ACT == ACT_I8);
-    const dim3 fgrid(grid - 1, TN / fixup_tokens_per_block(TN));
-    switch (p.out_type) {
-      case OUT_F16: streamk_fixup_kernel<__half, TN, kInt><<<fgrid, kTileRows, 0, stream>>>(p); break;
-      case OUT_BF16: streamk_fixup_kernel<__nv_bfloat16, TN, kInt><<<fgrid, kTileRows, 0, stream>>>(p); break;
-      case OUT_F32: streamk_fixup_kernel<float, TN, kInt><<<fgrid, kTileRows, 0, stream>>>(p); break;
-      default: streamk_fixup_kernel<int, TN, kInt><<<fgrid, kTileRows, 0, stream>>>(p); break;
-    }
-    CUDA_OK(cudaGetLastError());
-  }
-  return 0;
-}
-
 // The small-M kernel takes dense problems of at most 16 tokens with 4-bit weights on 16-bit
-// activations when the caller leaves the token tile to the library (an explicit
-// token_tile = 16 keeps the tcgen05 kernel).
+// activations and K a multiple of 128 when the caller leaves the token tile to the library
+// (an explicit token_tile = 16 keeps the tcgen05 kernel).
 bool takes_skinny_path(const b200dq_gemm_args* a) {
   if (a->num_groups > 0 || a->M > kSkinnyTokens || a->token_tile != 0) return false;
   if (a->act_type != ACT_F16 && a->act_type != ACT_BF16) return false;
   if (a->out_type == OUT_I32) return false;
+  if (a->K % 128 != 0) return false;
   if (a->weight_format == WF_FP4_E8M0) return a->act_type == ACT_BF16;
   return a->weight_format == WF_U4_SZ || a->weight_format == WF_U4_RAW || a->weight_format == WF_S4_RAW;
 }
 
-template <int WF, int ACT>
-int dispatch_tn(int tn, const CUtensorMap& tmap, const GemmParams& p, int grid, cudaStream_t stream) {
-  switch (tn) {
-    case 16: return launch_gemm<16, WF, ACT>(tmap, p, grid, stream);
-    case 32: return launch_gemm<32, WF, ACT>(tmap, p, grid, stream);
-    case 64: return launch_gemm<64, WF, ACT>(tmap, p, grid, stream);
-    case 128: return launch_gemm<128, WF, ACT>(tmap, p, grid, stream);
-    default: return launch_gemm<256, WF, ACT>(tmap, p, grid, stream);
+// SM count of the current device once b200dq_init has run on it, else an upper bound that
+// needs no device (256 SMs), so that a size query never under-reports.
+int sm_count_or_bound() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices &&
+      g_dev[dev].ready.load(std::memory_order_acquire))
+    return g_dev[dev].sm_count;
+  return 256;
+}
+
+int resolve_encoder() {
+  if (g_encode != nullptr) return 0;
+  void* fn = nullptr;
+  cudaDriverEntryPointQueryResult qres;
+  CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
+  if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return fail("driver has no cuTensorMapEncodeTiled");
+  g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  return 0;
+}
+
+// Scratch bytes the schedule of a dense call needs on a part with `sm_count` SMs (what
+// b200dq_gemm_static_scratch compares with its array; no device needed).
+int static_scratch_need(const b200dq_gemm_args* a, int sm_count, size_t* need) {
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0)
+    return fail("gemm: M, N, K must be positive (got %d, %d, %d)", a->M, a->N, a->K);
+  Schedule s;
+  const int tile = takes_skinny_path(a) ? kSkinnyTokens : a->token_tile;
+  if (make_schedule(a->M, a->N, a->K, a->act_type, tile, a->max_ctas, sm_count, &s) != 0) return -1;
+  *need = s.needs_scratch ? s.workspace_bytes : 0;
+  return 0;
+}
+
+// The one implementation behind b200dq_gemm and b200dq_gemm_static_scratch: validation,
+// schedule, tensor map, kernel choice and launch. `scratch` receives the stream-K partial
+// tiles; `who` prefixes error messages.
+int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t scratch_bytes, int sm_count,
+             DeviceStatus* status, cudaStream_t stream) {
+  if (a->a == nullptr || a->wp == nullptr || a->c == nullptr) return fail("%s: null tensor pointer", who);
+  if (a->M <= 0 || a->N <= 0 || a->K <= 0)
+    return fail("%s: M, N, K must be positive (got %d, %d, %d)", who, a->M, a->N, a->K);
+  const int wf = a->weight_format, act = a->act_type;
+  const bool int_act = (act == ACT_I8);
+  const bool wf_int = (wf == WF_I2_I8 || wf == WF_I4_I8);
+  if (wf < WF_U4_SZ || wf > WF_I4_I8) return fail("%s: unknown weight format %d", who, wf);
+  if (act < ACT_F16 || act > ACT_I8) return fail("%s: unknown activation type %d", who, act);
+  if (a->out_type < OUT_F16 || a->out_type > OUT_I32) return fail("%s: unknown output type %d", who, a->out_type);
+  if (wf_int != int_act) return fail("%s: weight format %d and activation type %d do not go together", who, wf, act);
+  if (wf == WF_FP4_E8M0 && act != ACT_BF16) return fail("%s: e2m1 weights need bf16 activations", who);
+  if (wf == WF_U4_SZ && (a->group_size <= 0 || a->K % a->group_size != 0))
+    return fail("%s: group_size=%d must divide K=%d", who, a->group_size, a->K);
+  if ((a->flags & GF_HAS_BIAS) && a->bias == nullptr) return fail("%s: HAS_BIAS set but bias is null", who);
+  if ((a->flags & GF_ROW_SCALE) && a->row_scale == nullptr) return fail("%s: ROW_SCALE set but row_scale is null", who);
+  if ((reinterpret_cast<uintptr_t>(a->wp) & 15) != 0) return fail("%s: packed weights must be 16-byte aligned", who);
+
+  const bool grouped = a->num_groups > 0;
+  if (grouped) {
+    if (a->group_row_prefix == nullptr || a->group_tile_prefix == nullptr)
+      return fail("%s: grouped mode needs group_row_prefix and group_tile_prefix", who);
+    if (a->total_tiles <= 0) return fail("%s: grouped mode needs total_tiles > 0", who);
+    if (a->token_tile == 0) return fail("%s: grouped mode needs an explicit token_tile (the prefix arrays depend on it)", who);
+    if (a->flags & (GF_TRANS_C | GF_HAS_BIAS)) return fail("%s: grouped mode supports neither TRANS_C nor bias", who);
   }
+  const bool skinny = takes_skinny_path(a);
+  Schedule s;
+  if (make_schedule(a->M, a->N, a->K, act, skinny ? kSkinnyTokens : a->token_tile, a->max_ctas, sm_count, &s,
+                    grouped ? a->total_tiles : -1) != 0) return -1;
+  if (s.needs_scratch) {
+    if (scratch == nullptr || scratch_bytes < s.workspace_bytes)
+      return fail("%s: workspace too small: need %zu bytes, got %zu", who, s.workspace_bytes, scratch_bytes);
+    if ((reinterpret_cast<uintptr_t>(scratch) & 15) != 0) return fail("%s: workspace must be 16-byte aligned", who);
+  }
+
+  CUtensorMap tmap;
+  int b_group = 1;
+  if (skinny) {
+    if (encode_skinny_activation_map(&tmap, a->a, a->M, a->K, act, skinny_box_tokens(a->M)) != 0) return -1;
+  } else {
+    b_group = encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn, group_kblocks_for(s.tn));
+    if (b_group < 0) return -1;
+  }
+  int flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
+  if (output_takes_vector_stores(a->c, a->N, a->out_type, flags)) flags |= GF_VEC_STORE;
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.b_group = b_group;
+  p.wp = static_cast<const uint8_t*>(a->wp);
+  p.a = a->a;
+  p.c = a->c;
+  p.partial = static_cast<uint32_t*>(scratch);
+  p.bias = a->bias;
+  p.row_scale = a->row_scale;
+  p.tensor_scale = a->tensor_scale;
+  p.code_bias = a->code_bias;
+  p.fp4_exp_bias = a->fp4_exp_bias;
+  p.M = a->M; p.N = a->N; p.K = a->K;
+  p.n_tiles = s.n_tiles; p.m_tiles = s.m_tiles; p.st_total = s.st_total;
+  p.span = s.span; p.units = s.units;
+  p.stage_bytes = stage_bytes_for(wf, a->group_size);
+  p.sz_per_kb = (wf == WF_U4_SZ && a->group_size == 64) ? 1 : 0;
+  p.ldc = (a->flags & GF_TRANS_C) ? a->M : a->N;
+  p.flags = flags;
+  p.out_type = a->out_type;
+  p.tn = s.tn;
+  p.num_groups = grouped ? a->num_groups : 0;
+  p.grp_row_prefix = grouped ? a->group_row_prefix : nullptr;
+  p.grp_tile_prefix = grouped ? a->group_tile_prefix : nullptr;
+  p.grp_w_stride = grouped ? a->group_weight_stride : 0;
+  p.status = status;
+
+  if (skinny) {
+    CUDA_OK(launch_skinny_gemm(wf, act, tmap, p, s.grid, stream));
+    return 0;
+  }
+  const cudaError_t e = launch_umma_gemm(wf, act, s.tn, tmap, p, s.grid, stream);
+  if (e == cudaSuccess) return 0;
+  if (e != cudaErrorInvalidValue) return fail("%s: launch failed: %s", who, cudaGetErrorString(e));
+  return fail("%s: no kernel for weight format %d with activation type %d", who, wf, act);
 }
 
 }  // namespace
@@ -251,23 +413,17 @@ int b200dq_init(void) {
   int dev = 0;
   CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return fail("device index %d out of range", dev);
-  if (g_dev[dev].ready) return 0;
+  if (g_dev[dev].ready.load(std::memory_order_relaxed)) return 0;
   cudaDeviceProp prop;
   CUDA_OK(cudaGetDeviceProperties(&prop, dev));
   if (prop.major != 10) return fail("b200dq needs an sm_100 GPU, device %d is sm_%d%d", dev, prop.major, prop.minor);
-  if (g_encode == nullptr) {
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
-    if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return fail("driver has no cuTensorMapEncodeTiled");
-    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-  }
+  if (resolve_encoder() != 0) return -1;
   DeviceStatus* st = nullptr;
   CUDA_OK(cudaMalloc(&st, sizeof(DeviceStatus)));
   CUDA_OK(cudaMemset(st, 0, sizeof(DeviceStatus)));
   g_dev[dev].status = st;
   g_dev[dev].sm_count = prop.multiProcessorCount;
-  g_dev[dev].ready = true;
+  g_dev[dev].ready.store(true, std::memory_order_release);
   return 0;
 }
 
@@ -275,13 +431,18 @@ size_t b200dq_gemm_workspace_bytes(int32_t M, int32_t N, int32_t K, int32_t weig
                                    int32_t token_tile, int32_t max_ctas) {
   (void)weight_format;
   Schedule s;
-  // grouped calls are bounded by the same figure: at most one CTA per SM, two slots each
-  // an upper bound that does not need a device: assume at most 256 SMs
-  int sm = 256;
-  int dev = 0;
-  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices && g_dev[dev].ready) sm = g_dev[dev].sm_count;
   if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if (make_schedule(M, N, K, act_type, token_tile, max_ctas, sm, &s) != 0) return 0;
+  if (make_schedule(M, N, K, act_type, token_tile, max_ctas, sm_count_or_bound(), &s) != 0) return 0;
+  return s.workspace_bytes;
+}
+
+size_t b200dq_gemm_workspace_bytes_for(const b200dq_gemm_args* a) {
+  if (a == nullptr || a->M <= 0 || a->N <= 0 || a->K <= 0) return 0;
+  Schedule s;
+  const bool grouped = a->num_groups > 0;
+  const int tile = takes_skinny_path(a) ? kSkinnyTokens : a->token_tile;
+  if (make_schedule(a->M, a->N, a->K, a->act_type, tile, a->max_ctas, sm_count_or_bound(), &s,
+                    grouped ? a->total_tiles : -1) != 0) return 0;
   return s.workspace_bytes;
 }
 
@@ -343,104 +504,11 @@ int b200dq_pack_weights(const void* q_natural, const void* scales, const void* z
 
 int b200dq_gemm(const b200dq_gemm_args* a, void* cuda_stream) {
   if (a == nullptr) return fail("gemm: null argument struct");
-  if (a->a == nullptr || a->wp == nullptr || a->c == nullptr) return fail("gemm: null tensor pointer");
-  if (a->M <= 0 || a->N <= 0 || a->K <= 0) return fail("gemm: M, N, K must be positive (got %d, %d, %d)", a->M, a->N, a->K);
-  const int wf = a->weight_format, act = a->act_type;
-  const bool int_act = (act == ACT_I8);
-  const bool wf_int = (wf == WF_I2_I8 || wf == WF_I4_I8);
-  if (wf < WF_U4_SZ || wf > WF_I4_I8) return fail("gemm: unknown weight format %d", wf);
-  if (act < ACT_F16 || act > ACT_I8) return fail("gemm: unknown activation type %d", act);
-  if (a->out_type < OUT_F16 || a->out_type > OUT_I32) return fail("gemm: unknown output type %d", a->out_type);
-  if (wf_int != int_act) return fail("gemm: weight format %d and activation type %d do not go together", wf, act);
-  if (wf == WF_FP4_E8M0 && act != ACT_BF16) return fail("gemm: e2m1 weights need bf16 activations");
-  if (wf == WF_U4_SZ && (a->group_size <= 0 || a->K % a->group_size != 0))
-    return fail("gemm: group_size=%d must divide K=%d", a->group_size, a->K);
-  if ((a->flags & GF_HAS_BIAS) && a->bias == nullptr) return fail("gemm: HAS_BIAS set but bias is null");
-  if ((a->flags & GF_ROW_SCALE) && a->row_scale == nullptr) return fail("gemm: ROW_SCALE set but row_scale is null");
-  if ((reinterpret_cast<uintptr_t>(a->wp) & 15) != 0) return fail("gemm: packed weights must be 16-byte aligned");
-
   DeviceState* ds = nullptr;
   if (current_device_state(&ds) != 0) return -1;
-  const bool grouped = a->num_groups > 0;
-  if (grouped) {
-    if (a->group_row_prefix == nullptr || a->group_tile_prefix == nullptr)
-      return fail("gemm: grouped mode needs group_row_prefix and group_tile_prefix");
-    if (a->total_tiles <= 0) return fail("gemm: grouped mode needs total_tiles > 0");
-    if (a->token_tile == 0) return fail("gemm: grouped mode needs an explicit token_tile (the prefix arrays depend on it)");
-    if (a->flags & (GF_TRANS_C | GF_HAS_BIAS)) return fail("gemm: grouped mode supports neither TRANS_C nor bias");
-  }
-  Schedule s;
-  if (make_schedule(a->M, a->N, a->K, act, a->token_tile, a->max_ctas, ds->sm_count, &s,
-                    grouped ? a->total_tiles : -1) != 0) return -1;
-  const bool needs_ws = (s.span % s.st_total != 0) && s.grid > 1;
-  if (needs_ws) {
-    if (a->workspace == nullptr || a->workspace_bytes < s.workspace_bytes)
-      return fail("gemm: workspace too small: need %zu bytes, got %zu", s.workspace_bytes, a->workspace_bytes);
-    if ((reinterpret_cast<uintptr_t>(a->workspace) & 15) != 0) return fail("gemm: workspace must be 16-byte aligned");
-  }
-
-  const bool skinny = takes_skinny_path(a);
-  CUtensorMap tmap;
-  int b_group = 1;
-  if (skinny) {
-    if ((reinterpret_cast<uintptr_t>(a->a) & 15) != 0) return fail("activation pointer must be 16-byte aligned");
-    if (a->K % 8 != 0) return fail("activation row pitch must be a multiple of 16 bytes");
-  } else {
-    b_group = encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn, group_kblocks_for(s.tn));
-    if (b_group < 0) return -1;
-  }
-  int flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
-  if (output_takes_vector_stores(a->c, a->N, a->out_type, flags)) flags |= GF_VEC_STORE;
-
-  GemmParams p;
-  memset(&p, 0, sizeof(p));
-  p.b_group = b_group;
-  p.wp = static_cast<const uint8_t*>(a->wp);
-  p.a = a->a;
-  p.c = a->c;
-  p.partial = static_cast<uint32_t*>(a->workspace);
-  p.bias = a->bias;
-  p.row_scale = a->row_scale;
-  p.tensor_scale = a->tensor_scale;
-  p.code_bias = a->code_bias;
-  p.fp4_exp_bias = a->fp4_exp_bias;
-  p.M = a->M; p.N = a->N; p.K = a->K;
-  p.n_tiles = s.n_tiles; p.m_tiles = s.m_tiles; p.st_total = s.st_total;
-  p.span = s.span; p.units = s.units;
-  p.stage_bytes = stage_bytes_for(wf, a->group_size);
-  p.sz_per_kb = (wf == WF_U4_SZ && a->group_size == 64) ? 1 : 0;
-  p.ldc = (a->flags & GF_TRANS_C) ? a->M : a->N;
-  p.flags = flags;
-  p.out_type = a->out_type;
-  p.tn = s.tn;
-  p.num_groups = grouped ? a->num_groups : 0;
-  p.grp_row_prefix = grouped ? a->group_row_prefix : nullptr;
-  p.grp_tile_prefix = grouped ? a->group_tile_prefix : nullptr;
-  p.grp_w_stride = grouped ? a->group_weight_stride : 0;
-  p.status = ds->status;
-  p.prof = g_prof;
-
-  auto stream = static_cast<cudaStream_t>(cuda_stream);
-  if (skinny) {
-    CUDA_OK(launch_skinny_gemm(wf, act, p, s.grid, stream));
-    return 0;
-  }
-  if (wf == WF_U4_SZ && act == ACT_F16) return dispatch_tn<WF_U4_SZ, ACT_F16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_U4_SZ && act == ACT_BF16) return dispatch_tn<WF_U4_SZ, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_U4_RAW && act == ACT_F16) return dispatch_tn<WF_U4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_U4_RAW && act == ACT_BF16) return dispatch_tn<WF_U4_RAW, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_S4_RAW && act == ACT_F16) return dispatch_tn<WF_S4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_S4_RAW && act == ACT_BF16) return dispatch_tn<WF_S4_RAW, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_FP4_E8M0) return dispatch_tn<WF_FP4_E8M0, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_I2_I8) return dispatch_tn<WF_I2_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_I4_I8) return dispatch_tn<WF_I4_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
-  return fail("gemm: no kernel for weight format %d with activation type %d", wf, act);
+  return run_gemm("gemm", a, a->workspace, a->workspace_bytes, ds->sm_count, ds->status,
+                  static_cast<cudaStream_t>(cuda_stream));
 }
-
-#ifdef B200DQ_PROFILE
-// profiling builds only: device buffer of 32 x u64 per CTA for phase timers
-void b200dq_debug_set_profile_buffer(void* buf) { g_prof = static_cast<unsigned long long*>(buf); }
-#endif
 
 int b200dq_gemm_static_scratch(const b200dq_gemm_args* a, void* cuda_stream) {
   if (a == nullptr) return fail("gemm_static_scratch: null argument struct");
@@ -448,96 +516,50 @@ int b200dq_gemm_static_scratch(const b200dq_gemm_args* a, void* cuda_stream) {
   CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDevices) return fail("device index %d out of range", dev);
   StaticScratchState& ss = g_static_dev[dev];
-  if (!ss.ready) {
+  if (!ss.ready.load(std::memory_order_acquire)) {
     // One-time set-up for this device, with this device current. In host code the
     // array's name is only a stand-in; the kernels need its device address.
     std::lock_guard<std::mutex> lock(g_mu);
-    if (!ss.ready) {
+    if (!ss.ready.load(std::memory_order_relaxed)) {
       cudaDeviceProp prop;
       CUDA_OK(cudaGetDeviceProperties(&prop, dev));
       if (prop.major != 10) return fail("b200dq needs an sm_100 GPU, device %d is sm_%d%d", dev, prop.major, prop.minor);
-      if (g_encode == nullptr) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        CUDA_OK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres));
-        if (fn == nullptr || qres != cudaDriverEntryPointSuccess) return fail("driver has no cuTensorMapEncodeTiled");
-        g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-      }
+      if (resolve_encoder() != 0) return -1;
       void* ptr = nullptr;
       CUDA_OK(cudaGetSymbolAddress(&ptr, g_static_scratch));
       if (ptr == nullptr) return fail("gemm_static_scratch: no device address for the static scratch array");
       ss.scratch = ptr;
       ss.sm_count = prop.multiProcessorCount;
-      ss.ready = true;
+      ss.ready.store(true, std::memory_order_release);
     }
   }
-  if (a->a == nullptr || a->wp == nullptr || a->c == nullptr) return fail("gemm_static_scratch: null tensor pointer");
   if (a->num_groups > 0) return fail("gemm_static_scratch: grouped mode is not offered by this entry point");
-  if (a->M <= 0 || a->N <= 0 || a->K <= 0)
-    return fail("gemm_static_scratch: M, N, K must be positive (got %d, %d, %d)", a->M, a->N, a->K);
-  Schedule s;
-  if (make_schedule(a->M, a->N, a->K, a->act_type, a->token_tile, a->max_ctas, ss.sm_count, &s) != 0) return -1;
-  if (s.workspace_bytes > kStaticScratchBytes)
+  size_t need = 0;
+  if (static_scratch_need(a, ss.sm_count, &need) != 0) return -1;
+  if (need > kStaticScratchBytes)
     return fail("gemm_static_scratch: this problem needs %zu bytes of scratch, the static array holds %zu; "
                 "lower max_ctas or use b200dq_gemm with a caller-provided workspace",
-                s.workspace_bytes, kStaticScratchBytes);
-  // Same checks, schedule and launch as b200dq_gemm, with the scratch pointer replaced.
-  const int wf = a->weight_format, act = a->act_type;
-  const bool int_act = (act == ACT_I8);
-  const bool wf_int = (wf == WF_I2_I8 || wf == WF_I4_I8);
-  if (wf < WF_U4_SZ || wf > WF_I4_I8) return fail("gemm_static_scratch: unknown weight format %d", wf);
-  if (act < ACT_F16 || act > ACT_I8) return fail("gemm_static_scratch: unknown activation type %d", act);
-  if (a->out_type < OUT_F16 || a->out_type > OUT_I32) return fail("gemm_static_scratch: unknown output type %d", a->out_type);
-  if (wf_int != int_act) return fail("gemm_static_scratch: weight format %d and activation type %d do not go together", wf, act);
-  if (wf == WF_FP4_E8M0 && act != ACT_BF16) return fail("gemm_static_scratch: e2m1 weights need bf16 activations");
-  if (wf == WF_U4_SZ && (a->group_size <= 0 || a->K % a->group_size != 0))
-    return fail("gemm_static_scratch: group_size=%d must divide K=%d", a->group_size, a->K);
-  if ((a->flags & GF_HAS_BIAS) && a->bias == nullptr) return fail("gemm_static_scratch: HAS_BIAS set but bias is null");
-  if ((a->flags & GF_ROW_SCALE) && a->row_scale == nullptr) return fail("gemm_static_scratch: ROW_SCALE set but row_scale is null");
-  if ((reinterpret_cast<uintptr_t>(a->wp) & 15) != 0) return fail("gemm_static_scratch: packed weights must be 16-byte aligned");
-
-  CUtensorMap tmap;
-  const int b_group = encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn, group_kblocks_for(s.tn));
-  if (b_group < 0) return -1;
-  int flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
-  if (output_takes_vector_stores(a->c, a->N, a->out_type, flags)) flags |= GF_VEC_STORE;
-
-  GemmParams p;
-  memset(&p, 0, sizeof(p));
-  p.b_group = b_group;
-  p.wp = static_cast<const uint8_t*>(a->wp);
-  p.c = a->c;
-  p.partial = static_cast<uint32_t*>(ss.scratch);
-  p.bias = a->bias;
-  p.row_scale = a->row_scale;
-  p.tensor_scale = a->tensor_scale;
-  p.code_bias = a->code_bias;
-  p.fp4_exp_bias = a->fp4_exp_bias;
-  p.M = a->M; p.N = a->N; p.K = a->K;
-  p.n_tiles = s.n_tiles; p.m_tiles = s.m_tiles; p.st_total = s.st_total;
-  p.span = s.span; p.units = s.units;
-  p.stage_bytes = stage_bytes_for(wf, a->group_size);
-  p.sz_per_kb = (wf == WF_U4_SZ && a->group_size == 64) ? 1 : 0;
-  p.ldc = (a->flags & GF_TRANS_C) ? a->M : a->N;
-  p.flags = flags;
-  p.out_type = a->out_type;
+                need, kStaticScratchBytes);
   // device-side status reporting needs the word b200dq_init allocates; without it the
   // kernels still bound every wait, they just have nowhere to record one that gave up
-  p.status = g_dev[dev].ready ? g_dev[dev].status : nullptr;
-  p.prof = nullptr;
-  p.tn = s.tn;
+  DeviceStatus* status = g_dev[dev].ready.load(std::memory_order_acquire) ? g_dev[dev].status : nullptr;
+  return run_gemm("gemm_static_scratch", a, ss.scratch, kStaticScratchBytes, ss.sm_count, status,
+                  static_cast<cudaStream_t>(cuda_stream));
+}
 
-  auto stream = static_cast<cudaStream_t>(cuda_stream);
-  if (wf == WF_U4_SZ && act == ACT_F16) return dispatch_tn<WF_U4_SZ, ACT_F16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_U4_SZ && act == ACT_BF16) return dispatch_tn<WF_U4_SZ, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_U4_RAW && act == ACT_F16) return dispatch_tn<WF_U4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_U4_RAW && act == ACT_BF16) return dispatch_tn<WF_U4_RAW, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_S4_RAW && act == ACT_F16) return dispatch_tn<WF_S4_RAW, ACT_F16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_S4_RAW && act == ACT_BF16) return dispatch_tn<WF_S4_RAW, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_FP4_E8M0) return dispatch_tn<WF_FP4_E8M0, ACT_BF16>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_I2_I8) return dispatch_tn<WF_I2_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
-  if (wf == WF_I4_I8) return dispatch_tn<WF_I4_I8, ACT_I8>(s.tn, tmap, p, s.grid, stream);
-  return fail("gemm_static_scratch: no kernel for weight format %d with activation type %d", wf, act);
+int b200dq_static_scratch_check(const b200dq_gemm_args* a, int32_t sm_count, size_t* needed_bytes,
+                                size_t* capacity_bytes) {
+  if (a == nullptr) return fail("static_scratch_check: null argument struct");
+  if (sm_count <= 0) return fail("static_scratch_check: sm_count must be positive");
+  size_t need = 0;
+  if (static_scratch_need(a, sm_count, &need) != 0) return -1;
+  if (needed_bytes != nullptr) *needed_bytes = need;
+  if (capacity_bytes != nullptr) *capacity_bytes = kStaticScratchBytes;
+  if (need > kStaticScratchBytes)
+    return fail("gemm_static_scratch: this problem needs %zu bytes of scratch, the static array holds %zu; "
+                "lower max_ctas or use b200dq_gemm with a caller-provided workspace",
+                need, kStaticScratchBytes);
+  return 0;
 }
 
 int b200dq_absmax_quant_int8(const void* x, void* q, float* scale, int32_t M, int32_t K, int32_t act_type,

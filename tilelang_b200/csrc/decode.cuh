@@ -24,6 +24,10 @@
 
 namespace b200dq {
 
+// Position of row r inside the 2 KiB slab that holds chunk c (counted over the whole stage)
+// of a packed stage: r ^ chunk_swizzle(c). See pack_kernels.cuh for why.
+__host__ __device__ constexpr int chunk_swizzle(int chunk_in_stage) { return (2 * chunk_in_stage) & 6; }
+
 __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t magic) {
   uint32_t r;
   asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(magic));

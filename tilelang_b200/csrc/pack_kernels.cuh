@@ -2,13 +2,16 @@
 // (N, K*bits/8) -> the tiled, pre-interleaved image the GEMM streams.
 //
 // Packed image: [n_tile][stage][ codes of 2 k-blocks | scale words ], where the
-// codes of one k-block are [chunk][row 0..127][16 bytes] and the scale words are
+// codes of a stage are [chunk][position 0..127][16 bytes] and the scale words are
 // [word][row 0..127][4 bytes]. One (n_tile, stage) record is contiguous, so the
-// kernel fetches it with a single bulk copy, and the dequant thread of row r
-// reads chunk c at byte c*2048 + r*16: consecutive rows hit consecutive 16-byte
-// slots, which is bank-conflict free. The scale words of the k-blocks travel in
-// the same record, so the dequant warps never touch global memory. K is padded
-// to a whole stage with zero codes and zero scales.
+// kernel fetches it with a single bulk copy. Chunk c (counted over the whole stage) of
+// row r sits at position r ^ (2c & 6) of its 2 KiB slab. Both readers are then free
+// of shared-memory bank conflicts: the tcgen05 dequant thread of row r reads chunk c
+// at byte c*2048 + (r ^ (2c & 6))*16 (consecutive rows, one chunk: a permutation of 8
+// consecutive 16-byte slots), and a lane quad of the small-M kernel reads chunks 0..3
+// of rows r and r+1 (eight different slots modulo 8). The scale words of the k-blocks
+// travel in the same record, so the dequant warps never touch global memory. K is
+// padded to a whole stage with zero codes and zero scales.
 //
 // Inside a 32-bit word the codes are permuted for the shift-and-mask decoders
 // (decode.cuh). For integer codes this is the permutation of the reference's
@@ -20,6 +23,8 @@
 #include <cstdint>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+
+#include "decode.cuh"
 
 namespace b200dq {
 
@@ -88,8 +93,9 @@ __global__ void pack_image_kernel(const PackParams p) {
     const int h = wi / p.code_words_per_kb;
     const int r = wi % p.code_words_per_kb;
     const int j = r & 3;
-    const int row = (r >> 2) & 127;
     const int c = r >> 9;
+    const int chunk_in_stage = h * (p.code_words_per_kb >> 9) + c;
+    const int row = ((r >> 2) & 127) ^ chunk_swizzle(chunk_in_stage);   // the row stored at this position
     const int n = nt * 128 + row;
     const int elems_per_word = 32 / p.bits;
     const int k0 = (stg * 2 + h) * p.elems_per_kblock + (c * 4 + j) * elems_per_word;

@@ -93,6 +93,22 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// try_wait with a suspend-time hint (nanoseconds): the hardware may park the thread until
+// the phase completes or the hint runs out, instead of returning after its short default
+// limit. A parked thread issues nothing; a thread that spins on the plain form competes
+// for issue slots with the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait. `abort_flag` lives in shared memory; once set, every wait of the
 // CTA returns at once. Returns false if the wait gave up (or the CTA aborted).
 static __device__ __noinline__ void mbar_wait_failed(volatile int* abort_flag, DeviceStatus* st,
@@ -112,8 +128,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   uint64_t t0 = 0;
   uint32_t it = 0;
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (((++it) & 0x3f) == 0) {
+    // parked by the hardware for up to 20 us per probe, so this loop turns rarely
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+    if (((++it) & 0x7) == 0) {
       if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;

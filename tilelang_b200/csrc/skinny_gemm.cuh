@@ -2,26 +2,34 @@
 // with W dequantised in registers from the same packed image the tcgen05 kernel streams.
 //
 // With so few tokens the tcgen05 pipeline (TMA -> registers -> TMEM -> MMA, a chain of
-// barrier hand-offs per k-block) is latency-bound far below HBM speed. Here every warp is
-// independent: it reads packed codes straight from global memory with 128-bit loads (a
-// bulk L2 prefetch runs a few stages ahead), decodes them with the same register
-// routines, and multiplies with warp-level mma.sync.m16n8k16 -- weights are the 16-row
-// operand, tokens the 8-column one -- so the only waits are the hardware scoreboard's.
-// The reference's counterpart is its split-K SIMT GEMV (examples/dequantize_gemm/
-// example_dequant_gemv_fp16xint4.py:21-136, examples/gemv/example_gemv.py:58-96).
-// Measured alternatives that lost on B200: a plain SIMT variant on the mixed-precision
-// scalar FMA (fma.rn.f32.bf16) for 1-2 tokens, and a lane-private cp.async ring in
-// shared memory in place of the direct loads. mma.sync.m16n8k16 (bf16) sustains one
-// instruction per 8 cycles per SM sub-partition here (dependent-issue latency 21 cycles), so
-// the legacy tensor path is not the limit (1.5 k to 3.1 k instructions per sub-partition on
-// the 28672 x 8192 benchmark weight). 4-bit integer weights (with or without scales) and
-// e2m1 weights with e8m0 block scales take this path.
+// barrier hand-offs per k-block) is latency-bound far below HBM speed. This kernel is built
+// around the memory stream instead: four producer threads keep a deep shared-memory ring
+// full (one cp.async.bulk per packed stage plus one tiled TMA of the activations of the
+// same 128 k), so the bytes in flight per SM do not depend on what the compute warps are
+// doing; 16 consumer warps decode and multiply with warp-level mma.sync.m16n8k16 (weights
+// are the 16-row operand, tokens the 8-column one). The reference's counterpart is its
+// split-K SIMT GEMV (examples/dequantize_gemm/example_dequant_gemv_fp16xint4.py:21-136,
+// examples/gemv/example_gemv.py:58-96). 4-bit integer weights (with or without scales)
+// and e2m1 weights with e8m0 block scales take this path.
 //
 // Work split: the same stream-K schedule, segments and scratch format as the tcgen05
-// kernel (token tile 16), so the same fix-up pass finishes tiles cut between CTAs. Inside
-// a CTA, warp w takes weight rows [64 * (w & 1), +64) of the 128-row tile and the stages
-// st_begin + (w >> 1), + 8, ...; the 8 partial sums of every output are added in a fixed
-// order through shared memory when the segment ends (deterministic).
+// kernel (token tile 16), so the same fix-up pass finishes tiles cut between CTAs. A ring
+// slot holds one stage (128 rows x 128 k of codes, their scale words, and the tokens'
+// 128 k). The consumer warps form four teams of four; team t takes the slots whose
+// CTA-wide index is t modulo 4, warp r of the team the weight rows [32 r, +32). The four
+// warps of one SM sub-partition belong to four different teams, which run out of phase, so
+// the load, decode and MMA phases of different slots overlap on the sub-partition's pipes
+// (with two teams in lockstep the phases added up instead). The four partial sums of every
+// output (one per team) are added in a fixed order through shared memory when the segment
+// ends (deterministic). The ring depth is a multiple of 4, so a team meets every phase of
+// the barriers of its slots: a parity wait cannot tell "two phases behind" from "done".
+//
+// Every format is dequantised completely in registers with the routines of the tcgen05
+// kernel (decode.cuh), so both kernels multiply the same 16-bit weights and differ only in the
+// order of the fp32 additions. (Applying the group scale to per-stage fp32 sums instead --
+// one packed fma less per code pair -- was measured 5 % faster at 1 token and slower at 16,
+// and it no longer rounds each weight to 16 bits the way the reference's ref_program does; it
+// was not kept.)
 //
 // Fragment mapping. The instruction fixes which lane holds which (row, k) slot: lanes
 // 4j..4j+3 hold rows j and j+8, lane l the k slots {2q, 2q+1, 2q+8, 2q+9}, q = l % 4. A
@@ -29,29 +37,65 @@
 // agree, so lane (j, q) loads the 16-byte chunk q of rows j and j+8 (32 consecutive k
 // each) and MMA i of 8 uses the lane's real k = 32q + 4i .. 4i+3 for its four slots; the
 // activation fragment is then 8 contiguous bytes of the token row.
+//
+// Shared-memory reads are bank-conflict free: the image stores chunk c of row r at
+// 16-byte position r ^ 2c of its slab (pack_kernels.cuh), and the activations arrive
+// through a 4-D tensor map {64 k, k-block parity, token, stage} with the 128-byte swizzle,
+// which places (token t, parity p) in row 2t + p.
 #pragma once
 #include "skinny_launch.h"
 #include "umma_gemm.cuh"
 
 namespace b200dq {
 
-constexpr int kSkinnyThreads = 512;
-constexpr int kSkinnyRedStride = kTileRows + 4;      // padded row pitch of the reduction buffer (floats)
-constexpr int kSkinnyPhases = kSkinnyThreads / 64;   // mma.sync kernel: 2 row halves x 8 phases
-constexpr int kSkinnySmemBytes = kSkinnyPhases * kSkinnyTokens * kSkinnyRedStride * 4;
-#ifndef B200DQ_SKINNY_PREFETCH
-#define B200DQ_SKINNY_PREFETCH 2                     // stages (per warp) requested into L2 ahead of use
-#endif
+constexpr int kSkinnyTeams = 4;                         // consumer teams = partial sums per output
+constexpr int kSkinnyConsumerWarps = 4 * kSkinnyTeams;
+constexpr int kSkinnyConsumers = kSkinnyConsumerWarps * 32;
+constexpr int kSkinnyProducerWarps = 4;
+constexpr int kSkinnyThreads = kSkinnyConsumers + kSkinnyProducerWarps * 32;
+constexpr int kSkinnyRedStride = kTileRows + 4;         // padded row pitch of the reduction buffer (floats)
+constexpr int kSkinnyCtlBytes = 1024;
+constexpr int kSkinnyMaxSlots = 16;
+// Registers per thread after the hand-over (multiples of 8): 128 x 32 + 512 x 112 is exactly
+// the 640 x 96 the launch reserved.
+constexpr int kSkinnyProducerRegs = 32;
+constexpr int kSkinnyConsumerRegs = 112;
 
-__device__ __forceinline__ uint4 ldg_stream_v4(const void* ptr) {
-  uint4 v;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(ptr));
-  return v;
+// Shared-memory plan of one kernel instance. NT = 8-token column blocks (1 or 2).
+template <int NT, int WF>
+struct SkinnyRing {
+  static constexpr int kTok = NT * 8;
+  static constexpr int kWStage = 2 * codes_per_kblock_bytes(WF) + sz_smem_bytes(WF);  // largest packed stage
+  static constexpr int kWSlot = (kWStage + 1023) / 1024 * 1024;
+  static constexpr int kASlot = kTok * 256;              // activations of the stage: [token][parity][128 B]
+  static constexpr int kSlot = kASlot + kWSlot;          // activations first: their swizzle needs a 1 KiB aligned base
+  static constexpr int kRedBytes = kSkinnyTeams * kTok * kSkinnyRedStride * 4;
+  static constexpr int kFit = (232448 - 1024 /*align*/ - kSkinnyCtlBytes - kRedBytes) / kSlot;
+  static constexpr int kSlots = (kFit > kSkinnyMaxSlots ? kSkinnyMaxSlots : kFit) & ~(kSkinnyTeams - 1);
+  static constexpr int kSmemBytes = 1024 + kSkinnyCtlBytes + kRedBytes + kSlots * kSlot;
+  static_assert(kSlot % 1024 == 0 && kASlot % 1024 == 0, "slot and code bases keep their alignment");
+  static_assert(kSlots >= 2 * kSkinnyTeams, "every team needs a slot to work on and one in flight");
+};
+
+struct SkinnyCtl {
+  uint64_t full[kSkinnyMaxSlots];
+  uint64_t empty[kSkinnyMaxSlots];
+  int abort_flag;
+};
+static_assert(sizeof(SkinnyCtl) <= kSkinnyCtlBytes, "control block must fit its slot");
+
+// 4-D tiled load; c0 * element_size must stay a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_4d(void* smem_dst, const CUtensorMap* tmap, int c0, int c1, int c2, int c3,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cta.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(smem_u32(smem_dst)),
+      "l"(tmap), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(smem_u32(bar))
+      : "memory");
 }
 
-__device__ __forceinline__ void prefetch_l2_bulk(const void* ptr, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(ptr), "r"(bytes) : "memory");
+__device__ __forceinline__ void skinny_consumer_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kSkinnyConsumers) : "memory");
 }
 
 template <bool kBf16>
@@ -68,6 +112,15 @@ __device__ __forceinline__ void mma_m16n8k16(float (&d)[4], uint32_t a0, uint32_
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
   }
+}
+
+// Warp-wide wait on a ring barrier. The common case (the copy landed long ago) costs one
+// probe by the whole warp; otherwise lane 0 alone polls, so that 32 spinning lanes do not
+// flood the shared-memory pipe the producers' issues and every arrive go through.
+__device__ __forceinline__ bool skinny_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                            DeviceStatus* st, uint32_t site, int lane) {
+  if (mbar_test_wait(bar, parity)) return true;
+  return mbar_wait_warp(bar, parity, abort_flag, st, site, lane);
 }
 
 // `sz` is the row's scale word of the stage; `q` the lane's chunk (uint4: one {scale, zero}
@@ -102,136 +155,194 @@ __device__ __forceinline__ void skinny_store(const GemmParams& p, const Segment&
 }
 
 // ---------------------------------------------------------------------------------------
-// mma.sync kernel. NT: 8-token column blocks (1 for M <= 8, else 2).
-// Warp w: rows [64 * (w & 1), +64) of the tile, phase w >> 1.
+// NT: 8-token column blocks (1 for M <= 8, else 2).
 // ---------------------------------------------------------------------------------------
 template <int NT, int WF, int ACT>
-__global__ void __launch_bounds__(kSkinnyThreads, 1) skinny_dequant_gemm_kernel(const GemmParams p) {
+__global__ void __launch_bounds__(kSkinnyThreads, 1)
+skinny_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
   static_assert(WF == WF_U4_SZ || WF == WF_U4_RAW || WF == WF_S4_RAW || WF == WF_FP4_E8M0,
                 "4-bit weights on 16-bit activations");
   static_assert(WF != WF_FP4_E8M0 || ACT == ACT_BF16, "e2m1 weights decode to bf16");
+  using Ring = SkinnyRing<NT, WF>;
   constexpr bool kBf16 = (ACT == ACT_BF16);
-  constexpr int PH = kSkinnyPhases;
-  constexpr int PD = B200DQ_SKINNY_PREFETCH;
+  constexpr int RING = Ring::kSlots;
+  constexpr int kTok = Ring::kTok;
   constexpr int kCodeBytes = 2 * codes_per_kblock_bytes(WF);   // 8192: four 2 KiB chunk slabs
-  extern __shared__ float red[];                               // [phase][token][row (padded)]
+
+  extern __shared__ uint8_t skinny_smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(skinny_smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* ring = smem;                                                 // RING x (activations | packed stage)
+  float* red = reinterpret_cast<float*>(ring + RING * Ring::kSlot);     // [team][token][row (padded)]
+  SkinnyCtl* ctl = reinterpret_cast<SkinnyCtl*>(reinterpret_cast<uint8_t*>(red) + Ring::kRedBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int half = warp & 1;
-  const int phase = warp >> 1;
-  const int j = lane >> 2;
-  const int q = lane & 3;
-  const uint16_t* A = reinterpret_cast<const uint16_t*>(p.a);
+  volatile int* abort_flag = &ctl->abort_flag;
+  DeviceStatus* st_word = p.status;
 
-  SegmentWalk walk(p);
-  Segment w;
-  while (walk.next(p, w)) {
-    float acc[4][NT][4];
-#pragma unroll
-    for (int mt = 0; mt < 4; ++mt)
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int c = 0; c < 4; ++c) acc[mt][nt][c] = 0.f;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < RING; ++i) {
+      mbar_init(&ctl->full[i], 1);
+      mbar_init(&ctl->empty[i], 4);   // the four warps of the slot's team
+    }
+    ctl->abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kSkinnyConsumerWarps && lane == 0) tma_prefetch_desc(&tmap_a);
+  __syncthreads();
 
-    const uint8_t* tile_base = p.wp + w.wp_off + static_cast<size_t>(w.n_tile) * p.st_total * p.stage_bytes;
-    const bool prefetcher = (PD > 0) && half == 0 && lane == 0;
-    if (prefetcher) {
-#pragma unroll
-      for (int d = 0; d < PD; ++d) {
-        const int s = w.st_begin + phase + PH * d;
-        if (s < w.st_end) prefetch_l2_bulk(tile_base + static_cast<size_t>(s) * p.stage_bytes, p.stage_bytes);
+  // The launch gives every thread the same register count (what 20 warps can share). The
+  // producer warpgroup hands most of its registers back and the consumer warpgroups take
+  // them: the consumers' fragments, decoded weights and sums need more than the even split.
+  if (warp >= kSkinnyConsumerWarps) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kSkinnyProducerRegs));
+    // ---------------- producers ----------------
+    // Four issuing threads, one per warp; producer t fills the slots of team t: one bulk copy
+    // of the packed stage and one tiled TMA of the activations of its 128 k. The schedule is
+    // dense with one token tile, so unit u of the (tile, stage) space is stage u % st_total of
+    // K and its packed bytes start at u * stage_bytes: no segment walk needed.
+    const uint32_t team = static_cast<uint32_t>(warp - kSkinnyConsumerWarps);
+    if (lane == 0) {
+      const long long pos0 = static_cast<long long>(blockIdx.x) * p.span;
+      const uint32_t n_slots = static_cast<uint32_t>(min(static_cast<long long>(p.span), p.units - pos0));
+      uint32_t slot = team, phase = 0;
+      for (uint32_t cnt = team; cnt < n_slots; cnt += kSkinnyTeams) {
+        if (!mbar_wait(&ctl->empty[slot], phase ^ 1u, abort_flag, st_word, 11)) break;
+        uint8_t* dst = ring + slot * Ring::kSlot;
+        mbar_arrive_expect_tx(&ctl->full[slot], static_cast<uint32_t>(p.stage_bytes) + Ring::kASlot);
+        tma_bulk_g2s(dst + Ring::kASlot, p.wp + static_cast<size_t>(pos0 + cnt) * p.stage_bytes,
+                     static_cast<uint32_t>(p.stage_bytes), &ctl->full[slot]);
+        tma_load_4d(dst, &tmap_a, 0, 0, 0, static_cast<int>((pos0 + cnt) % p.st_total), &ctl->full[slot]);
+        slot += kSkinnyTeams;
+        if (slot >= static_cast<uint32_t>(RING)) { slot -= RING; phase ^= 1u; }
       }
     }
-    // the lane's token rows (one per 8-token block)
-    const uint16_t* arow[NT];
-    bool tok_ok[NT];
+  } else {
+    // ---------------- consumers ----------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kSkinnyConsumerRegs));
+    const uint32_t team = static_cast<uint32_t>(warp >> 2);
+    const int rq = warp & 3;           // 32-row quarter of the tile
+    const int j = lane >> 2;
+    const int q = lane & 3;
+    const int row_lo = rq * 32 + j;
+    // Per-lane byte offsets inside a slot, fixed for the whole kernel, so that every load of
+    // the inner loop is base + constant.
+    // Activations of (token t, this lane's 32 k): row 2t + (q >> 1) of the stage's block,
+    // 16-byte chunks 4 (q & 1) + v, v = 0..3, swizzled with the row index.
+    const int a_par = q >> 1;
+    const uint32_t a_xor = static_cast<uint32_t>((2 * j + a_par) & 7);
+    uint32_t a_off[4];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const int t = w.row0 + nt * 8 + j;
-      tok_ok[nt] = t < w.row_end;
-      arow[nt] = A + static_cast<size_t>(tok_ok[nt] ? t : 0) * p.K;
-    }
-    const int row_lo = half * 64 + j;
+    for (int v = 0; v < 4; ++v)
+      a_off[v] = static_cast<uint32_t>(j * 256 + a_par * 128) + (((static_cast<uint32_t>(4 * (q & 1)) + v) ^ a_xor) << 4);
+    // Codes: chunk q of row r at q * 2048 + (r ^ chunk_swizzle(q)) * 16. The swizzle touches
+    // bits 1-2 of the row only, so the rows j + 8, + 16, + 24 of this lane are the first one
+    // plus a constant.
+    const uint32_t c_off = static_cast<uint32_t>(Ring::kASlot + q * 2048) +
+                           ((static_cast<uint32_t>(row_lo) ^ static_cast<uint32_t>(chunk_swizzle(q))) << 4);
+    // Scale words: [word][row], 4 bytes each; with one word per k-block the lane's chunk picks it.
+    const uint32_t z_off = static_cast<uint32_t>(Ring::kASlot + kCodeBytes + (p.sz_per_kb ? (q >> 1) * 512 : 0) +
+                                                 row_lo * 4);
 
-    for (int st = w.st_begin + phase; st < w.st_end; st += PH) {
-      const uint8_t* stage = tile_base + static_cast<size_t>(st) * p.stage_bytes;
-      if (prefetcher) {
-        const int s = st + PH * PD;
-        if (s < w.st_end) prefetch_l2_bulk(tile_base + static_cast<size_t>(s) * p.stage_bytes, p.stage_bytes);
-      }
-      // ---- all loads of the stage first: 8 code chunks, their scale words, the activations
-      uint4 codes[4][2];
-      uint32_t szw[4][2];
+    uint32_t my_cnt = team;            // CTA-wide index of this team's next slot
+    uint32_t slot = team, phase = 0;
+    uint32_t cnt0 = 0;                 // slots of this CTA before the current segment
+    bool ok = true;
+
+    SegmentWalk walk(p);
+    Segment w;
+    while (walk.next(p, w)) {
+      float acc[2][NT][4];
 #pragma unroll
-      for (int mt = 0; mt < 4; ++mt) {
+      for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int r = row_lo + mt * 16 + h * 8;
-          codes[mt][h] = ldg_stream_v4(stage + q * 2048 + r * 16);
-          if constexpr (WF == WF_U4_SZ) {
-            const int si = p.sz_per_kb ? (q >> 1) : 0;
-            szw[mt][h] = __ldg(reinterpret_cast<const uint32_t*>(stage + kCodeBytes + si * 512) + r);
-          } else if constexpr (WF == WF_FP4_E8M0) {
-            szw[mt][h] = __ldg(reinterpret_cast<const uint32_t*>(stage + kCodeBytes) + r);
-          } else {
-            szw[mt][h] = 0;
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[mt][nt][c] = 0.f;
+
+      const uint32_t nst = static_cast<uint32_t>(w.st_end - w.st_begin);
+      for (; my_cnt < cnt0 + nst; my_cnt += kSkinnyTeams) {
+        ok &= skinny_wait(&ctl->full[slot], phase, abort_flag, st_word, 13, lane);
+        if (ok) {
+          const uint8_t* slot_base = ring + slot * Ring::kSlot;
+          // ---- the lane's activations: 32 k of token j (and j + 8)
+          uint32_t b[NT][16];
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            const uint8_t* src = slot_base + a_off[v];
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+              const uint4 t = *reinterpret_cast<const uint4*>(src + nt * (8 * 256));
+              b[nt][4 * v] = t.x; b[nt][4 * v + 1] = t.y; b[nt][4 * v + 2] = t.z; b[nt][4 * v + 3] = t.w;
+            }
+          }
+          const uint8_t* c_src = slot_base + c_off;
+          const uint8_t* z_src = slot_base + z_off;
+          // ---- decode and multiply, one 16-row block at a time
+#pragma unroll
+          for (int mt = 0; mt < 2; ++mt) {
+            uint4 codes[2];
+            uint32_t szw[2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+              codes[hh] = *reinterpret_cast<const uint4*>(c_src + (mt * 16 + hh * 8) * 16);
+              if constexpr (WF == WF_U4_SZ || WF == WF_FP4_E8M0)
+                szw[hh] = *reinterpret_cast<const uint32_t*>(z_src + (mt * 16 + hh * 8) * 4);
+              else
+                szw[hh] = 0;
+            }
+            uint32_t wa[16], wb[16];
+            skinny_decode<WF, kBf16>(p, codes[0], szw[0], q, wa);
+            skinny_decode<WF, kBf16>(p, codes[1], szw[1], q, wb);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                mma_m16n8k16<kBf16>(acc[mt][nt], wa[2 * i], wb[2 * i], wa[2 * i + 1], wb[2 * i + 1], b[nt][2 * i],
+                                    b[nt][2 * i + 1]);
+            }
           }
         }
+        // every lane has read its part of the slot
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&ctl->empty[slot]);
+        slot += kSkinnyTeams;
+        if (slot >= static_cast<uint32_t>(RING)) { slot -= RING; phase ^= 1u; }
       }
-      const int k0 = st * 128 + q * 32;
-      uint4 av[NT][4];
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        if (tok_ok[nt] && k0 < p.K) {
-          const uint4* src = reinterpret_cast<const uint4*>(arow[nt] + k0);
-#pragma unroll
-          for (int v = 0; v < 4; ++v) av[nt][v] = __ldg(src + v);
-        } else {
-#pragma unroll
-          for (int v = 0; v < 4; ++v) av[nt][v] = make_uint4(0u, 0u, 0u, 0u);
-        }
-      }
-      // ---- decode and multiply, one 16-row block at a time
-#pragma unroll
-      for (int mt = 0; mt < 4; ++mt) {
-        uint32_t wa[16], wb[16];
-        skinny_decode<WF, kBf16>(p, codes[mt][0], szw[mt][0], q, wa);
-        skinny_decode<WF, kBf16>(p, codes[mt][1], szw[mt][1], q, wb);
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const uint32_t* b = reinterpret_cast<const uint32_t*>(&av[nt][0]);
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            mma_m16n8k16<kBf16>(acc[mt][nt], wa[2 * i], wb[2 * i], wa[2 * i + 1], wb[2 * i + 1], b[2 * i], b[2 * i + 1]);
-        }
-      }
-    }
+      cnt0 += nst;
 
-    // ---- add the phases' partial sums in a fixed order
-    __syncthreads();   // the previous segment's readers are done with the buffer
+      // ---- add the teams' partial sums of every output in a fixed order
+      skinny_consumer_sync();   // the previous segment's readers are done with the buffer
 #pragma unroll
-    for (int mt = 0; mt < 4; ++mt)
+      for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const int row = half * 64 + mt * 16 + j + (c >> 1) * 8;
-          const int tok = nt * 8 + 2 * q + (c & 1);
-          red[(phase * kSkinnyTokens + tok) * kSkinnyRedStride + row] = acc[mt][nt][c];
-        }
-    __syncthreads();
-    const int n_tok = NT * 8;
-    for (int o = threadIdx.x; o < n_tok * kTileRows; o += kSkinnyThreads) {
-      const int tok = o >> 7;
-      const int row = o & (kTileRows - 1);
-      float v = 0.f;
+          for (int c = 0; c < 4; ++c) {
+            const int row = rq * 32 + mt * 16 + j + (c >> 1) * 8;
+            const int tok = nt * 8 + 2 * q + (c & 1);
+            red[(team * kTok + tok) * kSkinnyRedStride + row] = acc[mt][nt][c];
+          }
+      skinny_consumer_sync();
+      for (int o = threadIdx.x; o < kTok * kTileRows; o += kSkinnyConsumers) {
+        const int tok = o >> 7;
+        const int row = o & (kTileRows - 1);
+        float v = 0.f;
 #pragma unroll
-      for (int ph = 0; ph < PH; ++ph) v += red[(ph * kSkinnyTokens + tok) * kSkinnyRedStride + row];
-      skinny_store(p, w, tok, row, v);
+        for (int t = 0; t < kSkinnyTeams; ++t) v += red[(t * kTok + tok) * kSkinnyRedStride + row];
+        skinny_store(p, w, tok, row, v);
+      }
     }
   }
+
+  // ---------------- teardown ----------------
+  if (*abort_flag) {
+    // give copies that may still be in flight time to land before the CTA's
+    // shared memory goes away
+    const uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
+  }
+  __syncthreads();
 }
 
 }  // namespace b200dq

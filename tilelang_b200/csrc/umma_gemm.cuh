@@ -52,15 +52,6 @@
 
 namespace b200dq {
 
-#ifdef B200DQ_PROFILE
-#define PROF_DECL(name) long long name = 0
-#define PROF_T0(t) long long t = clock64()
-#define PROF_ADD(acc, t) do { long long _n = clock64(); acc += _n - t; t = _n; } while (0)
-#else
-#define PROF_DECL(name)
-#define PROF_T0(t)
-#define PROF_ADD(acc, t)
-#endif
 
 enum WeightFormat : int {
   WF_U4_SZ = 0,       // uint4, per-group scale + zero (16-bit activations)
@@ -110,7 +101,6 @@ struct GemmParams {
   int num_groups;
   int tn;                        // tokens per tile (the kernel's TN)
   DeviceStatus* status;
-  unsigned long long* prof;  // optional per-CTA phase timers (profiling builds only)
 };
 
 constexpr int kTileRows = 128;        // weight rows per CTA tile (= TMEM lanes)
@@ -345,9 +335,6 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
   constexpr int BKE = kInt ? 128 : 64;   // K elements per k-block
   constexpr int NV = TN >= 32 ? 32 : 16; // accumulator columns per tcgen05.ld
 
-#ifdef B200DQ_PROFILE
-  __shared__ long long prof_ts_b[8];   // issue time of the activation load in each ring slot
-#endif
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_b = smem;                                   // NBG x (GB x TN x 128 B), 1024-aligned slabs
@@ -424,9 +411,6 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
           } else {
             mbar_wait(&ctl->empty_b[s], ((gc / NBG) & 1) ^ 1, abort_flag, st, 2);
           }
-#ifdef B200DQ_PROFILE
-          prof_ts_b[s] = clock64();
-#endif
           mbar_arrive_expect_tx(&ctl->full_b[s], static_cast<uint32_t>(gsz) * Ring::kBSlabBytes);
           if (GB == 1 || gsz == 1)
             tma_load_2d(smem_b + s * Ring::kBGroupBytes, &tmap_a, kb * BKE, w.row0, &ctl->full_b[s]);
@@ -460,9 +444,6 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
       bool ok = true;
       SegmentWalk walk(p);
       Segment w;
-      PROF_DECL(pm_loop); PROF_DECL(pm_a); PROF_DECL(pm_b); PROF_DECL(pm_acc); PROF_DECL(pm_turn); PROF_DECL(pm_issue);
-      PROF_DECL(pm_commit); PROF_DECL(pm_n);
-      PROF_T0(tm);
       while (walk.next(p, w)) {
         const int nst = w.st_end - w.st_begin;
         // my stages of the segment: those whose CTA-wide index g0 + i has my parity
@@ -472,20 +453,14 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
           const uint32_t grp0 = gc0 + (static_cast<uint32_t>(2 * i) >> gshift);
           const uint32_t grp1 = gc0 + (static_cast<uint32_t>(2 * i + 1) >> gshift);
           const uint32_t sb0 = grp0 % NBG, sb1 = grp1 % NBG;
-          PROF_ADD(pm_loop, tm);
           ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
-          PROF_ADD(pm_a, tm);
           ok &= mbar_wait(&ctl->full_b[sb0], (grp0 / NBG) & 1u, abort_flag, st, 5);
-          PROF_ADD(pm_b, tm);
           if (grp1 != grp0) ok &= mbar_wait(&ctl->full_b[sb1], (grp1 / NBG) & 1u, abort_flag, st, 5);
-          PROF_ADD(pm_b, tm);
           if (i < NI) ok &= mbar_wait(&ctl->acc_empty, (tc & 1u) ^ 1u, abort_flag, st, 3);   // my first stage here
-          PROF_ADD(pm_acc, tm);
           if (NI == 1 && !first_ever) {
             ok &= mbar_wait(&ctl->turn[me], my_turns & 1u, abort_flag, st, 9);
             ++my_turns;
           }
-          PROF_ADD(pm_turn, tm);
           tc_fence_after_sync();
           if (ok) {
 #pragma unroll
@@ -502,7 +477,6 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
               }
             }
           }
-          PROF_ADD(pm_issue, tm);
           if constexpr (NI == 1) {
             tc_fence_before_sync();
             mbar_arrive(&ctl->turn[me ^ 1]);
@@ -516,10 +490,6 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
             if (gsz == 4 && (i & 1) == 0 && i == nst - 1) mbar_arrive(&ctl->empty_b[sb0]);
           }
           if (NI == 1 ? (i == nst - 1) : (i + 2 >= nst)) tc_commit(&ctl->acc_full);   // my last stage here
-          PROF_ADD(pm_commit, tm);
-#ifdef B200DQ_PROFILE
-          ++pm_n;
-#endif
           sa += 4; if (sa >= static_cast<uint32_t>(NS)) { sa -= NS; pa ^= 1u; }
         }
         // a one-stage segment leaves the other issuer without work: it still owes its arrival
@@ -533,9 +503,6 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
         gc0 += (static_cast<uint32_t>(2 * nst) + gmask) >> gshift;
         ++tc;
       }
-#ifdef B200DQ_PROFILE
-      if (p.prof && me == 0) { unsigned long long* o = p.prof + blockIdx.x * 32; o[0] = pm_acc; o[1] = pm_a; o[2] = pm_b; o[3] = pm_issue; o[4] = pm_n; o[5] = pm_commit; o[6] = pm_turn; o[7] = pm_loop; }
-#endif
     }
   } else if (warp >= 4 && warp < 12) {
     // ---------------- dequant warpgroups: group d takes stage d of every pair ----
@@ -548,15 +515,11 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
     bool ok = true;
     SegmentWalk walk(p);
     Segment w;
-    PROF_DECL(pd_w); PROF_DECL(pd_dec); PROF_DECL(pd_a); PROF_DECL(pd_st); PROF_DECL(pd_n);
-    PROF_T0(td);
     while (walk.next(p, w)) {
       for (int sti = w.st_begin; sti < w.st_end; sti += 2, ++wc) {
         const int n = min(2, w.st_end - sti);
         const uint32_t sw = wc % NWP;
-        PROF_ADD(pd_dec, td);
         ok &= mbar_wait(&ctl->full_w[sw], (wc / NWP) & 1, abort_flag, st, 6);
-        PROF_ADD(pd_w, td);
         const bool mine = dg < n;
         const uint8_t* stage = smem_w + sw * WPS + dg * p.stage_bytes;
         constexpr int CH = CPK / 2048;            // 16-byte chunks per row and k-block
@@ -576,7 +539,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
             const int h = it / CH, q = it % CH;
             const uint32_t kc = kc0 + dg * 2 + h;
             const uint32_t sa = kc % NS;
-            const uint4 cq = codes[it * 128 + row_in_tile];
+            const uint4 cq = codes[it * 128 + (row_in_tile ^ chunk_swizzle(it))];
             if (it == 2 * CH - 1) {
               // every thread of this warp has issued its last read of the stage
               __syncwarp();
@@ -596,14 +559,12 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
             } else {
               decode_i2_chunk(cq, p.code_bias, regs);
             }
-            PROF_ADD(pd_dec, td);
             if (q == 0) {
               if (h == 0 && kc >= static_cast<uint32_t>(NS)) {
                 const uint32_t prev = kc - NS;   // first k-block of the stage that used these two slots
                 ok &= mbar_wait(&ctl->cons[sa >> 1], (prev / NS) & 1, abort_flag, st, 7);
               }
               tc_fence_after_sync();
-              PROF_ADD(pd_a, td);
             }
             const uint32_t dst = tmem_base + lane_addr + kAccCols + sa * 32 + q * RPC;
             if constexpr (RPC == 16) tmem_st_32x32b_x16(dst, regs);
@@ -615,12 +576,8 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
               tc_fence_before_sync();
               __syncwarp();
               if (lane == 0) mbar_arrive(&ctl->a_full[sa - 1]);
-              PROF_ADD(pd_st, td);
             }
           }
-#ifdef B200DQ_PROFILE
-          ++pd_n;
-#endif
         } else {
           __syncwarp();
           if (lane == 0) mbar_arrive(&ctl->empty_w[sw]);
@@ -628,9 +585,6 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
         kc0 += 2 * n;
       }
     }
-#ifdef B200DQ_PROFILE
-    if (p.prof && lane == 0 && quarter == 0) { unsigned long long* o = p.prof + blockIdx.x * 32 + 8 + dg * 8; o[0] = pd_w; o[1] = pd_dec; o[2] = pd_a; o[3] = pd_st; o[4] = pd_n; }
-#endif
     (void)ok;
   } else if (warp >= 12) {
     // ---------------- epilogue ----------------
@@ -645,8 +599,6 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
     bool ok = true;
     SegmentWalk walk(p);
     Segment w;
-    PROF_DECL(pe_wait); PROF_DECL(pe_ld); PROF_DECL(pe_store);
-    PROF_T0(te);
     while (walk.next(p, w)) {
       const int n0_warp = w.n_tile * kTileRows + quarter * 32;
       const int n = n0_warp + lane;
@@ -658,7 +610,6 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
       (void)nkb;
       ok &= mbar_wait(&ctl->acc_full, tc & 1, abort_flag, st, 8);
       tc_fence_after_sync();
-      PROF_ADD(pe_wait, te);
       auto store_chunk = [&](const uint32_t (&acc)[NV], int c) {
         const int m0 = w.row0 + c * NV;
         if (w.slot >= 0) {
@@ -700,15 +651,11 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
         for (int c = 0; c < TN / NV; c += 2) {
           tc_wait_ld();
           tmem_ld_32x32b_x32(tmem_base + lane_addr + (c + 1) * NV, buf_b);
-          PROF_ADD(pe_ld, te);
           store_chunk(buf_a, c);
-          PROF_ADD(pe_store, te);
           tc_wait_ld();
           if (c + 2 < TN / NV) tmem_ld_32x32b_x32(tmem_base + lane_addr + (c + 2) * NV, buf_a);
           else release_acc();
-          PROF_ADD(pe_ld, te);
           store_chunk(buf_b, c + 1);
-          PROF_ADD(pe_store, te);
         }
       } else {
 #pragma unroll 1
@@ -734,17 +681,12 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
               }
             }
           }
-          PROF_ADD(pe_ld, te);
           if (c == TN / NV - 1) release_acc();
           store_chunk(acc, c);
-          PROF_ADD(pe_store, te);
         }
       }
       ++tc;
     }
-#ifdef B200DQ_PROFILE
-    if (p.prof && lane == 0 && quarter == 0) { unsigned long long* o = p.prof + blockIdx.x * 32 + 24; o[0] = pe_wait; o[1] = pe_ld; o[2] = pe_store; o[3] = tc; }
-#endif
     (void)ok;
   }
 

@@ -14,7 +14,7 @@ Weights arrive in the reference's natural packed layout (two uint4 per byte alon
 K, low nibble first: example_dequant_gemm_fine_grained.py:11-13,
 quantize/utils.py:50-67). The kernels stream a private pre-tiled image, so the
 first call with a given weight tensor repacks it on the device
-(``ops.pack_*``) and caches the image, keyed by the tensors' storage and version;
+(``ops.pack_*``) and caches the image, keyed by the tensor objects and their versions;
 ``kernel.pack(...)`` does the same ahead of time.
 """
 from __future__ import annotations
@@ -89,18 +89,25 @@ class DequantKernel:
         return self._packed(*weight_tensors)
 
     def _packed(self, *tensors) -> ops.PackedWeight:
-        key = tuple((t.data_ptr(), t._version, tuple(t.shape)) if t is not None else None for t in tensors)
+        """The packed image of these weight tensors, repacked unless the cache holds an image
+        made from the very same tensor objects at the same version. An entry keeps its source
+        tensors alive: a storage address alone does not identify a weight, because the
+        allocator hands a freed address to the next tensor of the same size."""
+        key = tuple(id(t) if t is not None else None for t in tensors)
         hit = self._cache.get(key)
-        if hit is None:
-            hit = self._pack_fn(*tensors)
-            if len(self._cache) >= 64:
-                self._cache.clear()
-            self._cache[key] = hit
-        return hit
+        if hit is not None:
+            sources, versions, packed = hit
+            if all(a is b for a, b in zip(sources, tensors)) and versions == self._versions(tensors):
+                return packed
+        packed = self._pack_fn(*tensors)
+        if len(self._cache) >= 16:
+            self._cache.clear()
+        self._cache[key] = (tuple(tensors), self._versions(tensors), packed)
+        return packed
 
-
-def _input_params(out_idx, params):
-    return params
+    @staticmethod
+    def _versions(tensors):
+        return tuple(t._version if t is not None else None for t in tensors)
 
 
 # ---------------------------------------------------------------------------

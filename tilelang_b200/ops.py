@@ -267,16 +267,17 @@ def gemm_grouped(A: torch.Tensor, w: PackedWeight, counts, out: Optional[torch.T
         return out
     _ensure_init(dev)
     prefix = torch.tensor(rows + tiles, dtype=torch.int32).to(dev, non_blocking=True)
-    need = lib.b200dq_gemm_workspace_bytes(M, w.N, w.K, w.weight_format, w.act_type, token_tile, 0)
-    workspace = workspace_for(dev, need)
     args = _lib.GemmArgs(
         a=A.data_ptr(), wp=w.wp.data_ptr(), bias=None, row_scale=None, c=out.data_ptr(),
-        workspace=workspace.data_ptr(), workspace_bytes=workspace.numel(),
+        workspace=None, workspace_bytes=0,
         M=M, N=w.N, K=w.K, group_size=w.group_size, weight_format=w.weight_format, act_type=w.act_type,
         out_type=_OUT_OF[out.dtype], flags=0, tensor_scale=1.0, code_bias=w.code_bias, fp4_exp_bias=w.fp4_exp_bias,
         token_tile=token_tile, max_ctas=0,
         group_row_prefix=prefix.data_ptr(), group_tile_prefix=prefix.data_ptr() + 4 * (G + 1),
         group_weight_stride=w.group_stride, num_groups=G, total_tiles=tiles[-1])
+    # the grouped schedule follows total_tiles, not M: size the scratch from the arguments
+    workspace = workspace_for(dev, lib.b200dq_gemm_workspace_bytes_for(ctypes.byref(args)))
+    args.workspace, args.workspace_bytes = workspace.data_ptr(), workspace.numel()
     with torch.cuda.device(dev):
         _lib.check(lib.b200dq_gemm(ctypes.byref(args), _stream_ptr(dev)), "b200dq_gemm (grouped)")
     # the prefix tensor must outlive the launch that reads it
