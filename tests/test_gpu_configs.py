@@ -1,0 +1,186 @@
+"""GPU parity at the stated sizes of the five benchmark configurations: the CUDA path through
+the public factories against the CPU oracle on the same seeded inputs, every output element.
+
+  C1  W4A16 16 x 1024 x 1024, group 128, fp16, zero-point 8
+  C2  W4A16 + group zeros, N = 28672, K = 8192, M in {1, 16, 128, 1024, 4096}, bf16
+  C3  MXFP4 (e2m1 + e8m0 per 32), N = 14336, K = 4096, M in {1, 32, 512, 8192}, bf16
+  C4  BitNet int8 x int2, (N, K) in {(3200, 3200), (8640, 3200), (3200, 8640)}, M in {1, 64, 2048}
+  C5  MoE: 64 experts, W1 2 x 1408 x 2048 and W2 2048 x 1408, uint4 group 128, 16384 tokens, top-6
+
+Integer results must be equal. Float results follow the reference's rule (rtol = atol = 1e-2,
+at most 1 % of the elements outside: tilelang/profiler/__init__.py:104-111) and the north star's
+bound, max |x - ref| / max(|ref|, rms(ref)) <= 1e-2 (2e-2 for the chained MoE layer); the same
+ratio with the floor at 0.1 rms is printed beside it (run with -s to see it): a bf16 output
+near zero is a few ulps of the typical magnitude away from the oracle by rounding alone, so that
+figure grows with the number of outputs (up to 6e-2 over the 117 M outputs of C2 at 4096 tokens,
+0.13 for the chained MoE layer) and is reported, not asserted. The oracle runs on the host: the largest case (C2 at 4096 tokens) takes it a few seconds.
+"""
+import pytest
+import torch
+
+import tilelang_b200 as tb
+from tilelang_b200 import moe, ops, quantize
+from oracle import ref_programs as R
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def gen(seed):
+    g = torch.Generator()
+    g.manual_seed(seed)
+    return g
+
+
+def check_float(name, out, ref, strict=1e-2):
+    out, ref = out.float().cpu(), ref.float().cpu()
+    assert torch.isfinite(out).all()
+    bad = R.mismatch_ratio(out, ref, 1e-2, 1e-2)
+    e1, e01 = R.max_rel_error(out, ref), R.max_rel_error(out, ref, floor_frac=0.1)
+    print(f"\n{name}: outside rtol=atol=1e-2: {bad:.4%}; max rel error {e1:.2e} (floor rms), {e01:.2e} (floor 0.1 rms)")
+    assert bad <= 0.01
+    assert e1 <= strict
+
+
+# ------------------------------- C1 ------------------------------------------
+
+def test_c1_w4a16_fp16():
+    M, N, K, group = 16, 1024, 1024, 128
+    A = torch.randn(M, K, generator=gen(0)).to(torch.float16)
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(1), dtype=torch.uint8)
+    s = (torch.rand(N, K // group, generator=gen(2)) * 0.015 + 0.005).to(torch.float16)
+    kernel = tb.matmul(M, N, K, "float16", "float16", "float32", num_bits=4, group_size=group)
+    C = kernel(A.to(DEV), qB.to(DEV), s.to(DEV))
+    tb.check_status()
+    check_float("C1", C, R.ref_w4a16(A, qB, s, None, group, torch.float16))
+
+
+# ------------------------------- C2 ------------------------------------------
+
+@pytest.fixture(scope="module")
+def c2_weight():
+    N, K, group = 28672, 8192, 128
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(1), dtype=torch.uint8)
+    s = (torch.rand(N, K // group, generator=gen(2)) * 0.015 + 0.005).to(torch.bfloat16)
+    z = (torch.rand(N, K // group, generator=gen(3)) * 4 + 6).to(torch.bfloat16)
+    W = R.dequant_w4_group(qB, s, z, group, torch.bfloat16).float()        # the oracle's weights, once
+    dev = [t.to(DEV) for t in (qB, s, z)]
+    yield N, K, group, dev, W
+    del dev, W
+    torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("M", [1, 16, 128, 1024, 4096])
+def test_c2_llama70b_mlp_w4a16_with_zeros(c2_weight, M):
+    N, K, group, (qB, s, z), W = c2_weight
+    A = torch.randn(M, K, generator=gen(100 + M)).to(torch.bfloat16)
+    kernel = tb.matmul(M, N, K, "bfloat16", "bfloat16", "float32", num_bits=4, group_size=group, with_zeros=True)
+    C = kernel(A.to(DEV), qB, s, z)
+    tb.check_status()
+    ref = torch.matmul(A.float(), W.T).to(torch.bfloat16)                 # ref_w4a16 with the cached weights
+    check_float(f"C2 M={M}", C, ref)
+
+
+# ------------------------------- C3 ------------------------------------------
+
+@pytest.fixture(scope="module")
+def c3_weight():
+    N, K = 14336, 4096
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(1), dtype=torch.uint8)      # all 16 codes
+    scale = (torch.randint(-8, 1, (N, K // 32), generator=gen(2)) + 127).to(torch.uint8)
+    W = R.dequant_mxfp4(qB, scale, 127, "e2m1").float()
+    dev = [qB.to(DEV), scale.to(DEV)]
+    yield N, K, dev, W
+    del dev, W
+    torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("M", [1, 32, 512, 8192])
+def test_c3_mxfp4(c3_weight, M):
+    N, K, (qB, scale), W = c3_weight
+    A = torch.randn(M, K, generator=gen(200 + M)).to(torch.bfloat16)
+    kernel = tb.matmul(M, N, K, "bfloat16", "bfloat16", "float32", source_format="fp4", num_bits=4, scale_size=32)
+    C = kernel(A.to(DEV), qB, scale)
+    tb.check_status()
+    check_float(f"C3 M={M}", C, torch.matmul(A.float(), W.T).to(torch.bfloat16))
+
+
+# ------------------------------- C4 ------------------------------------------
+
+@pytest.mark.parametrize("N,K", [(3200, 3200), (8640, 3200), (3200, 8640)])
+@pytest.mark.parametrize("M", [1, 64, 2048])
+def test_c4_bitnet_ternary(M, N, K):
+    W = torch.multinomial(torch.tensor([0.25, 0.5, 0.25]), N * K, replacement=True, generator=gen(1)).reshape(N, K) - 1
+    x = torch.randn(M, K, generator=gen(2)).to(torch.bfloat16)
+    s_w = 0.03
+    # activation quantiser on the device, bit-exact against the oracle's
+    A_q, s_act = ops.absmax_quant_int8(x.to(DEV))
+    A_ref, s_ref = R.bitnet_activation_quant(x)
+    assert torch.equal(A_q.cpu(), A_ref) and torch.equal(s_act.cpu(), s_ref.reshape(-1))
+    codes = quantize.compress_codes((W + 2).to(torch.uint8), 2)
+    factory = tb.bitnet_158_int8xint2_decode if M == 1 else tb.bitnet_158_int8xint2_prefill
+    kernel = factory(M, N, K, "int8", "int32", "int32", fast_decoding=False, code_offset=2)
+    C = torch.zeros(M, N, dtype=torch.int32, device=DEV)
+    kernel(A_q, codes.view(torch.int8).to(DEV), C)
+    tb.check_status()
+    assert torch.equal(C.cpu(), R.ref_bitnet_int32(A_ref, W.to(torch.int8)))
+    layer = tb.BitLinear(W.to(torch.int8).to(DEV), s_w, out_dtype=torch.bfloat16)
+    out = layer.forward_quantized(A_q, s_act)
+    assert torch.equal(out.cpu(), R.ref_bitnet_linear(A_ref, s_ref, W.to(torch.int8), s_w, torch.bfloat16))
+
+
+# ------------------------------- C5 ------------------------------------------
+
+@pytest.fixture(scope="module")
+def c5_experts():
+    E, H, F, group = 64, 2048, 1408, 128
+
+    def make(n, k, seed):
+        q = torch.randint(0, 256, (E, n, k // 2), generator=gen(seed), dtype=torch.uint8)
+        s = (torch.rand(E, n, k // group, generator=gen(seed + 1)) * 0.015 + 0.005).to(torch.bfloat16)
+        packed = ops.stack_packed([ops.pack_w4a16(q[e].to(DEV), s[e].to(DEV), None, n, k, group, torch.bfloat16)
+                                   for e in range(E)])
+        return q, s, packed
+
+    w1, w2 = make(2 * F, H, 10), make(H, F, 20)
+    yield E, H, F, group, w1, w2
+    del w1, w2
+    torch.cuda.empty_cache()
+
+
+def test_c5_grouped_gemms_at_full_token_count(c5_experts):
+    """The two grouped GEMMs alone on 16384 x 6 rows sorted by expert (routing of seeded
+    logits), against the per-expert oracle on a sample of experts."""
+    E, H, F, group, (w1_q, w1_s, w1_p), (w2_q, w2_s, w2_p) = c5_experts
+    T, k = 16384, 6
+    logits = torch.randn(T, E, generator=gen(2))
+    _, experts = moe.route(logits, k)
+    counts = torch.bincount(experts.reshape(-1), minlength=E).tolist()
+    x = torch.randn(T * k, H, generator=gen(3)).to(torch.bfloat16)
+    a = torch.randn(T * k, F, generator=gen(4)).to(torch.bfloat16)
+    h = ops.gemm_grouped(x.to(DEV), w1_p, counts)
+    y = ops.gemm_grouped(a.to(DEV), w2_p, counts)
+    tb.check_status()
+    starts = [0]
+    for c in counts:
+        starts.append(starts[-1] + c)
+    for e in (0, 17, 40, 63):
+        rows = slice(starts[e], starts[e + 1])
+        check_float(f"C5 W1 expert {e} ({counts[e]} rows)", h[rows],
+                    R.ref_w4a16(x[rows], w1_q[e], w1_s[e], None, group, torch.bfloat16))
+        check_float(f"C5 W2 expert {e} ({counts[e]} rows)", y[rows],
+                    R.ref_w4a16(a[rows], w2_q[e], w2_s[e], None, group, torch.bfloat16))
+
+
+def test_c5_moe_layer_64_experts_top6(c5_experts):
+    """The whole layer (route, dispatch, W1, silu * up, W2, weighted combine) at 64 experts,
+    top-6, 16384 tokens against the oracle's per-expert loop."""
+    E, H, F, group, (w1_q, w1_s, w1_p), (w2_q, w2_s, w2_p) = c5_experts
+    T, k = 16384, 6
+    x = torch.randn(T, H, generator=gen(5)).to(torch.bfloat16)
+    logits = torch.randn(T, E, generator=gen(6))
+    mlp = moe.make_gpu_expert_mlp(w1_p, w2_p, token_tile=256)
+    out = moe.moe_forward(x.to(DEV), logits.to(DEV), k, E, mlp)
+    tb.check_status()
+    ref = R.ref_moe_w4a16(x, logits, k, w1_q, w1_s, w2_q, w2_s, group)
+    check_float("C5 layer", out, ref, strict=2e-2)     # two chained GEMMs and a bf16 intermediate
