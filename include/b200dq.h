@@ -30,7 +30,8 @@ enum b200dq_weight_format {
   B200DQ_WF_U4_SZ = 0,    /* uint4 + per-group scale/zero term; fp16/bf16 activations   */
   B200DQ_WF_U4_RAW = 1,   /* uint4, weight = q (no scale)                               */
   B200DQ_WF_S4_RAW = 2,   /* int4 stored as q + 8, weight = q (no scale)                */
-  B200DQ_WF_FP4_E8M0 = 3, /* e2m1 codes + one e8m0 exponent byte per 32 K elements      */
+  B200DQ_WF_FP4_E8M0 = 3, /* fp4 codes + one e8m0 exponent byte per 32 K elements (bf16
+                           * activations; with fp16 activations the exponent bytes are ignored) */
   B200DQ_WF_I2_I8 = 4,    /* 2-bit codes -> int8 (minus code_bias); int8 activations    */
   B200DQ_WF_I4_I8 = 5     /* 4-bit codes -> int8 (minus code_bias); int8 activations    */
 };
@@ -39,7 +40,10 @@ enum b200dq_out_type { B200DQ_OUT_F16 = 0, B200DQ_OUT_BF16 = 1, B200DQ_OUT_F32 =
 enum b200dq_gemm_flags {
   B200DQ_GF_TRANS_C = 1,   /* write C^T (N x M), the orientation of the reference's fp4/w4a8 examples */
   B200DQ_GF_HAS_BIAS = 2,  /* add bias[M][N] (output dtype) before the cast                           */
-  B200DQ_GF_ROW_SCALE = 4  /* integer path: acc / row_scale[m] / tensor_scale before the cast          */
+  B200DQ_GF_ROW_SCALE = 4, /* integer path: acc / row_scale[m] / tensor_scale before the cast          */
+  B200DQ_GF_FP4_SIMPLE = 16 /* FP4 codes follow the reference's no-subnormal rule 2^(e-1) * (1 + m/2)
+                             * (example_dequant_gemm_fp4_hopper.py:10-29, dequantize_utils.py:57-84)
+                             * instead of true e2m1 */
 };
 
 /* Replaces init() of tilelang/jit/adapter/wrapper.py:60-70: selects nothing, but

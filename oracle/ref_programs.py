@@ -183,18 +183,25 @@ def encode_fp4_e2m1(x: np.ndarray) -> np.ndarray:
 # dequantisation rules
 # ---------------------------------------------------------------------------
 
-def dequant_w4_group(qB: torch.Tensor, scales, zeros, group_size: int, dtype: torch.dtype) -> torch.Tensor:
+def dequant_w4_group(qB: torch.Tensor, scales, zeros, group_size: int, dtype: torch.dtype,
+                     zeros_mode: str = "original") -> torch.Tensor:
     """W = (q - z) * s computed in fp32 and rounded once to the activation dtype:
     the reference's "original" zeros mode (quantize/lop3.py:684-689; symmetric case
     z = 8 in quantize/utils.py:29-30), dequantised to in_dtype before the matmul as
     its intrinsics and oracles do. ``zeros=None`` is the fixed zero-point 8;
-    ``scales=None`` leaves the raw code q."""
+    ``scales=None`` leaves the raw code q. ``zeros_mode`` "rescale" is q * s - z
+    (lop3.py:233-271) and "quantized" (q - qz) * s with integer zero-points
+    (lop3.py:326-363), under the same compute-in-fp32, round-once rule."""
     q = unpack_u4(qB).to(torch.float32)
     if scales is None:
         return q.to(dtype)
     g = group_size if group_size and group_size > 0 else q.shape[1]
     s = scales.to(torch.float32).repeat_interleave(g, dim=1)
     z = (zeros.to(torch.float32).repeat_interleave(g, dim=1) if zeros is not None else 8.0)
+    if zeros_mode == "rescale":
+        return (q * s - z).to(dtype)
+    if zeros_mode not in ("original", "quantized"):
+        raise ValueError(zeros_mode)
     return ((q - z) * s).to(dtype)
 
 
@@ -235,9 +242,9 @@ def ref_w4a16_noscale(A: torch.Tensor, qB: torch.Tensor, out_dtype: torch.dtype)
 
 
 def ref_w4a16(A: torch.Tensor, qB: torch.Tensor, scales, zeros, group_size: int,
-              out_dtype: torch.dtype) -> torch.Tensor:
+              out_dtype: torch.dtype, zeros_mode: str = "original") -> torch.Tensor:
     """Dequantise to the activation dtype, fp32 matmul, cast (group scale/zero rule above)."""
-    W = dequant_w4_group(qB, scales, zeros, group_size, A.dtype)
+    W = dequant_w4_group(qB, scales, zeros, group_size, A.dtype, zeros_mode)
     return _matmul_f32(A, W).to(out_dtype)
 
 

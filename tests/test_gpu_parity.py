@@ -228,6 +228,79 @@ def test_w4a16_repeated_cold_launches_are_bit_identical_at_full_width(M):
     tb.check_status()
 
 
+@pytest.mark.parametrize("mode", ["rescale", "quantized"])
+@pytest.mark.parametrize("M,dtype", [(4, torch.float16), (200, torch.bfloat16)])
+def test_w4a16_other_zero_point_modes(mode, M, dtype):
+    """q * s - z and (q - qz) * s (quantize/lop3.py:233-271, 326-363) through the same kernels:
+    both are an offline rewrite of the image's zero-point term."""
+    N, K, group = 384, 1024, 128
+    A, qB, s, _ = w4_inputs(M, N, K, group, dtype, False, seed=40)
+    if mode == "rescale":
+        z = (torch.rand(N, K // group, generator=gen(44)) * 0.1 + 0.05).to(dtype)      # z of the order of 8 s
+    else:
+        z = torch.randint(1, 16, (N, K // group), generator=gen(44), dtype=torch.int32)
+    kernel = tb.matmul(M, N, K, dtype, dtype, "float32", num_bits=4, group_size=group, with_zeros=True, zeros_mode=mode)
+    C = kernel(A.to(DEV), qB.to(DEV), s.to(DEV), z.to(DEV))
+    tb.check_status()
+    ref = R.ref_w4a16(A, qB, s, z, group, dtype, zeros_mode=mode)
+    if mode == "rescale" and dtype == torch.bfloat16:
+        # the image carries the zero-point z / s in the activation dtype: 8 significant bits in
+        # bf16, a per-group offset of up to 0.4 % of a typical weight. The reference has this
+        # rule for fp16 only (its LOP3 intrinsics are fp16), where the strict check holds.
+        out = C.float().cpu()
+        assert R.max_rel_error(out, ref.float()) <= 2e-2 and R.mismatch_ratio(out, ref.float(), RTOL, ATOL) <= 0.05
+    else:
+        check_float(C, ref)
+
+
+def test_gptq_checkpoint_through_the_adapter():
+    """AutoGPTQ tensors -> quantize.from_gptq -> matmul(zeros_mode="quantized") against the
+    dequantised checkpoint."""
+    K, N, group, M = 512, 256, 128, 24
+    g = gen(50)
+    q = torch.randint(0, 16, (K, N), generator=g)
+    z = torch.randint(1, 16, (K // group, N), generator=g)
+    s = (torch.rand(K // group, N, generator=g) * 0.015 + 0.005).to(torch.float16)
+
+    def pack(v):      # eight 4-bit fields per int32 along the last dimension
+        v = v.to(torch.int64).reshape(*v.shape[:-1], v.shape[-1] // 8, 8)
+        w = (v << (4 * torch.arange(8))).sum(-1)
+        return torch.where(w >= 2 ** 31, w - 2 ** 32, w).to(torch.int32)
+
+    qweight, qzeros = pack(q.t().contiguous()).t().contiguous(), pack(z - 1)
+    qB, s_nk, z_nk = quantize.from_gptq(qweight.to(DEV), s.to(DEV), qzeros.to(DEV))
+    A = torch.randn(M, K, generator=g).to(torch.float16)
+    kernel = tb.matmul(M, N, K, "float16", "float16", "float32", group_size=group, with_zeros=True, zeros_mode="quantized")
+    C = kernel(A.to(DEV), qB, s_nk, z_nk)
+    W = ((q.float() - z.repeat_interleave(group, 0).float()) * s.float().repeat_interleave(group, 0)).half()   # (K, N)
+    check_float(C, (A.float() @ W.float()).half())
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 256, 256), (150, 384, 640)])
+def test_w4_raw_codes_on_int8_activations(M, N, K):
+    # example_dequant_gemm_fine_grained.py:427-428: int8 activations, raw uint4 codes, int32 out
+    A = torch.randint(-128, 128, (M, K), generator=gen(1), dtype=torch.int8)
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(2), dtype=torch.uint8)
+    kernel = tb.matmul(M, N, K, "int8", "int32", "int32", num_bits=4)
+    C = kernel(A.to(DEV), qB.to(DEV))
+    assert C.dtype == torch.int32
+    assert torch.equal(C.cpu(), torch.matmul(A.to(torch.int64), R.unpack_u4(qB).to(torch.int64).T).to(torch.int32))
+
+
+def test_bitlinear_module_forward_matches_the_reference_layer():
+    """utils_quant.py:199-209: quantise the activations per token, ternary GEMM, post-scale."""
+    N, K = 640, 1024
+    w = torch.randn(N, K, generator=gen(3)) * 0.02
+    x = torch.randn(3, 17, K, generator=gen(4)).to(torch.bfloat16)
+    layer = tb.BitLinear.from_float(w.to(DEV), out_dtype=torch.bfloat16)
+    out = layer(x.to(DEV))
+    assert out.shape == (3, 17, N)
+    W_t, s_w = R.bitnet_weight_quant(w)
+    A_q, s_act = R.bitnet_activation_quant(x.reshape(-1, K))
+    ref = R.ref_bitnet_linear(A_q, s_act, W_t, float(s_w), torch.bfloat16).reshape(3, 17, N)
+    assert torch.equal(out.cpu(), ref)
+
+
 # ------------------------------- small-M entry point ------------------------------------
 
 def test_dequantize_gemv_reference_flow():
@@ -302,6 +375,49 @@ def test_mxfp4_reference_twiddled_bytes_with_raw_exponent_and_bias():
                        scale_exp_bias=0)
     C = kernel(A.to(DEV), quantize.untwiddle_fp4(qB_tw).to(DEV), scale.to(DEV), bias.to(DEV))
     check_float(C, R.ref_mxfp4(A, qB_tw, scale, bias, exp_bias=0, fmt="twiddled"))
+
+
+@pytest.mark.parametrize("M", [4, 96])
+def test_fp4_simple_rule_with_and_without_block_scale(M):
+    """The reference's scalar fp4 decoders (dequantize_utils.py:57-84: .5, .75, 1, 1.5, 2, 3, 4, 6,
+    no zero) with the raw 2**Scale exponent (ref_program_simple,
+    example_dequant_gemm_bf16_mxfp4_hopper.py:426-475) and without a scale
+    (example_dequant_gemm_bf16_fp4_hopper.py): byte-level drop-in for fast_dequant=False."""
+    N, K = 256, 512
+    A = (torch.rand(M, K, generator=gen(1)) * 2 - 1).to(torch.bfloat16)
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(2), dtype=torch.uint8)
+    scale = torch.randint(0, 4, (N, K // 32), generator=gen(3)).to(torch.uint8)
+    kernel = tb.matmul(M, N, K, "bfloat16", "bfloat16", "float32", source_format="fp4", fp4_format="tilelang_simple",
+                       scale_exp_bias=0)
+    C = kernel(A.to(DEV), qB.to(DEV), scale.to(DEV))
+    check_float(C, R.ref_mxfp4(A, qB, scale, None, exp_bias=0, fmt="simple"))
+    plain = tb.matmul(M, N, K, "bfloat16", "bfloat16", "float32", source_format="fp4", fp4_format="tilelang_simple",
+                      with_scaling=False)
+    C = plain(A.to(DEV), qB.to(DEV))
+    W = R.decode_fp4_simple(qB).float()
+    check_float(C, torch.matmul(A.float(), W.T).to(torch.bfloat16))
+    # one-hot rows read every decoded weight back bit for bit
+    eye = torch.eye(K, dtype=torch.bfloat16)[:64]
+    k64 = tb.matmul(64, N, K, "bfloat16", "bfloat16", "float32", source_format="fp4", fp4_format="tilelang_simple",
+                    with_scaling=False)
+    assert torch.equal(k64(eye.to(DEV), qB.to(DEV)).cpu().float(), W[:, :64].T.contiguous())
+
+
+@pytest.mark.parametrize("M", [1, 40, 256])
+def test_fp16_x_fp4_transposed_output(M):
+    """example_dequant_gemm_fp4_hopper.py:108-228: fp16 activations, fp4 weights by the scalar
+    rule (bias + 14), no scale, C^T (N, M) out; M = 1 takes the small-M kernel."""
+    N, K = 256, 512
+    A = (torch.rand(M, K, generator=gen(5)) * 2 - 1).to(torch.float16)
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(6), dtype=torch.uint8)
+    kernel = tb.matmul(M, N, K, "float16", "float16", "float32", source_format="fp4", fp4_format="tilelang_simple",
+                       with_scaling=False, trans_c=True)
+    Ct = kernel(A.to(DEV), qB.to(DEV))
+    assert Ct.shape == (N, M)
+    check_float(Ct, R.ref_fp4_noscale(A, qB, fmt="simple", transpose_out=True))
+    true = tb.matmul(M, N, K, "float16", "float16", "float32", source_format="fp4", with_scaling=False)
+    W = R.decode_fp4_e2m1(qB).float()
+    check_float(true(A.to(DEV), qB.to(DEV)), torch.matmul(A.float(), W.T).to(torch.float16))
 
 
 # ------------------------------- integer paths (bit-exact) -------------------

@@ -90,8 +90,15 @@ def test_factory_signatures_and_checks():
     assert [p.name for p in kz.params] == ["A", "B", "Scale", "Zeros", "C"]
     kf = tilelang_b200.matmul(4, 256, 256, "bfloat16", "bfloat16", "float32", source_format="fp4", with_bias=True)
     assert [p.name for p in kf.params] == ["A", "B", "Scale", "Bias", "C"] and kf.params[2].dtype == torch.uint8
+    ki = tilelang_b200.matmul(4, 256, 256, "int8", "int32", "int32")      # fine_grained.py:427-428
+    assert [p.name for p in ki.params] == ["A", "B", "C"] and ki.params[2].dtype == torch.int32
     with pytest.raises(ValueError):
-        tilelang_b200.matmul(4, 256, 256, "int8", "int32", "int32")
+        tilelang_b200.matmul(4, 256, 256, "int8", "float16", "int32")
+    kq = tilelang_b200.matmul(4, 256, 256, "float16", "float16", "float32", group_size=128, with_zeros=True,
+                              zeros_mode="quantized")
+    assert kq.params[3].name == "Zeros" and kq.params[3].dtype == torch.uint8
+    with pytest.raises(ValueError):
+        tilelang_b200.matmul(4, 256, 256, "float16", "float16", "float32", group_size=128, zeros_mode="other")
     gv = tilelang_b200.dequantize_gemv(1, 1024, 1024, "float16", "float16", "float16", 4, "int8", "uint", 4, 32, True)
     assert gv.out_idx is None and len(gv.params) == 3
     w8 = tilelang_b200.matmul_int8xint4(128, 256, 256, "int8", "int32", "int32")
@@ -115,3 +122,80 @@ def test_product_does_not_import_oracle():
                 src = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"^\s*(from|import)\s+oracle", src, flags=re.M), f"{f} imports the oracle"
                 assert "oracle/" not in src and "oracle." not in src, f"{f} refers to the oracle"
+
+
+def test_packed_weight_cache_is_keyed_by_tensor_identity_and_version():
+    """A freed weight's address can be handed to the next tensor of the same shape (version 0
+    again): the cache must repack for a different tensor object and after an in-place write."""
+    calls = []
+
+    def pack_fn(q):
+        calls.append(q)
+        return ("packed", len(calls))
+
+    k = kernels.DequantKernel("t", [], None, None, pack_fn)
+    a = torch.zeros(4, 8, dtype=torch.uint8)
+    assert k._packed(a) == ("packed", 1) and k._packed(a) == ("packed", 1)
+    b = torch.zeros(4, 8, dtype=torch.uint8)            # same shape, same version, another object
+    assert k._packed(b) == ("packed", 2)
+    assert k._packed(a) == ("packed", 1)                # still cached, source kept alive by the entry
+    a.add_(1)                                           # in-place write bumps the version
+    assert k._packed(a) == ("packed", 3)
+
+
+def test_zero_point_modes_map_to_the_original_rule():
+    from tilelang_b200 import ops
+    s = (torch.rand(8, 4) * 0.015 + 0.005).to(torch.bfloat16)
+    z = (torch.rand(8, 4) * 0.1 + 0.05).to(torch.bfloat16)
+    assert ops.zeros_for_original_mode(s, z, "original") is z
+    zr = ops.zeros_for_original_mode(s, z, "rescale")
+    assert zr.dtype == torch.bfloat16 and torch.equal(zr, (z.float() / s.float()).to(torch.bfloat16))
+    zq = ops.zeros_for_original_mode(s, torch.randint(0, 16, (8, 4), dtype=torch.int32), "quantized")
+    assert zq.dtype == torch.bfloat16 and torch.equal(zq.float(), zq.float().round())
+    with pytest.raises(ValueError):
+        ops.zeros_for_original_mode(s, z, "other")
+
+
+def _pack_fields(vals, bits, order=None):
+    """(..., F) integer fields -> (..., F * bits / 32) int32 words, field f of a word at bit
+    bits * order[f % per] (written with plain loops: the thing the adapters must undo)."""
+    per = 32 // bits
+    order = list(range(per)) if order is None else order
+    v = vals.to(torch.int64)
+    words = torch.zeros(*v.shape[:-1], v.shape[-1] // per, dtype=torch.int64)
+    for f in range(v.shape[-1]):
+        words[..., f // per] |= (v[..., f] & ((1 << bits) - 1)) << (bits * order[f % per])
+    words = torch.where(words >= 2 ** 31, words - 2 ** 32, words)
+    return words.to(torch.int32)
+
+
+def test_gptq_and_awq_adapters_recover_codes_scales_and_zero_points():
+    g = torch.Generator().manual_seed(5)
+    K, N, group = 256, 64, 128
+    q = torch.randint(0, 16, (K, N), generator=g)                       # (in, out) as the checkpoints store it
+    z = torch.randint(1, 16, (K // group, N), generator=g)
+    s = (torch.rand(K // group, N, generator=g) * 0.015 + 0.005).to(torch.float16)
+    want_qB = torch.from_numpy(R.general_compress(q.t().contiguous().numpy().astype(np.uint8), 4))
+    # AutoGPTQ: codes packed along K, zero-points along N, stored minus one
+    qweight = _pack_fields(q.t().contiguous(), 4).t().contiguous()      # (K/8, N)
+    qzeros = _pack_fields(z - 1, 4)                                     # (groups, N/8)
+    qB, s_nk, z_nk = quantize.from_gptq(qweight, s, qzeros)
+    assert torch.equal(qB, want_qB) and torch.equal(s_nk, s.t()) and torch.equal(z_nk.long(), z.t())
+    # AutoAWQ GEMM: both packed along N in the order 0, 2, 4, 6, 1, 3, 5, 7
+    inv = [0, 4, 1, 5, 2, 6, 3, 7]
+    qB, s_nk, z_nk = quantize.from_awq(_pack_fields(q, 4, inv), s, _pack_fields(z, 4, inv))
+    assert torch.equal(qB, want_qB) and torch.equal(s_nk, s.t()) and torch.equal(z_nk.long(), z.t())
+    # and the weight they stand for, by the oracle's "quantized" rule
+    W = R.dequant_w4_group(qB, s_nk, z_nk, group, torch.float16, "quantized")
+    want = ((q.t().float() - z.t().repeat_interleave(group, 1).float()) * s.t().float().repeat_interleave(group, 1)).half()
+    assert torch.equal(W, want)
+
+
+def test_bitlinear_is_a_module_with_the_reference_quantisers():
+    import torch.nn as nn
+    assert issubclass(kernels.BitLinear, nn.Module)
+    w = torch.randn(16, 32)
+    s = 1.0 / w.abs().mean().clamp(min=1e-5)
+    W_t = (w * s).round().clamp(-1, 1)
+    q, scale = R.bitnet_weight_quant(w)
+    assert torch.equal(W_t.to(torch.int8), q.to(torch.int8)) and abs(float(scale) - float(s)) < 1e-6

@@ -276,7 +276,7 @@ bool takes_skinny_path(const b200dq_gemm_args* a) {
   if (a->act_type != ACT_F16 && a->act_type != ACT_BF16) return false;
   if (a->out_type == OUT_I32) return false;
   if (a->K % 128 != 0) return false;
-  if (a->weight_format == WF_FP4_E8M0) return a->act_type == ACT_BF16;
+  if (a->weight_format == WF_FP4_E8M0) return true;
   return a->weight_format == WF_U4_SZ || a->weight_format == WF_U4_RAW || a->weight_format == WF_S4_RAW;
 }
 
@@ -327,7 +327,7 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   if (act < ACT_F16 || act > ACT_I8) return fail("%s: unknown activation type %d", who, act);
   if (a->out_type < OUT_F16 || a->out_type > OUT_I32) return fail("%s: unknown output type %d", who, a->out_type);
   if (wf_int != int_act) return fail("%s: weight format %d and activation type %d do not go together", who, wf, act);
-  if (wf == WF_FP4_E8M0 && act != ACT_BF16) return fail("%s: e2m1 weights need bf16 activations", who);
+  if (wf == WF_FP4_E8M0 && act == ACT_I8) return fail("%s: fp4 weights need f16 or bf16 activations", who);
   if (wf == WF_U4_SZ && (a->group_size <= 0 || a->K % a->group_size != 0))
     return fail("%s: group_size=%d must divide K=%d", who, a->group_size, a->K);
   if ((a->flags & GF_HAS_BIAS) && a->bias == nullptr) return fail("%s: HAS_BIAS set but bias is null", who);
@@ -360,7 +360,7 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
     b_group = encode_activation_map(&tmap, a->a, a->M, a->K, act, s.tn, group_kblocks_for(s.tn));
     if (b_group < 0) return -1;
   }
-  int flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
+  int flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE | GF_FP4_SIMPLE);
   if (output_takes_vector_stores(a->c, a->N, a->out_type, flags)) flags |= GF_VEC_STORE;
 
   GemmParams p;

@@ -140,7 +140,7 @@ __device__ __forceinline__ void decode_i4_chunk(const uint4& packed, uint32_t bi
   }
 }
 
-// e2m1 -> bf16 with a power-of-two block scale.
+// e2m1 -> bf16 (or fp16) with a power-of-two block scale.
 // Offline bit layout per 16-bit half (4 codes; code = s e1 e0 m): the first
 // three codes sit where one shift and one mask move them to bf16 bit positions
 // (sign -> 15, e1 e0 m -> 8..6):
@@ -153,7 +153,18 @@ __device__ __forceinline__ void decode_i4_chunk(const uint4& packed, uint32_t bi
 // 2^126 it becomes the e2m1 value {0, .5, 1, 1.5, 2, 3, 4, 6} exactly (e = 0 is
 // a bf16 subnormal, which the multiply normalises). `mul_lo`/`mul_hi` are the
 // two factors whose product is 2^126 * 2^(block exponent).
-__device__ __forceinline__ void decode_fp4_word(uint32_t w, uint32_t m1, uint32_t m2, uint32_t* out) {
+//
+// `exp_add` = 0x00800080 selects the reference's other fp4 rule, value = 2^(e-1) * (1 + m/2)
+// for every code (no zero, no subnormal: _tir_u8_to_f4_to_f16,
+// examples/dequantize_gemm/example_dequant_gemm_fp4_hopper.py:10-29, and torch_convert,
+// dequantize_utils.py:57-84): one more in the exponent field makes every pattern a normal
+// number, and the caller halves the factor.
+//
+// fp16 target: the three bits e1 e0 m move up to fp16's positions 11..9 (exponent field e of
+// five bits, mantissa top bit m); times 2^14 the same values come out (e = 0 is an fp16
+// subnormal). fp16 has no room for a block exponent, so only one fixed factor is applied.
+template <bool kBf16>
+__device__ __forceinline__ void decode_fp4_word(uint32_t w, uint32_t m1, uint32_t m2, uint32_t exp_add, uint32_t* out) {
   const uint32_t kMask = 0x81c081c0u;
   uint32_t v[4];
   v[0] = w & kMask;
@@ -165,8 +176,13 @@ __device__ __forceinline__ void decode_fp4_word(uint32_t w, uint32_t m1, uint32_
   v[3] = t;
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    __nv_bfloat162 x = __hmul2(u32_as_bf162(v[i]), u32_as_bf162(m1));
-    out[i] = bf162_as_u32(__hmul2(x, u32_as_bf162(m2)));
+    if constexpr (kBf16) {
+      __nv_bfloat162 x = __hmul2(u32_as_bf162(v[i] + exp_add), u32_as_bf162(m1));
+      out[i] = bf162_as_u32(__hmul2(x, u32_as_bf162(m2)));
+    } else {
+      const uint32_t h = lop3_and_or(v[i] << 3, 0x0e000e00u, v[i] & 0x80008000u) + exp_add;
+      out[i] = h2_as_u32(__hmul2(u32_as_h2(h), u32_as_h2(m1)));
+    }
   }
 }
 
@@ -184,13 +200,24 @@ __device__ __forceinline__ void fp4_scale_factors(int exp_total, uint32_t& m1, u
   m2 = hb | (hb << 16);
 }
 
-__device__ __forceinline__ void decode_fp4_chunk(const uint4& packed, int exp_total, uint32_t (&out)[16]) {
-  uint32_t m1, m2;
-  fp4_scale_factors(exp_total, m1, m2);
-  decode_fp4_word(packed.x, m1, m2, &out[0]);
-  decode_fp4_word(packed.y, m1, m2, &out[4]);
-  decode_fp4_word(packed.z, m1, m2, &out[8]);
-  decode_fp4_word(packed.w, m1, m2, &out[12]);
+// `exp_total`: power of two that takes the masked pattern to the weight (126 + block exponent
+// for true e2m1 in bf16, one less for the reference's simple rule); `simple`: that rule. The
+// fp16 form ignores the block exponent: 2^14 (true e2m1) or 2^13 (simple).
+template <bool kBf16>
+__device__ __forceinline__ void decode_fp4_chunk(const uint4& packed, int exp_total, bool simple, uint32_t (&out)[16]) {
+  uint32_t m1, m2 = 0;
+  uint32_t exp_add;
+  if constexpr (kBf16) {
+    fp4_scale_factors(exp_total - (simple ? 1 : 0), m1, m2);
+    exp_add = simple ? 0x00800080u : 0u;
+  } else {
+    m1 = simple ? 0x70007000u : 0x74007400u;     // 2^13 : 2^14
+    exp_add = simple ? 0x04000400u : 0u;
+  }
+  decode_fp4_word<kBf16>(packed.x, m1, m2, exp_add, &out[0]);
+  decode_fp4_word<kBf16>(packed.y, m1, m2, exp_add, &out[4]);
+  decode_fp4_word<kBf16>(packed.z, m1, m2, exp_add, &out[8]);
+  decode_fp4_word<kBf16>(packed.w, m1, m2, exp_add, &out[12]);
 }
 
 }  // namespace b200dq

@@ -131,7 +131,8 @@ __device__ __forceinline__ void skinny_decode(const GemmParams& p, const uint4& 
   if constexpr (WF == WF_U4_SZ) decode_u4_chunk<kBf16>(codes, sz, out);
   else if constexpr (WF == WF_U4_RAW) decode_u4_chunk_noscale<kBf16, false>(codes, out);
   else if constexpr (WF == WF_S4_RAW) decode_u4_chunk_noscale<kBf16, true>(codes, out);
-  else decode_fp4_chunk(codes, 126 + static_cast<int>((sz >> (8 * q)) & 0xffu) - p.fp4_exp_bias, out);
+  else decode_fp4_chunk<kBf16>(codes, 126 + static_cast<int>((sz >> (8 * q)) & 0xffu) - p.fp4_exp_bias,
+                               (p.flags & GF_FP4_SIMPLE) != 0, out);
 }
 
 // One summed output of a segment: a raw partial into the CTA's scratch slot, or the
@@ -162,7 +163,6 @@ __global__ void __launch_bounds__(kSkinnyThreads, 1)
 skinny_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmParams p) {
   static_assert(WF == WF_U4_SZ || WF == WF_U4_RAW || WF == WF_S4_RAW || WF == WF_FP4_E8M0,
                 "4-bit weights on 16-bit activations");
-  static_assert(WF != WF_FP4_E8M0 || ACT == ACT_BF16, "e2m1 weights decode to bf16");
   using Ring = SkinnyRing<NT, WF>;
   constexpr bool kBf16 = (ACT == ACT_BF16);
   constexpr int RING = Ring::kSlots;

@@ -56,6 +56,7 @@ cudaError_t launch_skinny_gemm(int wf, int act, const CUtensorMap& tmap_a, const
                                cudaStream_t stream) {
   if (p.K % 128 != 0) return cudaErrorInvalidValue;
   if (wf == WF_FP4_E8M0 && act == ACT_BF16) return launch_format<WF_FP4_E8M0, ACT_BF16>(tmap_a, p, grid, stream);
+  if (wf == WF_FP4_E8M0 && act == ACT_F16) return launch_format<WF_FP4_E8M0, ACT_F16>(tmap_a, p, grid, stream);
   if (wf == WF_U4_SZ && act == ACT_F16) return launch_format<WF_U4_SZ, ACT_F16>(tmap_a, p, grid, stream);
   if (wf == WF_U4_SZ && act == ACT_BF16) return launch_format<WF_U4_SZ, ACT_BF16>(tmap_a, p, grid, stream);
   if (wf == WF_U4_RAW && act == ACT_F16) return launch_format<WF_U4_RAW, ACT_F16>(tmap_a, p, grid, stream);

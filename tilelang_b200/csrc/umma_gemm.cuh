@@ -57,7 +57,7 @@ enum WeightFormat : int {
   WF_U4_SZ = 0,       // uint4, per-group scale + zero (16-bit activations)
   WF_U4_RAW = 1,      // uint4, weight = q              (no scale)
   WF_S4_RAW = 2,      // uint4 storing q = w + 8        (no scale)
-  WF_FP4_E8M0 = 3,    // e2m1 + e8m0 block scale per 32 (bf16 activations)
+  WF_FP4_E8M0 = 3,    // e2m1 + e8m0 block scale per 32 (bf16 activations; fp16 without block scale)
   WF_I2_I8 = 4,       // 2-bit codes -> int8, minus `code_bias` (int8 activations)
   WF_I4_I8 = 5,       // 4-bit codes -> int8, minus `code_bias` (int8 activations)
 };
@@ -70,6 +70,7 @@ enum GemmFlags : int {
   GF_HAS_BIAS = 2,     // add bias[M][N] (output dtype) in the epilogue
   GF_ROW_SCALE = 4,    // integer path: acc / row_scale[m] / tensor_scale before the cast
   GF_VEC_STORE = 8,    // internal: base and pitch of the output allow 16-byte stores
+  GF_FP4_SIMPLE = 16,  // fp4 codes follow the reference's no-subnormal rule 2^(e-1) * (1 + m/2)
 };
 
 struct GemmParams {
@@ -555,7 +556,8 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
             } else if constexpr (WF == WF_S4_RAW) {
               decode_u4_chunk_noscale<kBf16, true>(cq, regs);
             } else if constexpr (WF == WF_FP4_E8M0) {
-              decode_fp4_chunk(cq, 126 + static_cast<int>((sz0 >> (8 * it)) & 0xff) - p.fp4_exp_bias, regs);
+              decode_fp4_chunk<kBf16>(cq, 126 + static_cast<int>((sz0 >> (8 * it)) & 0xff) - p.fp4_exp_bias,
+                                      (p.flags & GF_FP4_SIMPLE) != 0, regs);
             } else {
               decode_i2_chunk(cq, p.code_bias, regs);
             }

@@ -13,6 +13,7 @@ cudaError_t launch_umma_gemm(int wf, int act, int tn, const CUtensorMap& tmap, c
   if (wf == WF_S4_RAW && act == ACT_F16) return launch_umma_s4raw_f16(tn, tmap, p, grid, stream);
   if (wf == WF_S4_RAW && act == ACT_BF16) return launch_umma_s4raw_bf16(tn, tmap, p, grid, stream);
   if (wf == WF_FP4_E8M0 && act == ACT_BF16) return launch_umma_fp4_bf16(tn, tmap, p, grid, stream);
+  if (wf == WF_FP4_E8M0 && act == ACT_F16) return launch_umma_fp4_f16(tn, tmap, p, grid, stream);
   if (wf == WF_I2_I8 && act == ACT_I8) return launch_umma_i2_i8(tn, tmap, p, grid, stream);
   if (wf == WF_I4_I8 && act == ACT_I8) return launch_umma_i4_i8(tn, tmap, p, grid, stream);
   return cudaErrorInvalidValue;

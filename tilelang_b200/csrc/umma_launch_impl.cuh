@@ -63,6 +63,7 @@ cudaError_t launch_umma_u4raw_bf16(int, const CUtensorMap&, const GemmParams&, i
 cudaError_t launch_umma_s4raw_f16(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
 cudaError_t launch_umma_s4raw_bf16(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
 cudaError_t launch_umma_fp4_bf16(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
+cudaError_t launch_umma_fp4_f16(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
 cudaError_t launch_umma_i2_i8(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
 cudaError_t launch_umma_i4_i8(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
 

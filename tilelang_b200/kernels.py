@@ -132,19 +132,29 @@ def matmul(M: int, N: int, K: int, in_dtype, out_dtype, accum_dtype, num_bits: i
       (``source_format`` "fp4"/"e2m1"/"uint32" with ``scale_size`` 32; inputs
       ``(A, qB, Scale[, Bias])``, Scale (N, K/32) uint8).
 
-    ``fp4_format``: "e2m1" true e2m1 codes in natural nibble order (default);
+    With ``with_scaling=False`` the fp4 weights carry no block scale (inputs ``(A, qB)``): the
+    bf16 x fp4 and fp16 x fp4 examples (example_dequant_gemm_bf16_fp4_hopper.py:46-346,
+    example_dequant_gemm_fp4_hopper.py:108-220; the latter writes C^T: ``trans_c=True``).
+    ``fp4_format``: "e2m1" true e2m1 codes in natural nibble order (default), or
+    "tilelang_simple", the no-subnormal rule of the reference's scalar decoders;
     ``scale_exp_bias``: 127 for OCP e8m0 bytes, 0 for the raw ``2**Scale`` of the
-    reference's hopper example. Only ``zeros_mode="original"`` ((q - z) * s) exists.
+    reference's hopper example. ``zeros_mode``: "original" ((q - z) * s), "rescale"
+    (q * s - z) or "quantized" ((q - qz) * s with integer zero-points), quantize/lop3.py:684-689;
+    all three are an offline rewrite of the zero-point term of the packed image.
+    ``in_dtype="int8"`` (with ``out_dtype = accum_dtype = "int32"``) is the integer variant of
+    example_dequant_gemm_fine_grained.py:427-428: C = A_int8 @ unpack_u4(qB)^T, exact.
     """
     in_t, out_t, acc_t = as_torch_dtype(in_dtype), as_torch_dtype(out_dtype), as_torch_dtype(accum_dtype)
     if num_bits != 4:
         raise ValueError("matmul: only num_bits=4 weights are supported on the 16-bit activation path")
+    if in_t == torch.int8:
+        return _matmul_int8_unsigned(M, N, K, out_t, acc_t, group_size or with_scaling or with_zeros or with_bias)
     if in_t not in (torch.float16, torch.bfloat16):
-        raise ValueError("matmul: in_dtype must be float16 or bfloat16 (int8 activations: matmul_int8xint4)")
+        raise ValueError("matmul: in_dtype must be float16, bfloat16 or int8")
     if acc_t != torch.float32:
         raise ValueError("matmul: accumulation is float32 (tcgen05 kind::f16 accumulates in fp32)")
-    if zeros_mode != "original":
-        raise ValueError("matmul: only zeros_mode='original' ((q - z) * s) is implemented")
+    if zeros_mode not in ops.ZEROS_MODES:
+        raise ValueError(f"matmul: zeros_mode must be one of {ops.ZEROS_MODES}")
     is_fp4 = str(source_format).lower() in ("fp4", "e2m1", "mxfp4", "uint32", "fp")
     if with_scaling is None:
         with_scaling = bool(group_size) or is_fp4
@@ -152,34 +162,37 @@ def matmul(M: int, N: int, K: int, in_dtype, out_dtype, accum_dtype, num_bits: i
 
     params = [Param("A", (M, K), in_t), Param("B", (N, qk), torch.uint8)]
     if is_fp4:
-        if in_t != torch.bfloat16:
-            raise ValueError("matmul: e2m1 weights need bfloat16 activations")
-        if fp4_format != "e2m1":
-            raise ValueError("matmul: the device decoder takes natural-order true e2m1 codes; convert other "
-                             "layouts with tilelang_b200.quantize first")
-        params.append(Param("Scale", (N, K // scale_size), torch.uint8))
-        if scale_size != 32:
-            raise ValueError("matmul: MXFP4 uses one exponent byte per 32 K elements")
+        if fp4_format not in ("e2m1", "tilelang_simple"):
+            raise ValueError("matmul: fp4_format is 'e2m1' (true e2m1) or 'tilelang_simple' (the reference's scalar "
+                             "decoders); twiddled bytes go through tilelang_b200.quantize.untwiddle_fp4 first")
+        if in_t == torch.float16 and with_scaling:
+            raise ValueError("matmul: float16 activations take fp4 weights without a block scale (with_scaling=False)")
+        if with_scaling:
+            params.append(Param("Scale", (N, K // scale_size), torch.uint8))
+            if scale_size != 32:
+                raise ValueError("matmul: MXFP4 uses one exponent byte per 32 K elements")
     elif with_scaling:
         g = K if group_size in (None, -1, 0) else group_size
         params.append(Param("Scale", (N, K // g), in_t))
         if with_zeros:
-            params.append(Param("Zeros", (N, K // g), in_t))
+            # "quantized": one integer zero-point per (row, group), any integer dtype
+            params.append(Param("Zeros", (N, K // g), torch.uint8 if zeros_mode == "quantized" else in_t))
     if with_bias:
         params.append(Param("Bias", (M, N), out_t))
     params.append(Param("C", (N, M) if trans_c else (M, N), out_t))
 
     def pack_fn(qB, scale=None, zeros=None):
         if is_fp4:
-            return ops.pack_mxfp4(qB.view(torch.uint8), scale, N, K, exp_bias=scale_exp_bias)
+            return ops.pack_mxfp4(qB.view(torch.uint8), scale, N, K, exp_bias=scale_exp_bias, fp4_format=fp4_format,
+                                  dtype=in_t)
         if with_scaling:
             g = K if group_size in (None, -1, 0) else group_size
-            return ops.pack_w4a16(qB.view(torch.uint8), scale, zeros, N, K, g, in_t)
+            return ops.pack_w4a16(qB.view(torch.uint8), scale, zeros, N, K, g, in_t, zeros_mode=zeros_mode)
         return ops.pack_w4a16(qB.view(torch.uint8), None, None, N, K, 0, in_t)
 
     def impl(kernel: DequantKernel, A, qB, *rest):
         rest = list(rest)
-        scale = rest.pop(0) if (is_fp4 or with_scaling) else None
+        scale = rest.pop(0) if with_scaling else None
         zeros = rest.pop(0) if (with_scaling and with_zeros and not is_fp4) else None
         bias = rest.pop(0) if with_bias else None
         _check(A, params[0])
@@ -192,12 +205,34 @@ def matmul(M: int, N: int, K: int, in_dtype, out_dtype, accum_dtype, num_bits: i
     return DequantKernel("matmul", params, [-1], impl, pack_fn, desc)
 
 
+def _matmul_int8_unsigned(M: int, N: int, K: int, out_t: torch.dtype, acc_t: torch.dtype, extras) -> DequantKernel:
+    """``C[M, N] int32 = A_int8 @ unpack_u4(qB)^T`` with the raw unsigned codes: the int8 -> int32
+    variant of example_dequant_gemm_fine_grained.py (:427-428 run it with accum int32)."""
+    if out_t != torch.int32 or acc_t != torch.int32:
+        raise ValueError("matmul: int8 activations accumulate and return int32")
+    if extras:
+        raise ValueError("matmul: the int8 variant takes raw codes only (no scale, zeros or bias)")
+    params = [Param("A", (M, K), torch.int8), Param("B", (N, K // 2), torch.uint8), Param("C", (M, N), torch.int32)]
+
+    def pack_fn(qB):
+        return ops.pack_int4_for_int8(qB.view(torch.uint8), N, K, code_offset=0)
+
+    def impl(kernel: DequantKernel, A, qB):
+        _check(A, params[0])
+        _check(qB, params[1], any_int8=True)
+        return ops.gemm(A, kernel._packed(qB), out_dtype=torch.int32)
+
+    return DequantKernel("matmul", params, [-1], impl, pack_fn, f"b200dq kind::i8 int8 x uint4: M={M} N={N} K={K}")
+
+
 def _check(t: torch.Tensor, p: Param, any_int8: bool = False) -> None:
     if not isinstance(t, torch.Tensor):
         raise TypeError(f"{p.name}: expected a torch.Tensor")
     if tuple(t.shape) != p.shape:
         raise ValueError(f"{p.name}: expected shape {p.shape}, got {tuple(t.shape)}")
     ok = t.dtype == p.dtype or (any_int8 and t.dtype in (torch.int8, torch.uint8))
+    if p.name == "Zeros" and p.dtype == torch.uint8:
+        ok = not t.dtype.is_floating_point
     if not ok:
         raise TypeError(f"{p.name}: expected dtype {p.dtype}, got {t.dtype}")
 
@@ -342,19 +377,46 @@ def bitnet_158_int8xint2_prefill(M: int, N: int, K: int, in_dtype="int8", out_dt
                            code_offset)
 
 
-class BitLinear:
+class BitLinear(torch.nn.Module):
     """The BitNet linear layer's inference forward on top of the int8 x int2 kernel:
     per-token absmax int8 quantisation of the activations, ternary GEMM, then
-    ``out / s_act / s_w`` (examples/bitnet-1.58b/utils_quant.py:156-170, 199-209).
-    Weights are ternary codes w + 2 in 2 bits."""
+    ``out / s_act / s_w`` (examples/bitnet-1.58b/utils_quant.py:156-170; ``forward`` is
+    ``BitLinearBitBLAS.forward``, :199-209: quantise, GEMM, post-scale, bias).
+    Weights are ternary codes w + 2 in 2 bits. ``W_t`` is the ternary (N, K) int8 weight and
+    ``s_w`` its scale 1 / mean|W_fp| (``weight_quant``, :149-154); ``from_float`` derives both
+    from a floating-point weight."""
 
-    def __init__(self, W_t: torch.Tensor, s_w: float, out_dtype: torch.dtype = torch.bfloat16):
+    def __init__(self, W_t: torch.Tensor, s_w: float, out_dtype: torch.dtype = torch.bfloat16,
+                 bias: Optional[torch.Tensor] = None):
+        super().__init__()
         from .quantize import compress_codes
         N, K = W_t.shape
         self.N, self.K, self.s_w, self.out_dtype = N, K, float(s_w), out_dtype
+        self.in_features, self.out_features = K, N
         codes = compress_codes((W_t.to(torch.int16) + 2).to(torch.uint8), 2)
         self.weight = ops.pack_int2(codes, N, K, code_offset=2)
+        self.bias = bias
+
+    @classmethod
+    def from_float(cls, weight: torch.Tensor, out_dtype: torch.dtype = torch.bfloat16,
+                   bias: Optional[torch.Tensor] = None) -> "BitLinear":
+        """Ternarise a floating-point (N, K) weight: s = 1 / mean|W| (clamped at 1e-5),
+        W_t = round(W * s).clamp(-1, 1) (utils_quant.py:149-154)."""
+        s = 1.0 / weight.float().abs().mean().clamp_(min=1e-5)
+        W_t = (weight.float() * s).round().clamp_(-1, 1).to(torch.int8)
+        return cls(W_t, float(s), out_dtype, bias)
 
     def forward_quantized(self, A_q: torch.Tensor, s_act: torch.Tensor) -> torch.Tensor:
         return ops.gemm(A_q, self.weight, out_dtype=self.out_dtype, row_scale=s_act.reshape(-1).float().contiguous(),
                         tensor_scale=self.s_w)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """x (..., K) float16/bfloat16 -> (..., N): absmax-quantise every token on the device,
+        multiply, rescale; the bias (if any) is added in the output dtype."""
+        lead = x.shape[:-1]
+        x2 = x.reshape(-1, self.K).contiguous()
+        A_q, s_act = ops.absmax_quant_int8(x2)
+        out = self.forward_quantized(A_q, s_act)
+        if self.bias is not None:
+            out = out + self.bias.to(out.dtype)
+        return out.reshape(*lead, self.N)

@@ -15,7 +15,7 @@ from typing import Optional
 import torch
 
 from . import _lib
-from ._lib import (ACT_BF16, ACT_F16, ACT_I8, GF_HAS_BIAS, GF_ROW_SCALE, GF_TRANS_C, OUT_BF16, OUT_F16,
+from ._lib import (ACT_BF16, ACT_F16, ACT_I8, GF_FP4_SIMPLE, GF_HAS_BIAS, GF_ROW_SCALE, GF_TRANS_C, OUT_BF16, OUT_F16,
                    OUT_F32, OUT_I32, WF_FP4_E8M0, WF_I2_I8, WF_I4_I8, WF_S4_RAW, WF_U4_RAW, WF_U4_SZ)
 
 _ACT_OF = {torch.float16: ACT_F16, torch.bfloat16: ACT_BF16, torch.int8: ACT_I8}
@@ -61,6 +61,7 @@ class PackedWeight:
     group_size: int = 0
     code_bias: int = 0
     fp4_exp_bias: int = 127
+    fp4_simple: bool = False     # fp4 codes follow the reference's no-subnormal rule
     num_groups: int = 0          # > 0: a stack of per-group images (stack_packed)
     group_stride: int = 0        # bytes between consecutive group images
 
@@ -91,13 +92,40 @@ def _pack(q: torch.Tensor, scales: Optional[torch.Tensor], zeros: Optional[torch
     return wp
 
 
+ZEROS_MODES = ("original", "rescale", "quantized")
+
+
+def zeros_for_original_mode(scales: torch.Tensor, zeros: torch.Tensor, zeros_mode: str) -> torch.Tensor:
+    """The zero-point tensor that makes the device's ``(q - z) * s`` equal to the weight of the
+    given reference mode (examples/dequantize_gemm/quantize/lop3.py:684-689):
+
+    * ``original``: ``(q - z) * s`` -- unchanged;
+    * ``rescale``: ``q * s - z`` (:233-271) = ``(q - z / s) * s``, so ``z / s`` computed in fp32
+      and rounded once to the activation dtype. In float16 that agrees with the reference's
+      ``fma(q, s, -z)`` to about one unit in the last place of the weight; bfloat16 keeps only
+      8 significant bits of ``z / s``, a per-group offset of up to 0.4 % of a typical weight
+      (the reference has this rule for float16 only);
+    * ``quantized``: ``(q - qz) * s`` with integer zero-points (:326-363); ``zeros`` holds one
+      integer per (row, group) (any integer dtype, or the activation dtype), exact.
+    """
+    if zeros_mode == "original":
+        return zeros
+    if zeros_mode == "rescale":
+        return (zeros.float() / scales.float()).to(scales.dtype)
+    if zeros_mode == "quantized":
+        return zeros.to(scales.dtype)
+    raise ValueError(f"zeros_mode must be one of {ZEROS_MODES}, got {zeros_mode!r}")
+
+
 def pack_w4a16(qweight: torch.Tensor, scales: Optional[torch.Tensor], zeros: Optional[torch.Tensor], N: int, K: int,
-               group_size: int, dtype: torch.dtype, signed_storage: bool = False) -> PackedWeight:
+               group_size: int, dtype: torch.dtype, signed_storage: bool = False,
+               zeros_mode: str = "original") -> PackedWeight:
     """uint4 codes (N, K/2), two per byte with the even k in the low nibble.
 
     ``scales``/``zeros`` are (N, K/group_size) in ``dtype``; the weight is
     ``(q - z) * s`` (the reference's "original" zeros mode,
-    examples/dequantize_gemm/quantize/lop3.py:684-689). ``zeros=None`` means the
+    examples/dequantize_gemm/quantize/lop3.py:684-689) or, with ``zeros_mode``, one of its
+    other two rules (see :func:`zeros_for_original_mode`). ``zeros=None`` means the
     fixed zero-point 8; ``scales=None`` means the raw code ``q`` (or ``q - 8``
     with ``signed_storage``), as in example_dequant_gemm_fine_grained.py:11-13.
     """
@@ -112,6 +140,11 @@ def pack_w4a16(qweight: torch.Tensor, scales: Optional[torch.Tensor], zeros: Opt
     if group_size in (-1, 0, None):
         group_size = K
     groups = K // group_size
+    if zeros is not None and zeros_mode != "original":
+        _check_cuda_contig("zeros", zeros, qweight.device)
+        if tuple(zeros.shape) != (N, groups) or tuple(scales.shape) != (N, groups):
+            raise ValueError(f"scales and zeros must have shape {(N, groups)}")
+        zeros = zeros_for_original_mode(scales, zeros, zeros_mode).contiguous()
     for name, t in (("scales", scales), ("zeros", zeros)):
         if t is None:
             continue
@@ -122,18 +155,33 @@ def pack_w4a16(qweight: torch.Tensor, scales: Optional[torch.Tensor], zeros: Opt
     return PackedWeight(wp, N, K, WF_U4_SZ, act, group_size=group_size)
 
 
-def pack_mxfp4(qweight: torch.Tensor, scale_bytes: torch.Tensor, N: int, K: int, exp_bias: int = 127) -> PackedWeight:
-    """e2m1 codes (N, K/2) (even k in the low nibble) + one exponent byte per 32 K.
+def pack_mxfp4(qweight: torch.Tensor, scale_bytes: Optional[torch.Tensor], N: int, K: int, exp_bias: int = 127,
+               fp4_format: str = "e2m1", dtype: torch.dtype = torch.bfloat16) -> PackedWeight:
+    """fp4 codes (N, K/2) (even k in the low nibble) + one exponent byte per 32 K.
 
     ``exp_bias=127`` reads the bytes as OCP e8m0; ``exp_bias=0`` as the raw
     exponent the reference's hopper example applies with ``2**Scale``
-    (example_dequant_gemm_bf16_mxfp4_hopper.py:397).
-    """
+    (example_dequant_gemm_bf16_mxfp4_hopper.py:397). ``scale_bytes=None``: no block scale
+    (example_dequant_gemm_bf16_fp4_hopper.py, example_dequant_gemm_fp4_hopper.py).
+    ``fp4_format``: "e2m1" (true e2m1: 0, .5, 1, 1.5, 2, 3, 4, 6) or "tilelang_simple", the rule
+    of the reference's scalar decoders, 2^(e-1) * (1 + m/2) for every code (.5, .75, 1, 1.5, 2, 3,
+    4, 6: dequantize_utils.py:57-84, example_dequant_gemm_fp4_hopper.py:10-29).
+    ``dtype=torch.float16`` (the fp16 x fp4 example) takes no block scale."""
+    if fp4_format not in ("e2m1", "tilelang_simple"):
+        raise ValueError("fp4_format must be 'e2m1' or 'tilelang_simple'")
+    if dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("fp4 weights need float16 or bfloat16 activations")
+    if scale_bytes is None:
+        scale_bytes = torch.full((N, K // 32), exp_bias, dtype=torch.uint8, device=qweight.device)
+    elif dtype == torch.float16:
+        raise ValueError("float16 activations take fp4 weights without a block scale")
     _check_cuda_contig("scale bytes", scale_bytes, qweight.device)
     if scale_bytes.dtype != torch.uint8 or tuple(scale_bytes.shape) != (N, K // 32):
         raise ValueError(f"scale bytes must be uint8 of shape {(N, K // 32)}")
-    wp = _pack(qweight, scale_bytes, None, N, K, 4, 32, WF_FP4_E8M0, ACT_BF16)
-    return PackedWeight(wp, N, K, WF_FP4_E8M0, ACT_BF16, group_size=32, fp4_exp_bias=exp_bias)
+    act = _ACT_OF[dtype]
+    wp = _pack(qweight, scale_bytes, None, N, K, 4, 32, WF_FP4_E8M0, act)
+    return PackedWeight(wp, N, K, WF_FP4_E8M0, act, group_size=32, fp4_exp_bias=exp_bias,
+                        fp4_simple=(fp4_format == "tilelang_simple"))
 
 
 def pack_int2(qweight: torch.Tensor, N: int, K: int, code_offset: int = 0) -> PackedWeight:
@@ -186,7 +234,7 @@ def gemm(A: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None,
             raise ValueError(f"out must have shape {want}, got {tuple(out.shape)}")
     if out.dtype not in _OUT_OF:
         raise TypeError(f"unsupported output dtype {out.dtype}")
-    flags = GF_TRANS_C if trans_c else 0
+    flags = (GF_TRANS_C if trans_c else 0) | (GF_FP4_SIMPLE if w.fp4_simple else 0)
     if bias is not None:
         _check_cuda_contig("bias", bias, dev)
         if bias.dtype != out.dtype or tuple(bias.shape) != (M, w.N):

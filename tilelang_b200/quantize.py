@@ -95,3 +95,67 @@ def untwiddle_fp4(qB: torch.Tensor) -> torch.Tensor:
     lo = (c0 | (c1 << 4)).to(torch.uint8)
     hi = (c2 | (c3 << 4)).to(torch.uint8)
     return torch.stack((lo, hi), dim=-1).reshape(qB.shape)
+
+
+# ---------------------------------------------------------------------------
+# checkpoint adapters: (qweight, scales, qzeros) of common 4-bit formats -> the natural
+# layout the kernel factories take (codes (N, K/2), scales and integer zeros (N, K/group)).
+# The integer zero-points go with ``zeros_mode="quantized"`` ((q - qz) * s, the reference's
+# quantize/lop3.py:326-363); its BitNet checkpoints (examples/bitnet-1.58b/maint/
+# create_bitblas_ckpt.py, load_from_quantized.py) are covered by ``BitLinear.from_float``.
+# ---------------------------------------------------------------------------
+
+def _unpack_int32_fields(words: torch.Tensor, bits: int, order=None) -> torch.Tensor:
+    """(..., W) int32 words -> (..., W * 32 / bits) fields, field f of a word in bits
+    [bits * order[f], ...) (``order`` defaults to 0, 1, 2, ...)."""
+    per = 32 // bits
+    order = list(range(per)) if order is None else order
+    w = words.to(torch.int64) & 0xFFFFFFFF
+    shifts = torch.tensor([bits * o for o in order], dtype=torch.int64, device=words.device)
+    out = (w.unsqueeze(-1) >> shifts) & ((1 << bits) - 1)
+    return out.reshape(*words.shape[:-1], words.shape[-1] * per)
+
+
+def from_gptq(qweight: torch.Tensor, scales: torch.Tensor, qzeros: torch.Tensor, bits: int = 4,
+              zero_offset: int = 1):
+    """AutoGPTQ-style tensors of a (K -> N) linear layer:
+
+    * ``qweight`` int32 (K * bits / 32, N): code of input k, output n in bits
+      [bits * (k % 8), ...) of word (k // 8, n);
+    * ``scales`` (K / group, N) float16/bfloat16;
+    * ``qzeros`` int32 (K / group, N * bits / 32): zero-point of output n in bits
+      [bits * (n % 8), ...) of word (group, n // 8), stored minus ``zero_offset``
+      (1 in the original format, 0 in its "v2").
+
+    Returns ``(qB, scales_nk, zeros_nk)``: codes (N, K / 2) uint8 with the even k in the low
+    nibble, scales (N, K / group) and integer zero-points (N, K / group) uint8, for
+    ``matmul(..., group_size=K // scales.shape[0], with_zeros=True, zeros_mode="quantized")``.
+    Act-order checkpoints (a ``g_idx`` that is not k // group) must be un-permuted first."""
+    if bits != 4:
+        raise ValueError("from_gptq: 4-bit checkpoints only")
+    K = qweight.shape[0] * 32 // bits
+    N = qweight.shape[1]
+    codes_kn = _unpack_int32_fields(qweight.t().contiguous(), bits)            # (N, K)
+    zeros = _unpack_int32_fields(qzeros, bits)[:, :N] + zero_offset              # (groups, N)
+    if int(zeros.max()) > 16 or int(zeros.min()) < 0:
+        raise ValueError("from_gptq: zero-points leave [0, 16]; wrong zero_offset?")
+    qB = compress_codes(codes_kn.to(torch.uint8), bits)
+    assert tuple(qB.shape) == (N, K // 2)
+    return qB, scales.t().contiguous(), zeros.t().contiguous().to(torch.uint8)
+
+
+_AWQ_ORDER = [0, 4, 1, 5, 2, 6, 3, 7]    # nibble of a word that holds output 8 w + j, for j = 0..7
+
+
+def from_awq(qweight: torch.Tensor, scales: torch.Tensor, qzeros: torch.Tensor, bits: int = 4):
+    """AutoAWQ "GEMM" tensors of a (K -> N) linear layer: ``qweight`` int32 (K, N / 8) and
+    ``qzeros`` int32 (K / group, N / 8), eight outputs per word in the interleaved order
+    0, 2, 4, 6, 1, 3, 5, 7 (output 8 w + j sits in nibble [0, 4, 1, 5, 2, 6, 3, 7][j] of word w);
+    ``scales`` (K / group, N); zero-points are stored as they are. Returns the same triple as
+    :func:`from_gptq`."""
+    if bits != 4:
+        raise ValueError("from_awq: 4-bit checkpoints only")
+    codes = _unpack_int32_fields(qweight, bits, _AWQ_ORDER)       # (K, N)
+    zeros = _unpack_int32_fields(qzeros, bits, _AWQ_ORDER)        # (groups, N)
+    qB = compress_codes(codes.t().contiguous().to(torch.uint8), bits)
+    return qB, scales.t().contiguous(), zeros.t().contiguous().to(torch.uint8)
