@@ -144,6 +144,15 @@ int b200dq_pack_weights(const void* q_natural, const void* scales, const void* z
 int b200dq_absmax_quant_int8(const void* x, void* q, float* scale, int32_t M, int32_t K, int32_t act_type,
                              void* cuda_stream);
 
+/* (M, K) f16/bf16 activations -> MXFP4 at block 32 along K: scale_bytes (M, K/32) e8m0 bytes
+ * with scale = 2^ceil(log2(amax / 6)) (amax clamped below at 6 * 2^-126), codes (M, K/2) bytes
+ * holding the e2m1 codes of x / scale, round to nearest even, the even k in the low nibble; a
+ * negative value that rounds to zero keeps its sign bit. K % 32 == 0. Replaces the activation
+ * quantiser of examples/deepseek_v4/act_quant.py:112-164 (whose cast to float4_e2m1fn is the
+ * same hardware conversion; its torch reference, :249-268, breaks ties downwards instead). */
+int b200dq_quant_mxfp4(const void* x, void* codes, void* scale_bytes, int32_t M, int32_t K, int32_t act_type,
+                       void* cuda_stream);
+
 /* Mixture-of-experts combine: out[t, :] = sum over s < top_k of weights[t*top_k + s] *
  * y[row_of[t*top_k + s], :], fp32 accumulation in slot order, one rounding to the row type.
  * Deterministic stand-in for the scatter-add of

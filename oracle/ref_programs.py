@@ -322,6 +322,32 @@ def ref_bitnet_linear(A_q, s_act, W_t, s_w, out_dtype: torch.dtype = torch.bfloa
     return out.to(out_dtype)
 
 
+# ---- bf16 -> MXFP4 activation quantiser --------------------------------------
+
+def mxfp4_act_quant(x: torch.Tensor, block_size: int = 32, ties: str = "down"):
+    """Per row and block: scale = 2^ceil(log2(amax / 6)) with amax clamped below at 6 * 2^-126,
+    y = clamp(x / scale, -6, 6), code = nearest e2m1 value (index + 8 for negative y).
+    examples/deepseek_v4/act_quant.py:249-268 (``fp4_act_quant_ref``), whose argmin breaks ties
+    towards the smaller magnitude (``ties="down"``); its kernel (:112-164) casts to
+    float4_e2m1fn, which rounds ties to even (``ties="even"``). Returns (codes (M, K) uint8,
+    scale (M, K / block) float32)."""
+    M, N = x.shape
+    xf = x.float().reshape(M, N // block_size, block_size)
+    amax = xf.abs().amax(dim=-1).clamp(min=6.0 * (2.0 ** -126))
+    scale = torch.pow(2.0, torch.ceil(torch.log2(amax / 6.0)))
+    y = (xf / scale.unsqueeze(-1)).clamp(-6.0, 6.0).reshape(M, N)
+    vals = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+    d = (y.abs().unsqueeze(-1) - vals).abs()
+    idx = d.argmin(dim=-1)                                   # first minimum: the smaller magnitude on a tie
+    if ties == "even":
+        nxt = (idx + 1).clamp(max=7)
+        tie = d.gather(-1, nxt.unsqueeze(-1)).squeeze(-1) == d.gather(-1, idx.unsqueeze(-1)).squeeze(-1)
+        idx = torch.where(tie & (idx % 2 == 1) & (nxt != idx), nxt, idx)
+    elif ties != "down":
+        raise ValueError(ties)
+    return torch.where(y < 0, idx + 8, idx).to(torch.uint8), scale
+
+
 # ---- MoE -------------------------------------------------------------------
 
 def moe_route(logits: torch.Tensor, top_k: int):

@@ -6,7 +6,10 @@ reference. Modules are loaded by file path because the example package's
 ``__init__`` needs a full TileLang build:
   examples/dequantize_gemm/dequantize_utils.py  (torch_convert, torch_convert_bit_twiddling)
   examples/dequantize_gemm/quantize/utils.py    (general_compress, interleave_weight, gen_quant4)
-  examples/dequantize_gemm/quantize/nvfp4.py    (e2m1 encode / pack / decode)
+  examples/dequantize_gemm/quantize/nvfp4.py    (e2m1 encode / pack / decode, UE4M3 codec, scale
+                                                 swizzle, quantize_bf16_to_nvfp4_blockscaled)
+  examples/deepseek_v4/act_quant.py             (fp4_act_quant_ref, the bf16 -> MXFP4 quantiser)
+  examples/deepseek_v4/fp8_fp4_gemm_1d1d_sm100.py (quantize_mxfp4_with_packed_ue8m0, group-major words)
 
     python tests/golden/make_golden.py
 """
@@ -76,6 +79,31 @@ def main():
     np.savez_compressed(os.path.join(HERE, "e2m1.npz"), vals=vals.numpy(), codes=codes.numpy(),
                         packed=packed.numpy(), decoded=nv.decode_packed_fp4_e2m1(packed).numpy(),
                         lut=np.array(nv._FP4_E2M1_VALUES, dtype=np.float32))
+    # --- block-scale formats: UE4M3 codec, scale swizzle, NVFP4 and MXFP4 quantisers ---------
+    aq = load("ref_act_quant", "examples/deepseek_v4/act_quant.py")
+    fg = load("ref_fp8_fp4_gemm", "examples/deepseek_v4/fp8_fp4_gemm_1d1d_sm100.py")
+    allbytes = torch.arange(256, dtype=torch.uint8)
+    sweep = torch.cat((torch.linspace(0, 0.05, 400), torch.linspace(0.05, 500, 600),
+                       torch.tensor([2.0 ** -9, 2.0 ** -6, 448.0, 1e9, float("nan"), -1.0])))
+    words = torch.randint(0, 2 ** 31, (256, 8), generator=g, dtype=torch.int64).to(torch.uint32)
+    xa = torch.randn((128, 256), generator=g).to(torch.bfloat16) * 3
+    xa[5, :16] = 0                                                      # an all-zero scale block
+    nv_packed, nv_words, nv_bytes = nv.quantize_bf16_to_nvfp4_blockscaled(xa, return_scale_bytes=True)
+    xm = (torch.randn((16, 256), generator=g) * torch.logspace(-3, 2, 16).unsqueeze(1)).to(torch.bfloat16)
+    q32, s32 = aq.fp4_act_quant_ref(xm, 32)
+    q128, w128, sf128 = fg.quantize_mxfp4_with_packed_ue8m0(xm.float(), 128)
+    np.savez_compressed(
+        os.path.join(HERE, "blockscale.npz"),
+        ue4m3_decode_all=nv.decode_ue4m3_scale_bytes(allbytes).numpy(), sweep=sweep.numpy(),
+        ue4m3_nearest=nv.encode_ue4m3_scale_bytes(sweep).numpy(),
+        ue4m3_ceil=nv.encode_ue4m3_scale_bytes(sweep, rounding="ceil").numpy(),
+        ue4m3_ceil_minpos=nv.encode_ue4m3_scale_bytes(sweep, rounding="ceil", min_positive=True).numpy(),
+        words=words.view(torch.int32).numpy(),
+        swizzled=nv.swizzle_blockscaled_chunk_kmajor_scale_words(words).view(torch.int32).numpy(),
+        xa=xa.view(torch.int16).numpy(), nv_packed=nv_packed.numpy(), nv_words=nv_words.view(torch.int32).numpy(),
+        nv_bytes=nv_bytes.numpy(),
+        xm=xm.view(torch.int16).numpy(), mx32_packed=q32.view(torch.uint8).numpy(), mx32_scale=s32.numpy(),
+        mx128_packed=q128.view(torch.uint8).numpy(), mx128_words=w128.view(torch.int32).numpy(), mx128_sf=sf128.numpy())
     print("wrote", sorted(f for f in os.listdir(HERE) if f.endswith(".npz")))
 
 

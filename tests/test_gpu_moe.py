@@ -65,6 +65,23 @@ def test_absmax_quant_int8_bit_exact(M, K, dtype):
     assert torch.equal(q.cpu(), q_ref)
 
 
+@pytest.mark.parametrize("M,K,dtype", [(1, 4096, torch.bfloat16), (300, 4096, torch.bfloat16), (33, 256, torch.float16)])
+def test_mxfp4_activation_quantiser_bit_exact(M, K, dtype):
+    """The CUDA quantiser against the oracle's restatement of act_quant.py with the hardware's
+    tie rule: codes and e8m0 bytes must be equal, over scales from 1e-3 to 1e2, with exact
+    midpoints, zeros and an all-zero block in the input."""
+    x = (torch.randn(M, K, generator=gen(7)) * torch.logspace(-3, 2, M).unsqueeze(1)).to(dtype)
+    x[0, :8] = torch.tensor([0.25, 0.75, 1.25, 1.75, 2.5, 3.5, 5.0, 6.0]).to(dtype)      # midpoints at scale 1
+    x[0, 8:32] = 0
+    x[-1, 32:64] = 0
+    codes, sf = ops.quant_mxfp4(x.to(DEV))
+    ref_codes, ref_scale = R.mxfp4_act_quant(x, 32, ties="even")
+    assert torch.equal(sf.cpu(), ((ref_scale.view(torch.int32) >> 23) & 0xFF).to(torch.uint8))
+    got = codes.cpu()
+    unpacked = torch.stack((got & 15, got >> 4), dim=-1).reshape(M, K)
+    assert torch.equal(unpacked, ref_codes)
+
+
 def test_moe_layer_matches_oracle():
     """64-expert layout scaled down: 8 experts, top-2, W1 (2F, H) and W2 (H, F), group 128,
     fp16-range scales, zero-point 8."""

@@ -148,3 +148,18 @@ def test_moe_oracle_routes_top_k():
     torch.manual_seed(0)
     w, idx = R.moe_route(torch.randn(5, 8), 2)
     assert idx.shape == (5, 2) and torch.all(w > 0) and torch.all(w.sum(-1) <= 1.0 + 1e-6)
+
+
+def test_mxfp4_activation_quantiser_matches_reference_outputs():
+    """``fp4_act_quant_ref`` of examples/deepseek_v4/act_quant.py:249-268 run on seeded inputs
+    (scales over five decades) when the fixtures were made."""
+    g = load("blockscale.npz")
+    x = torch.from_numpy(g["xm"]).view(torch.bfloat16)
+    codes, scale = R.mxfp4_act_quant(x, 32, ties="down")
+    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).numpy()
+    assert np.array_equal(packed, g["mx32_packed"])
+    assert np.array_equal(scale.numpy(), g["mx32_scale"])
+    # the hardware tie rule differs from the reference's argmin only on exact midpoints
+    even, _ = R.mxfp4_act_quant(x, 32, ties="even")
+    assert (even != codes).float().mean() < 0.02
+

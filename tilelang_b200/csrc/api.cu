@@ -634,6 +634,28 @@ int b200dq_silu_mul(const void* h, void* out, int64_t rows, int32_t H, int32_t a
   return 0;
 }
 
+int b200dq_quant_mxfp4(const void* x, void* codes, void* scale_bytes, int32_t M, int32_t K, int32_t act_type,
+                       void* cuda_stream) {
+  if (x == nullptr || codes == nullptr || scale_bytes == nullptr) return fail("quant_mxfp4: null pointer");
+  if (M <= 0 || K <= 0 || K % 32 != 0) return fail("quant_mxfp4: M=%d, K=%d (K must be a positive multiple of 32)", M, K);
+  if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(codes) & 3) != 0)
+    return fail("quant_mxfp4: x must be 16-byte and codes 4-byte aligned");
+  auto stream = static_cast<cudaStream_t>(cuda_stream);
+  const long long n_vec = static_cast<long long>(M) * K / 8;
+  const unsigned blocks = static_cast<unsigned>((n_vec + 255) / 256);
+  if (act_type == ACT_BF16)
+    quant_mxfp4_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
+                                                                   static_cast<uint32_t*>(codes),
+                                                                   static_cast<uint8_t*>(scale_bytes), n_vec);
+  else if (act_type == ACT_F16)
+    quant_mxfp4_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half*>(x), static_cast<uint32_t*>(codes),
+                                                            static_cast<uint8_t*>(scale_bytes), n_vec);
+  else
+    return fail("quant_mxfp4: input must be f16 or bf16");
+  CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
 int b200dq_check_status(void* cuda_stream) {
   DeviceState* ds = nullptr;
   if (current_device_state(&ds) != 0) return -1;

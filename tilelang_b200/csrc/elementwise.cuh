@@ -144,4 +144,53 @@ __global__ void __launch_bounds__(256) unpack_int4_to_int8_kernel(const uint2* _
   }
 }
 
+// bf16 / fp16 activations -> MXFP4: per row and 32 consecutive K elements one power-of-two
+// scale 2^ceil(log2(amax / 6)) (amax clamped below at 6 * 2^-126), codes = e2m1 of x / scale
+// by the hardware's round-to-nearest-even conversion, two per byte with the even k in the low
+// nibble, scale as an e8m0 byte. The reference's quantiser
+// (examples/deepseek_v4/act_quant.py:112-164) does the same with a cast to float4_e2m1fn.
+// One thread takes 8 elements (one 16-byte load, one 4-byte store); the four threads of a
+// block of 32 agree on the maximum with two shuffles. Pure streaming: 2 bytes in, 0.53 out.
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float hi, float lo) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u32.u8 %0, t;\n\t}" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) quant_mxfp4_kernel(const T* __restrict__ x, uint32_t* __restrict__ codes,
+                                                          uint8_t* __restrict__ scale_bytes, long long n_vec) {
+  // n_vec = M * K / 8 is a multiple of 4 (K % 32 == 0), so the four lanes of a block are
+  // in range together and the shuffles below see whole blocks
+  const long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const bool in_range = v < n_vec;
+  float f[8];
+  if (in_range) {
+    const uint4 raw = reinterpret_cast<const uint4*>(x)[v];
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = static_cast<float>(e[i]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) f[i] = 0.f;
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(f[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+  amax = fmaxf(amax, 6.0f * 1.17549435e-38f);                     // 6 * 2^-126
+  // smallest power of two >= amax / 6, from the exponent field
+  const uint32_t bits = __float_as_uint(amax / 6.0f);
+  uint32_t e8 = ((bits >> 23) & 0xffu) + ((bits & 0x7fffffu) != 0u ? 1u : 0u);
+  e8 = min(max(e8, 1u), 254u);
+  const float inv = __uint_as_float((254u - e8) << 23);           // 2^-(e8 - 127), exact
+  if (!in_range) return;
+  uint32_t word = 0;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) word |= cvt_e2m1x2(f[2 * i + 1] * inv, f[2 * i] * inv) << (8 * i);
+  codes[v] = word;
+  if ((threadIdx.x & 3) == 0) scale_bytes[v >> 2] = static_cast<uint8_t>(e8);
+}
+
 }  // namespace b200dq

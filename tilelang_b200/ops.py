@@ -350,6 +350,25 @@ def absmax_quant_int8(x: torch.Tensor):
     return q, s
 
 
+def quant_mxfp4(x: torch.Tensor):
+    """(M, K) float16/bfloat16 -> MXFP4 at block 32: returns (codes (M, K/2) uint8, two e2m1 codes
+    per byte, and scale bytes (M, K/32) uint8, e8m0). The CUDA version of
+    ``blockscale.quantize_mxfp4(x, 32, ties="even")``."""
+    lib = _lib.load()
+    _check_cuda_contig("x", x)
+    if x.dim() != 2 or x.dtype not in (torch.float16, torch.bfloat16) or x.shape[1] % 32:
+        raise ValueError("x must be a 2-D float16/bfloat16 tensor with K a multiple of 32")
+    M, K = x.shape
+    codes = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
+    sf = torch.empty((M, K // 32), dtype=torch.uint8, device=x.device)
+    if M:
+        _ensure_init(x.device)
+        with torch.cuda.device(x.device):
+            _lib.check(lib.b200dq_quant_mxfp4(x.data_ptr(), codes.data_ptr(), sf.data_ptr(), M, K, _ACT_OF[x.dtype],
+                                              _stream_ptr(x.device)), "b200dq_quant_mxfp4")
+    return codes, sf
+
+
 def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
     """``out[t] = sum_s weights[t, s] * y[row_of[t, s]]`` (fp32 accumulate, slot order).
     y (rows, H) f16/bf16; row_of (T, k) int64; weights (T, k) float32."""
