@@ -151,7 +151,21 @@ int b200dq_absmax_quant_int8(const void* x, void* q, float* scale, int32_t M, in
  * quantiser of examples/deepseek_v4/act_quant.py:112-164 (whose cast to float4_e2m1fn is the
  * same hardware conversion; its torch reference, :249-268, breaks ties downwards instead). */
 int b200dq_quant_mxfp4(const void* x, void* codes, void* scale_bytes, int32_t M, int32_t K, int32_t act_type,
-                       void* cuda_stream);
+                       int32_t sf_blocked, void* cuda_stream);
+/* With sf_blocked != 0 (K % 128 == 0) the scale bytes are written in the 128 x 4 blocked layout
+ * of b200dq_gemm_mxfp4_native instead of row-major: byte kb % 4 of the uint32 word
+ * [m / 128][kb / 4][m % 32][(m % 128) / 32]; the buffer holds ceil(M / 128) * 128 * K / 32 bytes and
+ * the rows beyond M must have been zeroed by the caller. */
+
+/* Native MXFP4 GEMM: C[M, N] = A * W^T with both operands as e2m1 codes (M, K/2) and (N, K/2)
+ * bytes, row-major, the even k in the low nibble, each with one e8m0 scale per 32 K elements in
+ * the 128 x 4 blocked layout above (for W: rows are weight rows, padded with zero words to a
+ * multiple of 128), multiplied by tcgen05.mma kind::mxf4.block_scale with fp32 accumulation.
+ * K % 256 == 0; out_type f16, bf16 or f32; no scratch. The reference has the pieces
+ * (src/tl_templates/cuda/tcgen_05.h:123-178, src/op/tcgen5_meta.h:273-335, the mainloop of
+ * examples/deepseek_v4/fp8_fp4_gemm_1d1d_sm100.py:18-185) but no packed-fp4 kind. */
+int b200dq_gemm_mxfp4_native(const void* a_codes, const void* a_sf, const void* w_codes, const void* w_sf, void* c,
+                             int32_t M, int32_t N, int32_t K, int32_t out_type, void* cuda_stream);
 
 /* Mixture-of-experts combine: out[t, :] = sum over s < top_k of weights[t*top_k + s] *
  * y[row_of[t*top_k + s], :], fp32 accumulation in slot order, one rounding to the row type.

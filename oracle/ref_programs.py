@@ -348,6 +348,20 @@ def mxfp4_act_quant(x: torch.Tensor, block_size: int = 32, ties: str = "down"):
     return torch.where(y < 0, idx + 8, idx).to(torch.uint8), scale
 
 
+def ref_mxfp4_native(A: torch.Tensor, qB: torch.Tensor, scale_bytes: torch.Tensor, out_dtype=torch.bfloat16):
+    """Both operands MXFP4: the activation is re-quantised per row and 32-block the way the
+    reference's kernel does (:func:`mxfp4_act_quant`, ties to even), then
+    C = dequant(A_q) @ dequant(W)^T in fp32 -- what a block-scaled fp4 x fp4 tensor-core GEMM
+    computes up to the order of the fp32 additions (every product of two e2m1 values and two
+    powers of two is exact). The block-scaled mainloop this stands for is
+    examples/deepseek_v4/fp8_fp4_gemm_1d1d_sm100.py:18-185 (fp8 x fp4 there)."""
+    codes, scale = mxfp4_act_quant(A, 32, ties="even")
+    vals = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0, -0.0, -0.5, -1.0, -1.5, -2.0, -3.0, -4.0, -6.0])
+    a = vals[codes.long()] * scale.repeat_interleave(32, dim=1)
+    w = dequant_mxfp4(qB, scale_bytes, 127, "e2m1").float()
+    return torch.matmul(a, w.T).to(out_dtype)
+
+
 # ---- MoE -------------------------------------------------------------------
 
 def moe_route(logits: torch.Tensor, top_k: int):

@@ -34,6 +34,7 @@ EXPORTED_SYMBOLS = (
     "b200dq_check_status",
     "b200dq_absmax_quant_int8",
     "b200dq_quant_mxfp4",
+    "b200dq_gemm_mxfp4_native",
     "b200dq_silu_mul",
     "b200dq_unpack_int4_to_int8",
     "b200dq_moe_combine",
@@ -105,7 +106,9 @@ def _declare(lib):
     lib.b200dq_absmax_quant_int8.restype = ctypes.c_int
     lib.b200dq_absmax_quant_int8.argtypes = [vp, vp, vp, i32, i32, i32, vp]
     lib.b200dq_quant_mxfp4.restype = ctypes.c_int
-    lib.b200dq_quant_mxfp4.argtypes = [vp, vp, vp, i32, i32, i32, vp]
+    lib.b200dq_quant_mxfp4.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+    lib.b200dq_gemm_mxfp4_native.restype = ctypes.c_int
+    lib.b200dq_gemm_mxfp4_native.argtypes = [vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
     lib.b200dq_silu_mul.restype = ctypes.c_int
     lib.b200dq_silu_mul.argtypes = [vp, vp, ctypes.c_int64, i32, i32, vp]
     lib.b200dq_unpack_int4_to_int8.restype = ctypes.c_int

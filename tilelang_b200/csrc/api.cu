@@ -21,6 +21,7 @@
 #include "umma_gemm.cuh"
 #include "skinny_launch.h"
 #include "umma_launch.h"
+#include "mxf4_launch.h"
 
 namespace {
 
@@ -635,9 +636,10 @@ int b200dq_silu_mul(const void* h, void* out, int64_t rows, int32_t H, int32_t a
 }
 
 int b200dq_quant_mxfp4(const void* x, void* codes, void* scale_bytes, int32_t M, int32_t K, int32_t act_type,
-                       void* cuda_stream) {
+                       int32_t sf_blocked, void* cuda_stream) {
   if (x == nullptr || codes == nullptr || scale_bytes == nullptr) return fail("quant_mxfp4: null pointer");
   if (M <= 0 || K <= 0 || K % 32 != 0) return fail("quant_mxfp4: M=%d, K=%d (K must be a positive multiple of 32)", M, K);
+  if (sf_blocked && K % 128 != 0) return fail("quant_mxfp4: the blocked scale layout needs K to be a multiple of 128");
   if ((reinterpret_cast<uintptr_t>(x) & 15) != 0 || (reinterpret_cast<uintptr_t>(codes) & 3) != 0)
     return fail("quant_mxfp4: x must be 16-byte and codes 4-byte aligned");
   auto stream = static_cast<cudaStream_t>(cuda_stream);
@@ -646,13 +648,53 @@ int b200dq_quant_mxfp4(const void* x, void* codes, void* scale_bytes, int32_t M,
   if (act_type == ACT_BF16)
     quant_mxfp4_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(static_cast<const __nv_bfloat16*>(x),
                                                                    static_cast<uint32_t*>(codes),
-                                                                   static_cast<uint8_t*>(scale_bytes), n_vec);
+                                                                   static_cast<uint8_t*>(scale_bytes), n_vec, K, sf_blocked);
   else if (act_type == ACT_F16)
     quant_mxfp4_kernel<__half><<<blocks, 256, 0, stream>>>(static_cast<const __half*>(x), static_cast<uint32_t*>(codes),
-                                                            static_cast<uint8_t*>(scale_bytes), n_vec);
+                                                            static_cast<uint8_t*>(scale_bytes), n_vec, K, sf_blocked);
   else
     return fail("quant_mxfp4: input must be f16 or bf16");
   CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+int b200dq_gemm_mxfp4_native(const void* a_codes, const void* a_sf, const void* w_codes, const void* w_sf, void* c,
+                             int32_t M, int32_t N, int32_t K, int32_t out_type, void* cuda_stream) {
+  if (a_codes == nullptr || a_sf == nullptr || w_codes == nullptr || w_sf == nullptr || c == nullptr)
+    return fail("gemm_mxfp4_native: null pointer");
+  if (M <= 0 || N <= 0 || K <= 0) return fail("gemm_mxfp4_native: M, N, K must be positive (got %d, %d, %d)", M, N, K);
+  if (K % 256 != 0) return fail("gemm_mxfp4_native: K=%d must be a multiple of 256", K);
+  if (out_type != OUT_BF16 && out_type != OUT_F16 && out_type != OUT_F32)
+    return fail("gemm_mxfp4_native: output must be f16, bf16 or f32");
+  for (const void* ptr : {a_codes, a_sf, w_codes, w_sf, static_cast<const void*>(c)})
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return fail("gemm_mxfp4_native: pointers must be 16-byte aligned");
+  DeviceState* ds = nullptr;
+  if (current_device_state(&ds) != 0) return -1;
+  CUtensorMap maps[2];
+  const void* bases[2] = {a_codes, w_codes};
+  const int rows[2] = {M, N};
+  for (int i = 0; i < 2; ++i) {
+    cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 2), static_cast<cuuint64_t>(rows[i])};
+    cuuint64_t strides[1] = {static_cast<cuuint64_t>(K / 2)};
+    cuuint32_t box[2] = {kMxf4BoxBytes, kMxf4BoxRows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = g_encode(&maps[i], CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(bases[i]), dims, strides, box, estr,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("gemm_mxfp4_native: cuTensorMapEncodeTiled failed with CUresult %d", static_cast<int>(r));
+  }
+  Mxf4Params p;
+  memset(&p, 0, sizeof(p));
+  p.sfa = static_cast<const uint32_t*>(a_sf);
+  p.sfw = static_cast<const uint32_t*>(w_sf);
+  p.c = c;
+  p.M = M; p.N = N; p.K = K;
+  p.m_tiles = (M + 127) / 128;
+  p.n_tiles = (N + 127) / 128;
+  p.k_blocks = K / 256;
+  p.out_type = out_type;
+  p.status = ds->status;
+  CUDA_OK(launch_mxf4_gemm(maps[0], maps[1], p, ds->sm_count, static_cast<cudaStream_t>(cuda_stream)));
   return 0;
 }
 

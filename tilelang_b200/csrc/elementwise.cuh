@@ -157,9 +157,13 @@ __device__ __forceinline__ uint32_t cvt_e2m1x2(float hi, float lo) {
   return r;
 }
 
+// `sf_blocked`: write the scale bytes in the 128 x 4 blocked word layout the block-scaled MMA's
+// scale-factor copy reads -- byte j of word [row block m / 128][k word kb / 4][m % 32][(m % 128) / 32]
+// for block kb = 4 * word + j -- instead of row-major (M, K / 32).
 template <typename T>
 __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const T* __restrict__ x, uint32_t* __restrict__ codes,
-                                                          uint8_t* __restrict__ scale_bytes, long long n_vec) {
+                                                          uint8_t* __restrict__ scale_bytes, long long n_vec,
+                                                          int K, int sf_blocked) {
   // n_vec = M * K / 8 is a multiple of 4 (K % 32 == 0), so the four lanes of a block are
   // in range together and the shuffles below see whole blocks
   const long long v = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
@@ -190,7 +194,18 @@ __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const T* __restrict__ 
 #pragma unroll
   for (int i = 0; i < 4; ++i) word |= cvt_e2m1x2(f[2 * i + 1] * inv, f[2 * i] * inv) << (8 * i);
   codes[v] = word;
-  if ((threadIdx.x & 3) == 0) scale_bytes[v >> 2] = static_cast<uint8_t>(e8);
+  if ((threadIdx.x & 3) == 0) {
+    long long at = v >> 2;                                         // row-major: m * (K / 32) + kb
+    if (sf_blocked) {
+      const int blocks_per_row = K >> 5;
+      const long long m = at / blocks_per_row;
+      const int kb = static_cast<int>(at - m * blocks_per_row);
+      const int r = static_cast<int>(m & 127);
+      const long long word = (m >> 7) * (static_cast<long long>(K >> 7) * 128) + ((kb >> 2) * 32 + (r & 31)) * 4 + (r >> 5);
+      at = word * 4 + (kb & 3);
+    }
+    scale_bytes[at] = static_cast<uint8_t>(e8);
+  }
 }
 
 }  // namespace b200dq

@@ -205,6 +205,44 @@ def matmul(M: int, N: int, K: int, in_dtype, out_dtype, accum_dtype, num_bits: i
     return DequantKernel("matmul", params, [-1], impl, pack_fn, desc)
 
 
+def matmul_mxfp4_native(M: int, N: int, K: int, in_dtype="bfloat16", out_dtype="bfloat16", accum_dtype="float32",
+                        scale_size: int = 32, **ignored) -> DequantKernel:
+    """``C[M, N] = quant_mxfp4(A) @ dequant(qB, Scale)^T`` on the block-scaled fp4 tensor-core
+    instruction: inputs ``(A, qB, Scale)`` as for ``matmul(..., source_format="fp4")``, but the
+    activation is re-quantised to MXFP4 (one e8m0 scale per row and 32 K elements, ties to even:
+    the kernel of examples/deepseek_v4/act_quant.py:112-164) and neither operand is dequantised:
+    ``tcgen05.mma kind::mxf4.block_scale`` multiplies the codes and applies both scales. Twice the
+    tensor rate of the dequantising path at a quarter of the activation bytes, at the price of a
+    4-bit activation. The mainloop it stands for is examples/deepseek_v4/
+    fp8_fp4_gemm_1d1d_sm100.py:18-185. K must be a multiple of 256. Also callable on an
+    activation quantised earlier: ``kernel.quantized(a_codes, a_sf, qB, Scale)``."""
+    in_t, out_t, acc_t = as_torch_dtype(in_dtype), as_torch_dtype(out_dtype), as_torch_dtype(accum_dtype)
+    if in_t not in (torch.float16, torch.bfloat16) or acc_t != torch.float32 or scale_size != 32:
+        raise ValueError("matmul_mxfp4_native: float16/bfloat16 activations, float32 accumulation, scale_size 32")
+    if K % 256:
+        raise ValueError("matmul_mxfp4_native: K must be a multiple of 256")
+    params = [Param("A", (M, K), in_t), Param("B", (N, K // 2), torch.uint8), Param("Scale", (N, K // 32), torch.uint8),
+              Param("C", (M, N), out_t)]
+
+    def pack_fn(scale):
+        return ops.block_mxfp4_scales(scale)
+
+    def quantized(a_codes, a_sf, qB, scale):
+        _check(qB, params[1], any_int8=True)
+        _check(scale, params[2])
+        return ops.gemm_mxfp4_native(a_codes, a_sf, qB.view(torch.uint8), kernel._packed(scale), out_dtype=out_t)
+
+    def impl(kernel_: DequantKernel, A, qB, scale):
+        _check(A, params[0])
+        a_codes, a_sf = ops.quant_mxfp4(A, blocked_scales=True)
+        return quantized(a_codes, a_sf, qB, scale)
+
+    kernel = DequantKernel("matmul_mxfp4_native", params, [-1], impl, pack_fn,
+                           f"b200dq kind::mxf4.block_scale: M={M} N={N} K={K} in={in_t} out={out_t}")
+    kernel.quantized = quantized
+    return kernel
+
+
 def _matmul_int8_unsigned(M: int, N: int, K: int, out_t: torch.dtype, acc_t: torch.dtype, extras) -> DequantKernel:
     """``C[M, N] int32 = A_int8 @ unpack_u4(qB)^T`` with the raw unsigned codes: the int8 -> int32
     variant of example_dequant_gemm_fine_grained.py (:427-428 run it with accum int32)."""

@@ -350,23 +350,66 @@ def absmax_quant_int8(x: torch.Tensor):
     return q, s
 
 
-def quant_mxfp4(x: torch.Tensor):
+def quant_mxfp4(x: torch.Tensor, blocked_scales: bool = False):
     """(M, K) float16/bfloat16 -> MXFP4 at block 32: returns (codes (M, K/2) uint8, two e2m1 codes
-    per byte, and scale bytes (M, K/32) uint8, e8m0). The CUDA version of
-    ``blockscale.quantize_mxfp4(x, 32, ties="even")``."""
+    per byte, and the e8m0 scale bytes). The CUDA version of
+    ``blockscale.quantize_mxfp4(x, 32, ties="even")``. The scale bytes are (M, K/32) row-major,
+    or with ``blocked_scales`` (K % 128 == 0) a (ceil(M/128) * 128, K/128) uint32 tensor in the
+    128 x 4 blocked layout the native MXFP4 GEMM reads (``blockscale.sf_swizzle_128x4``)."""
     lib = _lib.load()
     _check_cuda_contig("x", x)
     if x.dim() != 2 or x.dtype not in (torch.float16, torch.bfloat16) or x.shape[1] % 32:
         raise ValueError("x must be a 2-D float16/bfloat16 tensor with K a multiple of 32")
     M, K = x.shape
     codes = torch.empty((M, K // 2), dtype=torch.uint8, device=x.device)
-    sf = torch.empty((M, K // 32), dtype=torch.uint8, device=x.device)
+    if blocked_scales:
+        if K % 128:
+            raise ValueError("blocked scales need K to be a multiple of 128")
+        rows = (M + 127) // 128 * 128
+        sf = (torch.zeros if rows != M else torch.empty)((rows, K // 128), dtype=torch.int32, device=x.device)
+    else:
+        sf = torch.empty((M, K // 32), dtype=torch.uint8, device=x.device)
     if M:
         _ensure_init(x.device)
         with torch.cuda.device(x.device):
             _lib.check(lib.b200dq_quant_mxfp4(x.data_ptr(), codes.data_ptr(), sf.data_ptr(), M, K, _ACT_OF[x.dtype],
-                                              _stream_ptr(x.device)), "b200dq_quant_mxfp4")
-    return codes, sf
+                                              1 if blocked_scales else 0, _stream_ptr(x.device)), "b200dq_quant_mxfp4")
+    return codes, (sf.view(torch.uint32) if blocked_scales else sf)
+
+
+def block_mxfp4_scales(scale_bytes: torch.Tensor) -> torch.Tensor:
+    """Row-major e8m0 bytes (rows, K/32), K % 128 == 0 -> uint32 words in the 128 x 4 blocked layout
+    (rows zero-padded to a multiple of 128) for :func:`gemm_mxfp4_native`. Offline, once per weight."""
+    from . import blockscale
+    return blockscale.sf_swizzle_128x4(blockscale.sf_bytes_to_words(scale_bytes)).contiguous()
+
+
+def gemm_mxfp4_native(a_codes: torch.Tensor, a_sf: torch.Tensor, w_codes: torch.Tensor, w_sf: torch.Tensor,
+                      out_dtype: torch.dtype = torch.bfloat16, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """C = A @ W^T on tcgen05.mma kind::mxf4.block_scale. ``a_codes`` (M, K/2) and ``w_codes``
+    (N, K/2) uint8 e2m1 codes (even k in the low nibble), ``a_sf`` / ``w_sf`` their e8m0 scales as
+    blocked uint32 words (:func:`quant_mxfp4` with ``blocked_scales``, :func:`block_mxfp4_scales`).
+    K % 256 == 0."""
+    lib = _lib.load()
+    for name, t in (("a_codes", a_codes), ("a_sf", a_sf), ("w_codes", w_codes), ("w_sf", w_sf)):
+        _check_cuda_contig(name, t, a_codes.device)
+    M, Kb = a_codes.shape
+    N, K = w_codes.shape[0], 2 * Kb
+    if w_codes.shape[1] != Kb or a_codes.dtype != torch.uint8 or w_codes.dtype != torch.uint8:
+        raise ValueError("a_codes and w_codes must be uint8 with the same K/2 columns")
+    for name, t, rows in (("a_sf", a_sf, M), ("w_sf", w_sf, N)):
+        if t.dtype != torch.uint32 or tuple(t.shape) != ((rows + 127) // 128 * 128, K // 128):
+            raise ValueError(f"{name} must be uint32 of shape {((rows + 127) // 128 * 128, K // 128)} (blocked layout)")
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a_codes.device)
+    if M == 0:
+        return out
+    _ensure_init(a_codes.device)
+    with torch.cuda.device(a_codes.device):
+        _lib.check(lib.b200dq_gemm_mxfp4_native(a_codes.data_ptr(), a_sf.data_ptr(), w_codes.data_ptr(), w_sf.data_ptr(),
+                                                out.data_ptr(), M, N, K, _OUT_OF[out.dtype], _stream_ptr(a_codes.device)),
+                   "b200dq_gemm_mxfp4_native")
+    return out
 
 
 def moe_combine(y: torch.Tensor, row_of: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
