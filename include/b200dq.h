@@ -164,6 +164,14 @@ int b200dq_quant_mxfp4(const void* x, void* codes, void* scale_bytes, int32_t M,
  * K % 256 == 0; out_type f16, bf16 or f32; no scratch. The reference has the pieces
  * (src/tl_templates/cuda/tcgen_05.h:123-178, src/op/tcgen5_meta.h:273-335, the mainloop of
  * examples/deepseek_v4/fp8_fp4_gemm_1d1d_sm100.py:18-185) but no packed-fp4 kind. */
+/* Calibration, not a GEMM: launches one CTA per SM that issues `mmas` back-to-back
+ * tcgen05.mma instructions of shape 128 x 256 x (32 bytes of K) from shared memory and waits for
+ * them. kind 0: bf16 (kind::f16), 1: int8 (kind::i8), 2: MXFP4 (kind::mxf4.block_scale). *ops
+ * receives the arithmetic operations of the launch; the caller times it with events on the
+ * same stream. The rate is the tensor-pipe ceiling the integer and fp4 results are quoted
+ * against. No reference counterpart (its benchmarks quote nominal peaks). */
+int b200dq_tensor_peak(int32_t kind, int32_t mmas, double* ops, void* cuda_stream);
+
 int b200dq_gemm_mxfp4_native(const void* a_codes, const void* a_sf, const void* w_codes, const void* w_sf, void* c,
                              int32_t M, int32_t N, int32_t K, int32_t out_type, void* cuda_stream);
 

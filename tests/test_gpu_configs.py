@@ -105,6 +105,27 @@ def test_c3_mxfp4(c3_weight, M):
     check_float(f"C3 M={M}", C, torch.matmul(A.float(), W.T).to(torch.bfloat16))
 
 
+@pytest.mark.parametrize("M", [512, 8192])
+def test_c3_mxfp4_native_block_scaled(c3_weight, M):
+    """The same weight through tcgen05.mma kind::mxf4.block_scale with the activation
+    re-quantised to MXFP4 on the device: asserted against the oracle that applies the same
+    quantiser (codes and scale bytes bit for bit, GEMM within 1e-2); the distance to the
+    un-requantised bf16 x fp4 oracle is the price of the 4-bit activation and is printed."""
+    N, K, (qB, scale), W = c3_weight
+    A = torch.randn(M, K, generator=gen(200 + M)).to(torch.bfloat16)
+    a_codes, a_sf = ops.quant_mxfp4(A.to(DEV))
+    codes_ref, scale_ref = R.mxfp4_act_quant(A, 32, ties="even")
+    assert torch.equal(a_codes.cpu(), codes_ref[:, 0::2] | (codes_ref[:, 1::2] << 4))
+    assert torch.equal(a_sf.cpu(), (torch.log2(scale_ref) + 127).to(torch.uint8))
+    kernel = tb.matmul_mxfp4_native(M, N, K, "bfloat16", "bfloat16", "float32")
+    C = kernel(A.to(DEV), qB, scale)
+    tb.check_status()
+    check_float(f"C3 native M={M}", C, R.ref_mxfp4_native(A, qB.cpu(), scale.cpu(), torch.bfloat16))
+    full = torch.matmul(A.float(), W.T)
+    err = (C.float().cpu() - full).norm() / full.norm()
+    print(f"C3 native M={M}: relative Frobenius distance to the bf16 x fp4 oracle {err:.3f} (4-bit activation)")
+
+
 # ------------------------------- C4 ------------------------------------------
 
 @pytest.mark.parametrize("N,K", [(3200, 3200), (8640, 3200), (3200, 8640)])

@@ -467,10 +467,37 @@ def test_bitnet_ragged_k_64_tokens_repeated_cold_launches():
     for rep in range(25):
         for C in outs:
             flush.zero_()
-            ops.gemm(A_d, pw, out=C)
+            ops.gemm(A_d, pw, out=C, token_tile=64)      # an explicit tile keeps the tcgen05 kernel
         ops.check_status(torch.device(DEV))
         for C in outs:
             assert torch.equal(C, ref32), f"repetition {rep}"
+
+
+@pytest.mark.parametrize("bits", [2, 4])
+@pytest.mark.parametrize("M,N,K", [(1, 256, 256), (5, 200, 1088), (8, 3200, 3200), (16, 384, 8640), (17, 130, 320),
+                                   (32, 640, 2048), (25, 8640, 3200), (33, 256, 512)])
+def test_integer_decode_shape_kernel_bit_exact(bits, M, N, K):
+    """At most 32 tokens of int8 activations take the one-launch mma.sync kernel: exact against
+    the oracle, equal to the tcgen05 kernel (forced by an explicit token tile), for both code
+    widths, ragged N, K that is not a whole stage, the scaled bf16 output and C^T."""
+    hi = 1 << bits
+    off = hi // 2
+    Wq = torch.randint(0, hi, (N, K), generator=gen(bits), dtype=torch.uint8)
+    A = torch.randint(-128, 128, (M, K), generator=gen(7), dtype=torch.int8)
+    codes = quantize.compress_codes(Wq, bits).to(DEV)
+    pw = ops.pack_int2(codes, N, K, code_offset=off) if bits == 2 else ops.pack_int4_for_int8(codes, N, K, code_offset=off)
+    ref = torch.matmul(A.to(torch.int64), (Wq.to(torch.int64) - off).T).to(torch.int32)
+    C = ops.gemm(A.to(DEV), pw, out_dtype=torch.int32)
+    C_mma = ops.gemm(A.to(DEV), pw, out_dtype=torch.int32, token_tile=64)
+    Ct = ops.gemm(A.to(DEV), pw, out_dtype=torch.int32, trans_c=True)
+    tb.check_status()
+    assert torch.equal(C.cpu(), ref)
+    assert torch.equal(C, C_mma)
+    assert torch.equal(Ct.cpu(), ref.T)
+    s_act = (torch.rand(M, generator=gen(8)) * 20 + 1).to(DEV)
+    out = ops.gemm(A.to(DEV), pw, out_dtype=torch.bfloat16, row_scale=s_act, tensor_scale=3.0)
+    out_mma = ops.gemm(A.to(DEV), pw, out_dtype=torch.bfloat16, row_scale=s_act, tensor_scale=3.0, token_tile=64)
+    assert torch.equal(out, out_mma)
 
 
 def test_bitnet_decode_reference_flow():

@@ -22,6 +22,8 @@
 #include "skinny_launch.h"
 #include "umma_launch.h"
 #include "mxf4_launch.h"
+#include "peak_launch.h"
+#include "int8_skinny_launch.h"
 
 namespace {
 
@@ -281,6 +283,15 @@ bool takes_skinny_path(const b200dq_gemm_args* a) {
   return a->weight_format == WF_U4_SZ || a->weight_format == WF_U4_RAW || a->weight_format == WF_S4_RAW;
 }
 
+// Integer codes on int8 activations with at most 32 tokens go to the decode-shape kernel
+// (one launch, no scratch) under the same rule: dense, token tile left to the library.
+bool takes_int8_skinny_path(const b200dq_gemm_args* a) {
+  if (a->num_groups > 0 || a->M > 32 || a->token_tile != 0) return false;
+  if (a->act_type != ACT_I8) return false;
+  if (a->K % 16 != 0 || (reinterpret_cast<uintptr_t>(a->a) & 15) != 0) return false;
+  return a->weight_format == WF_I2_I8 || a->weight_format == WF_I4_I8;
+}
+
 // SM count of the current device once b200dq_init has run on it, else an upper bound that
 // needs no device (256 SMs), so that a size query never under-reports.
 int sm_count_or_bound() {
@@ -307,6 +318,7 @@ int static_scratch_need(const b200dq_gemm_args* a, int sm_count, size_t* need) {
   if (a->M <= 0 || a->N <= 0 || a->K <= 0)
     return fail("gemm: M, N, K must be positive (got %d, %d, %d)", a->M, a->N, a->K);
   Schedule s;
+  if (takes_int8_skinny_path(a)) { *need = 0; return 0; }
   const int tile = takes_skinny_path(a) ? kSkinnyTokens : a->token_tile;
   if (make_schedule(a->M, a->N, a->K, a->act_type, tile, a->max_ctas, sm_count, &s) != 0) return -1;
   *need = s.needs_scratch ? s.workspace_bytes : 0;
@@ -342,6 +354,27 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
     if (a->total_tiles <= 0) return fail("%s: grouped mode needs total_tiles > 0", who);
     if (a->token_tile == 0) return fail("%s: grouped mode needs an explicit token_tile (the prefix arrays depend on it)", who);
     if (a->flags & (GF_TRANS_C | GF_HAS_BIAS)) return fail("%s: grouped mode supports neither TRANS_C nor bias", who);
+  }
+  if (takes_int8_skinny_path(a)) {
+    GemmParams p;
+    memset(&p, 0, sizeof(p));
+    p.wp = static_cast<const uint8_t*>(a->wp);
+    p.a = a->a;
+    p.c = a->c;
+    p.bias = a->bias;
+    p.row_scale = a->row_scale;
+    p.tensor_scale = a->tensor_scale;
+    p.code_bias = a->code_bias;
+    p.M = a->M; p.N = a->N; p.K = a->K;
+    p.n_tiles = (a->N + kTileRows - 1) / kTileRows;
+    p.st_total = stages_for(a->K, ACT_I8);
+    p.stage_bytes = stage_bytes_for(wf, a->group_size);
+    p.ldc = (a->flags & GF_TRANS_C) ? a->M : a->N;
+    p.flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
+    p.out_type = a->out_type;
+    p.status = status;
+    CUDA_OK(launch_int8_skinny_gemm(wf, p, stream));
+    return 0;
   }
   const bool skinny = takes_skinny_path(a);
   Schedule s;
@@ -441,6 +474,7 @@ size_t b200dq_gemm_workspace_bytes_for(const b200dq_gemm_args* a) {
   if (a == nullptr || a->M <= 0 || a->N <= 0 || a->K <= 0) return 0;
   Schedule s;
   const bool grouped = a->num_groups > 0;
+  if (takes_int8_skinny_path(a)) return 0;
   const int tile = takes_skinny_path(a) ? kSkinnyTokens : a->token_tile;
   if (make_schedule(a->M, a->N, a->K, a->act_type, tile, a->max_ctas, sm_count_or_bound(), &s,
                     grouped ? a->total_tiles : -1) != 0) return 0;
@@ -695,6 +729,15 @@ int b200dq_gemm_mxfp4_native(const void* a_codes, const void* a_sf, const void* 
   p.out_type = out_type;
   p.status = ds->status;
   CUDA_OK(launch_mxf4_gemm(maps[0], maps[1], p, ds->sm_count, static_cast<cudaStream_t>(cuda_stream)));
+  return 0;
+}
+
+int b200dq_tensor_peak(int32_t kind, int32_t mmas, double* ops, void* cuda_stream) {
+  if (kind < 0 || kind > 2) return fail("tensor_peak: kind must be 0 (bf16), 1 (int8) or 2 (mxfp4)");
+  if (mmas <= 0 || mmas > (1 << 22)) return fail("tensor_peak: mmas=%d outside [1, 2^22]", mmas);
+  DeviceState* ds = nullptr;
+  if (current_device_state(&ds) != 0) return -1;
+  CUDA_OK(launch_tensor_peak(kind, mmas, ds->sm_count, ds->status, ops, static_cast<cudaStream_t>(cuda_stream)));
   return 0;
 }
 

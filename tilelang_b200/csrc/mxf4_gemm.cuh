@@ -49,39 +49,6 @@ struct Mxf4Ctl {
   int abort_flag;
 };
 
-// tcgen05.cp: 32 rows x 128 bits from shared memory to the same four TMEM columns of all four
-// lane quarters.
-__device__ __forceinline__ void tmem_cp_32x128b_warpx4(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-
-// Shared-memory descriptor of a scale-factor piece: 32 rows of 16 bytes, no swizzle
-// (start address, stride between 8-row groups 128 B, descriptor version 1).
-__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
-  d |= static_cast<uint64_t>(128 >> 4) << 32;
-  d |= static_cast<uint64_t>(1) << 46;
-  return d;
-}
-
-// Block-scaled instruction descriptor for kind::mxf4: e2m1 x e2m1 (format 1), e8m0 scales,
-// both operands K-major, dense, K = 64 per instruction. The two scale-factor ids pick the
-// byte pair of the 4-byte scale word the instruction uses.
-__host__ __device__ constexpr uint32_t make_idesc_mxf4(uint32_t mma_m, uint32_t mma_n, uint32_t a_sf_id, uint32_t b_sf_id) {
-  return (b_sf_id << 4) | (1u << 7) | (1u << 10) | ((mma_n >> 3) << 17) | (1u << 23) | ((mma_m >> 4) << 24) |
-         (a_sf_id << 29);
-}
-
-__device__ __forceinline__ void umma_mxf4_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
-                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}" ::"r"(d_tmem),
-      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
-      : "memory");
-}
-
 __global__ void __launch_bounds__(kMxf4Threads, 1)
 mxf4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_w,
                  const Mxf4Params p) {

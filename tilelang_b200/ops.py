@@ -377,6 +377,27 @@ def quant_mxfp4(x: torch.Tensor, blocked_scales: bool = False):
     return codes, (sf.view(torch.uint32) if blocked_scales else sf)
 
 
+def tensor_peak(kind: str, mmas: int = 16384, repeats: int = 5, device=None) -> float:
+    """Measured rate (operations per second) of back-to-back ``tcgen05.mma`` of one kind on this
+    GPU: "bf16", "int8" or "mxfp4". Best of ``repeats`` launches timed with events."""
+    lib = _lib.load()
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    code = {"bf16": 0, "int8": 1, "mxfp4": 2}[kind]
+    _ensure_init(device)
+    ops_out = ctypes.c_double(0.0)
+    best = float("inf")
+    with torch.cuda.device(device):
+        for _ in range(repeats + 1):
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            _lib.check(lib.b200dq_tensor_peak(code, mmas, ctypes.byref(ops_out), _stream_ptr(device)), "b200dq_tensor_peak")
+            stop.record()
+            stop.synchronize()
+            best = min(best, start.elapsed_time(stop))
+    check_status(device)
+    return ops_out.value / (best * 1e-3)
+
+
 def block_mxfp4_scales(scale_bytes: torch.Tensor) -> torch.Tensor:
     """Row-major e8m0 bytes (rows, K/32), K % 128 == 0 -> uint32 words in the 128 x 4 blocked layout
     (rows zero-padded to a multiple of 128) for :func:`gemm_mxfp4_native`. Offline, once per weight."""
