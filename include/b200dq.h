@@ -87,7 +87,12 @@ typedef struct b200dq_gemm_args {
    * group_tile_prefix[g] = sum over earlier groups of ceil(rows / token_tile) * ceil(N / 128);
    * total_tiles is its last entry. Both prefix arrays are int32 device arrays of
    * num_groups + 1 entries; M is the total number of rows. Same semantics as the grouped
-   * GEMM of examples/grouped_gemm/example_grouped_gemm_fwd.py:8-36 with dequantised weights. */
+   * GEMM of examples/grouped_gemm/example_grouped_gemm_fwd.py:8-36 with dequantised weights.
+   * When the group sizes exist only on the device (a router's counts), fill the prefix
+   * arrays with b200dq_grouped_prefixes and pass total_tiles = -(an upper bound of the tile
+   * total), e.g. -(ceil(M / token_tile) + num_groups) * ceil(N / 128): the grid is planned
+   * for the bound and the kernel cuts the real total, read from group_tile_prefix[num_groups],
+   * evenly over it. No host synchronisation is needed then. */
   const int32_t* group_row_prefix;
   const int32_t* group_tile_prefix;
   int64_t group_weight_stride;
@@ -115,6 +120,11 @@ size_t b200dq_gemm_workspace_bytes(int32_t M, int32_t N, int32_t K, int32_t weig
  * schedule follows total_tiles (every group rounds up to whole tiles) and not M. The
  * pointers in the struct are not read. */
 size_t b200dq_gemm_workspace_bytes_for(const b200dq_gemm_args* args);
+
+/* Device-side row and tile prefixes (num_groups + 1 int32 entries each) of a grouped call
+ * from per-group row counts in device memory (int32, or int64 when counts_are_int64 != 0). */
+int b200dq_grouped_prefixes(const void* counts, int32_t counts_are_int64, int32_t num_groups, int32_t N,
+                            int32_t token_tile, int32_t* row_prefix, int32_t* tile_prefix, void* cuda_stream);
 
 /* Bytes of the packed weight image (codes and scale words) for an (N, K) weight. */
 size_t b200dq_packed_weight_bytes(int32_t N, int32_t K, int32_t group_size, int32_t weight_format);

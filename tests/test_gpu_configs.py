@@ -193,6 +193,28 @@ def test_c5_grouped_gemms_at_full_token_count(c5_experts):
                     R.ref_w4a16(a[rows], w2_q[e], w2_s[e], None, group, torch.bfloat16))
 
 
+def test_c5_grouped_gemm_with_device_counts(c5_experts):
+    """Counts left on the device (prefixes and the cut of the work computed there, no host
+    wait) against the host-planned call: the same products, cut between CTAs at other places, so
+    equal up to the order of fp32 additions -- at most one bf16 rounding apart, and rarely."""
+    E, H, F, group, (w1_q, w1_s, w1_p), _ = c5_experts
+    T, k = 4096, 6
+    logits = torch.randn(T, E, generator=gen(7))
+    _, experts = moe.route(logits, k)
+    counts = torch.bincount(experts.reshape(-1), minlength=E)
+    counts[5] += counts[6]                      # one empty group and one large one
+    counts[6] = 0
+    x = torch.randn(T * k, H, generator=gen(8)).to(torch.bfloat16).to(DEV)
+    h_host = ops.gemm_grouped(x, w1_p, counts.tolist())
+    h_dev = ops.gemm_grouped(x, w1_p, counts.to(DEV))
+    h_dev32 = ops.gemm_grouped(x, w1_p, counts.to(torch.int32).to(DEV), token_tile=128)
+    tb.check_status()
+    for other in (h_dev, h_dev32):
+        diff = (other.float() - h_host.float()).abs()
+        assert float((diff > 0).float().mean()) < 1e-2
+        assert R.max_rel_error(other.float().cpu(), h_host.float().cpu()) <= 8e-3
+
+
 def test_c5_moe_layer_64_experts_top6(c5_experts):
     """The whole layer (route, dispatch, W1, silu * up, W2, weighted combine) at 64 experts,
     top-6, 16384 tokens against the oracle's per-expert loop."""

@@ -36,6 +36,7 @@ EXPORTED_SYMBOLS = (
     "b200dq_quant_mxfp4",
     "b200dq_gemm_mxfp4_native",
     "b200dq_tensor_peak",
+    "b200dq_grouped_prefixes",
     "b200dq_silu_mul",
     "b200dq_unpack_int4_to_int8",
     "b200dq_moe_combine",
@@ -108,6 +109,8 @@ def _declare(lib):
     lib.b200dq_absmax_quant_int8.argtypes = [vp, vp, vp, i32, i32, i32, vp]
     lib.b200dq_quant_mxfp4.restype = ctypes.c_int
     lib.b200dq_quant_mxfp4.argtypes = [vp, vp, vp, i32, i32, i32, i32, vp]
+    lib.b200dq_grouped_prefixes.restype = ctypes.c_int
+    lib.b200dq_grouped_prefixes.argtypes = [vp, i32, i32, i32, i32, vp, vp, vp]
     lib.b200dq_tensor_peak.restype = ctypes.c_int
     lib.b200dq_tensor_peak.argtypes = [i32, i32, ctypes.POINTER(ctypes.c_double), vp]
     lib.b200dq_gemm_mxfp4_native.restype = ctypes.c_int

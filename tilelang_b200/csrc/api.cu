@@ -351,7 +351,7 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   if (grouped) {
     if (a->group_row_prefix == nullptr || a->group_tile_prefix == nullptr)
       return fail("%s: grouped mode needs group_row_prefix and group_tile_prefix", who);
-    if (a->total_tiles <= 0) return fail("%s: grouped mode needs total_tiles > 0", who);
+    if (a->total_tiles == 0) return fail("%s: grouped mode needs total_tiles (or minus an upper bound of it)", who);
     if (a->token_tile == 0) return fail("%s: grouped mode needs an explicit token_tile (the prefix arrays depend on it)", who);
     if (a->flags & (GF_TRANS_C | GF_HAS_BIAS)) return fail("%s: grouped mode supports neither TRANS_C nor bias", who);
   }
@@ -378,8 +378,13 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   }
   const bool skinny = takes_skinny_path(a);
   Schedule s;
+  // total_tiles < 0: the group sizes are known on the device only; plan the grid for the bound
+  // and let the kernel cut the real total (group_tile_prefix[num_groups]) evenly over it
+  const bool dyn = grouped && a->total_tiles < 0;
+  const long long plan_tiles = grouped ? (dyn ? -static_cast<long long>(a->total_tiles) : a->total_tiles) : -1;
   if (make_schedule(a->M, a->N, a->K, act, skinny ? kSkinnyTokens : a->token_tile, a->max_ctas, sm_count, &s,
-                    grouped ? a->total_tiles : -1) != 0) return -1;
+                    plan_tiles) != 0) return -1;
+  if (dyn && s.grid > 1) s.needs_scratch = true;
   if (s.needs_scratch) {
     if (scratch == nullptr || scratch_bytes < s.workspace_bytes)
       return fail("%s: workspace too small: need %zu bytes, got %zu", who, s.workspace_bytes, scratch_bytes);
@@ -419,6 +424,7 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   p.out_type = a->out_type;
   p.tn = s.tn;
   p.num_groups = grouped ? a->num_groups : 0;
+  p.dyn_grid = dyn ? s.grid : 0;
   p.grp_row_prefix = grouped ? a->group_row_prefix : nullptr;
   p.grp_tile_prefix = grouped ? a->group_tile_prefix : nullptr;
   p.grp_w_stride = grouped ? a->group_weight_stride : 0;
@@ -476,8 +482,8 @@ size_t b200dq_gemm_workspace_bytes_for(const b200dq_gemm_args* a) {
   const bool grouped = a->num_groups > 0;
   if (takes_int8_skinny_path(a)) return 0;
   const int tile = takes_skinny_path(a) ? kSkinnyTokens : a->token_tile;
-  if (make_schedule(a->M, a->N, a->K, a->act_type, tile, a->max_ctas, sm_count_or_bound(), &s,
-                    grouped ? a->total_tiles : -1) != 0) return 0;
+  const long long tiles = grouped ? (a->total_tiles < 0 ? -static_cast<long long>(a->total_tiles) : a->total_tiles) : -1;
+  if (make_schedule(a->M, a->N, a->K, a->act_type, tile, a->max_ctas, sm_count_or_bound(), &s, tiles) != 0) return 0;
   return s.workspace_bytes;
 }
 
@@ -738,6 +744,18 @@ int b200dq_tensor_peak(int32_t kind, int32_t mmas, double* ops, void* cuda_strea
   DeviceState* ds = nullptr;
   if (current_device_state(&ds) != 0) return -1;
   CUDA_OK(launch_tensor_peak(kind, mmas, ds->sm_count, ds->status, ops, static_cast<cudaStream_t>(cuda_stream)));
+  return 0;
+}
+
+int b200dq_grouped_prefixes(const void* counts, int32_t counts_are_int64, int32_t num_groups, int32_t N,
+                            int32_t token_tile, int32_t* row_prefix, int32_t* tile_prefix, void* cuda_stream) {
+  if (counts == nullptr || row_prefix == nullptr || tile_prefix == nullptr) return fail("grouped_prefixes: null pointer");
+  if (num_groups <= 0 || N <= 0) return fail("grouped_prefixes: num_groups and N must be positive");
+  if (token_tile != 16 && token_tile != 32 && token_tile != 64 && token_tile != 128 && token_tile != 256)
+    return fail("grouped_prefixes: token_tile must be 16, 32, 64, 128 or 256 (got %d)", token_tile);
+  grouped_prefix_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(
+      counts, counts_are_int64, num_groups, (N + kTileRows - 1) / kTileRows, token_tile, row_prefix, tile_prefix);
+  CUDA_OK(cudaGetLastError());
   return 0;
 }
 

@@ -208,4 +208,32 @@ __global__ void __launch_bounds__(256) quant_mxfp4_kernel(const T* __restrict__ 
   }
 }
 
+// Row and tile prefixes of a grouped GEMM from per-group row counts that live on the device
+// (a router's bincount): row_prefix[g] = rows before group g, tile_prefix[g] = tiles before it,
+// a group of c rows having ceil(c / token_tile) * n_tiles tiles. One warp, a shuffle scan per 32 groups.
+__global__ void grouped_prefix_kernel(const void* counts, int is_int64, int num_groups, int n_tiles, int token_tile,
+                                      int32_t* __restrict__ row_prefix, int32_t* __restrict__ tile_prefix) {
+  const int lane = threadIdx.x;
+  int rows_before = 0, tiles_before = 0;
+  for (int base = 0; base < num_groups; base += 32) {
+    const int g = base + lane;
+    int c = 0;
+    if (g < num_groups)
+      c = is_int64 ? static_cast<int>(static_cast<const long long*>(counts)[g]) : static_cast<const int*>(counts)[g];
+    int r = c, t = ((c + token_tile - 1) / token_tile) * n_tiles;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const int ru = __shfl_up_sync(0xffffffffu, r, d), tu = __shfl_up_sync(0xffffffffu, t, d);
+      if (lane >= d) { r += ru; t += tu; }
+    }
+    if (g < num_groups) {
+      row_prefix[g + 1] = rows_before + r;
+      tile_prefix[g + 1] = tiles_before + t;
+    }
+    rows_before += __shfl_sync(0xffffffffu, r, 31);
+    tiles_before += __shfl_sync(0xffffffffu, t, 31);
+  }
+  if (lane == 0) { row_prefix[0] = 0; tile_prefix[0] = 0; }
+}
+
 }  // namespace b200dq

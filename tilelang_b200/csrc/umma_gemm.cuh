@@ -100,6 +100,8 @@ struct GemmParams {
   const int* grp_tile_prefix;    // num_groups + 1 entries, device memory
   long long grp_w_stride;
   int num_groups;
+  int dyn_grid;                  // > 0: grouped mode planned on the device -- the tile total is read from
+                                 // grp_tile_prefix[num_groups] and cut evenly over dyn_grid CTAs (span, units unused)
   int tn;                        // tokens per tile (the kernel's TN)
   DeviceStatus* status;
 };
@@ -202,14 +204,28 @@ __device__ __forceinline__ void locate_tile(const GemmParams& p, long long tile,
   }
 }
 
+// Units (tile, stage pairs) of the problem and units per CTA: the host's plan, or, when the
+// group sizes are known only on the device, an even cut of the tile total found there.
+__device__ __forceinline__ void plan_of(const GemmParams& p, long long& units, long long& span) {
+  if (p.dyn_grid > 0) {
+    units = static_cast<long long>(p.grp_tile_prefix[p.num_groups]) * p.st_total;
+    span = (units + p.dyn_grid - 1) / p.dyn_grid;
+  } else {
+    units = p.units;
+    span = p.span;
+  }
+}
+
 // Walks the segments of this CTA's span; every warp role runs the same walk.
 struct SegmentWalk {
   long long pos, end;
   bool first;
   __device__ __forceinline__ SegmentWalk(const GemmParams& p) {
-    pos = static_cast<long long>(blockIdx.x) * p.span;
-    end = pos + p.span;
-    if (end > p.units) end = p.units;
+    long long units, span;
+    plan_of(p, units, span);
+    pos = static_cast<long long>(blockIdx.x) * span;
+    end = pos + span;
+    if (end > units) end = units;
     first = true;
   }
   __device__ __forceinline__ bool next(const GemmParams& p, Segment& s) {
@@ -717,15 +733,18 @@ template <typename OutT, int TN, bool kIntAcc>
 __global__ void __launch_bounds__(kTileRows)
 streamk_fixup_kernel(const GemmParams p) {
   constexpr int TCH = fixup_tokens_per_block(TN);
-  const long long pos = static_cast<long long>(blockIdx.x + 1) * p.span;
-  if (pos >= p.units) return;
+  long long units, span;
+  plan_of(p, units, span);
+  if (span == 0 || span % p.st_total == 0) return;          // no tile is cut
+  const long long pos = static_cast<long long>(blockIdx.x + 1) * span;
+  if (pos >= units) return;
   const long long tile = pos / p.st_total;
   const long long t_begin = tile * p.st_total;
   const long long t_end = t_begin + p.st_total;
   if (pos == t_begin) return;                               // the cut is a tile boundary
-  const int c_first = static_cast<int>(t_begin / p.span);
+  const int c_first = static_cast<int>(t_begin / span);
   if (static_cast<int>(blockIdx.x) != c_first) return;      // an earlier cut owns this tile
-  const int c_last = static_cast<int>((t_end - 1) / p.span);
+  const int c_last = static_cast<int>((t_end - 1) / span);
   Segment seg;
   locate_tile(p, tile, seg);
   const int row = threadIdx.x;
@@ -738,7 +757,7 @@ streamk_fixup_kernel(const GemmParams p) {
   for (int jj = 0; jj < TCH; ++jj) { facc[jj] = 0.f; iacc[jj] = 0; }
   for (int cta = c_first; cta <= c_last; ++cta) {
     // slot 0 if this tile holds the first segment of that CTA's span, else slot 1
-    const long long span_begin = static_cast<long long>(cta) * p.span;
+    const long long span_begin = static_cast<long long>(cta) * span;
     const int slot = cta * 2 + ((span_begin >= t_begin) ? 0 : 1);
     const uint32_t* src = p.partial + (static_cast<size_t>(slot) * TN + j0) * kTileRows + row;
     uint32_t raw[TCH];

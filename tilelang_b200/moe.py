@@ -80,7 +80,8 @@ def moe_forward(x: torch.Tensor, logits: torch.Tensor, top_k: int, num_experts: 
     weights, experts = route(logits, top_k)
     order, token_of_row, counts = sort_by_expert(experts, num_experts)
     x_sorted = x.index_select(0, token_of_row)
-    y = mlp(x_sorted, counts.tolist())
+    # on a GPU the counts stay on the device: the grouped GEMMs plan their work there
+    y = mlp(x_sorted, counts if counts.is_cuda else counts.tolist())
     return mlp.combine(y, rows_of_tokens(order, top_k), weights.contiguous())
 
 
@@ -104,22 +105,26 @@ def moe_forward_ep(x_local: torch.Tensor, logits_local: torch.Tensor, top_k: int
     flat_counts = counts.new_empty(world * num_experts)
     dist.all_gather_into_tensor(flat_counts, counts.contiguous(), group=group)
     all_counts_dev = flat_counts.view(world, num_experts)
-    all_counts = all_counts_dev.cpu()                                       # (world, E)
+    # The one host wait of the layer: the split sizes of the two all-to-alls are host
+    # arguments. Only the per-rank totals come to the host (2 * world numbers); the per-expert
+    # counts stay on the device and the grouped GEMMs plan their work there.
     my = ranges[rank]
-    send_rows = [int(all_counts[rank, r.start:r.stop].sum()) if len(r) else 0 for r in ranges]
-    mine = all_counts[:, my.start:my.stop] if len(my) else all_counts[:, :0]   # (world, local experts)
-    recv_rows = mine.sum(1).tolist()
+    bounds = torch.tensor([r.start for r in ranges] + [ranges[-1].stop], device=counts.device)
+    csum = torch.cat((all_counts_dev.new_zeros(world, 1), all_counts_dev.cumsum(1)), dim=1)    # (world, E + 1)
+    per_rank = csum[:, bounds[1:]] - csum[:, bounds[:-1]]                  # [source rank, owner rank] rows
+    totals = torch.stack((per_rank[rank], per_rank[:, rank])).cpu()        # what I send to / receive from each rank
+    send_rows, recv_rows = totals[0].tolist(), totals[1].tolist()
+    mine_dev = all_counts_dev[:, my.start:my.stop]                         # (world, local experts)
 
     recv = x_sorted.new_empty((sum(recv_rows), x_sorted.shape[1]))
     dist.all_to_all_single(recv, x_sorted.contiguous(), recv_rows, send_rows, group=group)
 
     # received rows are ordered (source rank, expert); regroup them by expert for the grouped GEMM
     local_ids = torch.arange(len(my), device=recv.device).repeat(world)
-    src_expert = torch.repeat_interleave(local_ids, all_counts_dev[:, my.start:my.stop].reshape(-1),
-                                         output_size=sum(recv_rows))
+    src_expert = torch.repeat_interleave(local_ids, mine_dev.reshape(-1), output_size=sum(recv_rows))
     regroup = torch.argsort(src_expert, stable=True)
-    local_counts = mine.sum(0).tolist()
-    y_grouped = local_mlp(recv.index_select(0, regroup), local_counts)
+    local_counts = mine_dev.sum(0)
+    y_grouped = local_mlp(recv.index_select(0, regroup), local_counts if local_counts.is_cuda else local_counts.tolist())
     y = torch.empty_like(y_grouped)
     y.index_copy_(0, regroup, y_grouped)                                   # back to (source rank, expert) order
 

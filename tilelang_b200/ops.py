@@ -296,7 +296,9 @@ def gemm_grouped(A: torch.Tensor, w: PackedWeight, counts, out: Optional[torch.T
                  out_dtype: Optional[torch.dtype] = None, token_tile: int = 256) -> torch.Tensor:
     """Grouped GEMM: rows of ``A`` are sorted by group, group g has ``counts[g]`` rows and
     multiplies its own weight ``w`` (from :func:`stack_packed`). ``counts`` is a host
-    sequence (the schedule is planned on the host)."""
+    sequence (the schedule is planned on the host) or an int32/int64 tensor on A's device
+    (a router's bincount): then the prefixes are built and the work is cut on the device and
+    the host never waits for the counts; they must sum to A's row count (not checked)."""
     lib = _lib.load()
     _check_cuda_contig("A", A)
     dev = A.device
@@ -304,17 +306,32 @@ def gemm_grouped(A: torch.Tensor, w: PackedWeight, counts, out: Optional[torch.T
     if G <= 0 or len(counts) != G:
         raise ValueError(f"counts must have one entry per group ({G})")
     M = A.shape[0]
-    rows, tiles = grouped_prefixes(counts, w.N, token_tile)
-    if rows[-1] != M:
-        raise ValueError(f"counts sum to {rows[-1]}, A has {M} rows")
     if A.shape[1] != w.K or _ACT_OF.get(A.dtype) != w.act_type:
         raise ValueError("A does not match the packed weights")
     if out is None:
         out = torch.empty((M, w.N), dtype=out_dtype or A.dtype, device=dev)
-    if M == 0 or tiles[-1] == 0:
-        return out
-    _ensure_init(dev)
-    prefix = torch.tensor(rows + tiles, dtype=torch.int32).to(dev, non_blocking=True)
+    on_device = isinstance(counts, torch.Tensor) and counts.is_cuda
+    if on_device:
+        if counts.device != dev or counts.dtype not in (torch.int32, torch.int64) or not counts.is_contiguous():
+            raise ValueError("device counts must be a contiguous int32/int64 tensor on A's device")
+        if M == 0:
+            return out
+        _ensure_init(dev)
+        prefix = torch.empty(2 * (G + 1), dtype=torch.int32, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(lib.b200dq_grouped_prefixes(counts.data_ptr(), 1 if counts.dtype == torch.int64 else 0, G, w.N,
+                                                   token_tile, prefix.data_ptr(), prefix.data_ptr() + 4 * (G + 1),
+                                                   _stream_ptr(dev)), "b200dq_grouped_prefixes")
+        total_tiles = -((M // token_tile + G) * ((w.N + 127) // 128))          # minus an upper bound
+    else:
+        rows, tiles = grouped_prefixes(counts, w.N, token_tile)
+        if rows[-1] != M:
+            raise ValueError(f"counts sum to {rows[-1]}, A has {M} rows")
+        if M == 0 or tiles[-1] == 0:
+            return out
+        _ensure_init(dev)
+        prefix = torch.tensor(rows + tiles, dtype=torch.int32).to(dev, non_blocking=True)
+        total_tiles = tiles[-1]
     args = _lib.GemmArgs(
         a=A.data_ptr(), wp=w.wp.data_ptr(), bias=None, row_scale=None, c=out.data_ptr(),
         workspace=None, workspace_bytes=0,
@@ -322,7 +339,7 @@ def gemm_grouped(A: torch.Tensor, w: PackedWeight, counts, out: Optional[torch.T
         out_type=_OUT_OF[out.dtype], flags=0, tensor_scale=1.0, code_bias=w.code_bias, fp4_exp_bias=w.fp4_exp_bias,
         token_tile=token_tile, max_ctas=0,
         group_row_prefix=prefix.data_ptr(), group_tile_prefix=prefix.data_ptr() + 4 * (G + 1),
-        group_weight_stride=w.group_stride, num_groups=G, total_tiles=tiles[-1])
+        group_weight_stride=w.group_stride, num_groups=G, total_tiles=total_tiles)
     # the grouped schedule follows total_tiles, not M: size the scratch from the arguments
     workspace = workspace_for(dev, lib.b200dq_gemm_workspace_bytes_for(ctypes.byref(args)))
     args.workspace, args.workspace_bytes = workspace.data_ptr(), workspace.numel()
