@@ -446,6 +446,11 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = flops * args.steps / t.item() / 1e12
 
+    # ---- what the other ranks take part in: the gather of C and the expert-parallel layer ----
+    multi = {}
+    if world > 1:
+        multi = multi_gpu_extras(args, rank, world, local_rank, A, pw, n_local, ms_step)
+
     if rank != 0:
         return
 
@@ -535,30 +540,131 @@ def run_ours(args, rank, world, local_rank):
         "configs": configs,
         "e2e_small": e2e_small,
     }
+    out.update(multi)
     print(json.dumps(out))
+
+
+def multi_gpu_extras(args, rank, world, local_rank, A, pw, n_local, ms_plain):
+    """The collectives of the sharded path, measured on the same shards as the headline step.
+
+    ``with_allgather``: the column-parallel GEMM followed by the all-gather of C that a
+    replicated consumer needs, (a) one gather after the GEMM and (b) the GEMM cut into token
+    chunks whose gathers run on NCCL's stream under the next chunk's GEMM. The gathered tensor
+    is (world, M, N / world): rank-major column blocks.
+    ``moe_ep``: the expert-parallel MoE layer (two all-to-alls per step) with its efficiency
+    against the same layer on one GPU, both measured in this run."""
+    import torch.distributed as dist
+    from tilelang_b200 import ops
+
+    dev = torch.device("cuda", local_rank)
+    M = A.shape[0]
+    flops = 2.0 * M * N_FULL * K_FULL
+    steps = args.steps
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        barrier()
+        t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item()
+
+    C = torch.empty(M, n_local, dtype=torch.bfloat16, device=dev)
+    C_full = torch.empty(world, M, n_local, dtype=torch.bfloat16, device=dev)
+
+    def serial():
+        ops.gemm(A, pw, out=C)
+        dist.all_gather_into_tensor(C_full.view(world * M, n_local), C)
+
+    chunks = 4 if M >= 1024 else 1
+    mc = M // chunks
+    C_parts = [torch.empty(mc, n_local, dtype=torch.bfloat16, device=dev) for _ in range(chunks)]
+    G_parts = [torch.empty(world * mc, n_local, dtype=torch.bfloat16, device=dev) for _ in range(chunks)]
+
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+
+    def overlapped(spare):
+        # The GEMM is persistent, one CTA per SM: NCCL's kernel only runs beside it if some SMs
+        # are left free, so the chunk GEMMs are capped at sms - spare CTAs.
+        works = []
+        for i in range(chunks):
+            ops.gemm(A[i * mc:(i + 1) * mc], pw, out=C_parts[i], max_ctas=sms - spare)
+            works.append(dist.all_gather_into_tensor(G_parts[i], C_parts[i], async_op=True))
+        for w in works:
+            w.wait()
+
+    # the gather done by the GEMM's own epilogue: peer stores over NVLink, then a barrier
+    from tilelang_b200.parallel import PeerGatheredOutput
+    peer_out = PeerGatheredOutput(M, n_local, torch.bfloat16, dev)
+
+    def fused():
+        peer_out.gemm(A, pw)
+        peer_out.wait()
+
+    ms_fused = timed(fused)
+    del peer_out
+    ms_serial = timed(serial)
+    ms_overlap = {}
+    if chunks > 1:
+        for spare in (0, 8, 16, 32):
+            ms_overlap[f"spare_sms_{spare}"] = timed(lambda: overlapped(spare))
+    ops.check_status(dev)
+    del C_full, G_parts, C_parts
+    best = min([ms_serial, ms_fused] + list(ms_overlap.values()))
+    gathered = (world - 1) * M * n_local * 2
+    out = {"with_allgather": {
+        "value": flops / best / 1e9, "unit": "TFLOPS", "ms_per_step": best,
+        "ms_peer_stores_from_the_epilogue": ms_fused,
+        "ms_gemm_then_gather": ms_serial, "ms_chunked_overlap": ms_overlap, "token_chunks": chunks,
+        "ms_without_collective": ms_plain, "bytes_received_per_rank": gathered,
+        "gather_gbs_per_rank_if_exposed": gathered / max(ms_serial - ms_plain, 1e-6) / 1e6,
+        "nvlink_floor_ms": gathered / 770e6,
+        "note": "peer stores = the GEMM epilogue writes every tile to all ranks' gathered buffers (symmetric memory), "
+                "then one barrier; the others use all_gather_into_tensor over NCCL: after the GEMM, or per token chunk "
+                "under the next chunk's GEMM with `spare` SMs left to NCCL's kernel. nvlink_floor_ms = bytes sent per "
+                "rank over the 770 GB/s measured per direction"}}
+
+    ms_step, ms_gemm, ms_single = moe_measure(max(5, steps // 3), 3, rank, world, local_rank, compare_single=True)
+    fl = moe_flops()
+    out["moe_ep"] = {
+        "value": fl / ms_step / 1e9, "unit": "TFLOPS", "ms_per_step": ms_step, "ms_grouped_gemms_only": ms_gemm,
+        "ms_routing_and_all_to_all": ms_step - ms_gemm, "ms_same_layer_one_gpu": ms_single,
+        "efficiency_vs_one_gpu": ms_single / (world * ms_step) if ms_step > 0 else None,
+        "config": "64 experts over the ranks, 16384 tokens, top-6; two all_to_all_single per step"}
+    return out
 
 
 # ---- secondary workload: the grouped W4A16 MoE layer, expert-parallel ------------------
 MOE = dict(experts=64, top_k=6, tokens=16384, hidden=2048, ffn=1408, group=128)
 
 
-def run_moe(args, rank, world, local_rank):
+def moe_measure(steps, warmup, rank, world, local_rank, compare_single=False):
     """64 experts of W1 (2*1408, 2048) and W2 (2048, 1408), uint4 g=128, 16384 tokens, top-6.
     Experts are split over the ranks, every rank starts with tokens/world tokens; one step
     is route + dispatch all-to-all + two grouped GEMMs with silu_mul between + combine
-    all-to-all + weighted sum. Strong scaling: the token count is the whole job's."""
+    all-to-all + weighted sum. Strong scaling: the token count is the whole job's. Returns
+    (on every rank) step time, grouped-GEMM time and, with ``compare_single``, the time of the
+    whole layer on one GPU measured on this rank (max over ranks), all in ms."""
     import torch.distributed as dist
     from tilelang_b200 import moe, ops
 
-    torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     c = MOE
     E, H, F, g = c["experts"], c["hidden"], c["ffn"], c["group"]
-    mine = moe.expert_ranges(E, world)[rank]
 
-    def pack_experts(n, k, seed):
+    def pack_experts(n, k, seed, which):
         packs = []
-        for e in mine:
+        for e in which:
             gen = torch.Generator().manual_seed(seed * 1000 + e)
             q = torch.randint(0, 256, (n, k // 2), generator=gen, dtype=torch.uint8).to(dev)
             sc = (torch.rand(n, k // g, generator=gen) * 0.015 + 0.005).to(torch.bfloat16).to(dev)
@@ -566,56 +672,66 @@ def run_moe(args, rank, world, local_rank):
             packs.append(ops.pack_w4a16(q, sc, z, n, k, g, torch.bfloat16))
         return ops.stack_packed(packs)
 
-    mlp = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1), pack_experts(H, F, 2), token_tile=256)
-    t_local = c["tokens"] // world
-    gen = torch.Generator().manual_seed(77 + rank)
-    x = torch.randn(t_local, H, generator=gen).to(torch.bfloat16).to(dev)
-    logits = torch.randn(t_local, E, generator=gen).to(dev)
-
-    def step():
-        if world == 1:
-            return moe.moe_forward(x, logits, c["top_k"], E, mlp)
-        return moe.moe_forward_ep(x, logits, c["top_k"], E, mlp)
-
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(max(args.warmup, 3)):
-        step()
-    with ClockSampler(local_rank) as clocks:
+    def timed(fn):
+        for _ in range(max(warmup, 3)):
+            fn()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
         e0.record()
-        for _ in range(args.steps):
-            out = step()
+        for _ in range(steps):
+            fn()
         e1.record()
         barrier()
-        ms_total = e0.elapsed_time(e1)
-        time.sleep(0.25)
+        return e0.elapsed_time(e1) / steps
+
+    mine = moe.expert_ranges(E, world)[rank]
+    mlp = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1, mine), pack_experts(H, F, 2, mine), token_tile=256)
+    t_local = c["tokens"] // world
+    gen = torch.Generator().manual_seed(77 + rank)
+    x = torch.randn(t_local, H, generator=gen).to(torch.bfloat16).to(dev)
+    logits = torch.randn(t_local, E, generator=gen).to(dev)
+    if world == 1:
+        ms_step = timed(lambda: moe.moe_forward(x, logits, c["top_k"], E, mlp))
+    else:
+        ms_step = timed(lambda: moe.moe_forward_ep(x, logits, c["top_k"], E, mlp))
     ops.check_status(dev)
 
     # the two grouped GEMMs alone, on this rank's share of evenly routed rows
     rows = c["tokens"] * c["top_k"] // world
     counts = [rows // len(mine)] * len(mine)
     xs = torch.randn(sum(counts), H, device=dev).to(torch.bfloat16)
-    for _ in range(3):
-        mlp(xs, counts)
-    k0, k1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    torch.cuda.synchronize()
-    k0.record()
-    for _ in range(args.steps):
-        mlp(xs, counts)
-    k1.record()
-    torch.cuda.synchronize()
-    t = torch.tensor([ms_total, k0.elapsed_time(k1)], dtype=torch.float64, device=dev)
+    ms_gemm = timed(lambda: mlp(xs, counts))
+    ms_single = 0.0
+    if compare_single and world > 1:
+        del mlp
+        full = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1, range(E)), pack_experts(H, F, 2, range(E)), token_tile=256)
+        xf = torch.randn(c["tokens"], H, generator=gen).to(torch.bfloat16).to(dev)
+        lf = torch.randn(c["tokens"], E, generator=gen).to(dev)
+        ms_single = timed(lambda: moe.moe_forward(xf, lf, c["top_k"], E, full))
+    t = torch.tensor([ms_step, ms_gemm, ms_single], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t[0].item(), t[1].item(), t[2].item()
+
+
+def moe_flops():
+    c = MOE
+    return 2.0 * c["tokens"] * c["top_k"] * (2 * c["ffn"] * c["hidden"] + c["hidden"] * c["ffn"])
+
+
+def run_moe(args, rank, world, local_rank):
+    torch.cuda.set_device(local_rank)
+    with ClockSampler(local_rank) as clocks:
+        ms_step, ms_gemm, _ = moe_measure(args.steps, args.warmup, rank, world, local_rank)
+        time.sleep(0.25)
     if rank != 0:
         return
-    ms_step, ms_gemm = t[0].item() / args.steps, t[1].item() / args.steps
-    flops = 2.0 * c["tokens"] * c["top_k"] * (2 * F * H + H * F)
+    flops = moe_flops()
     peaks = measured_peaks()
     print(json.dumps({
         "metric": "moe_w4a16_layer_tflops", "value": flops / ms_step / 1e9, "unit": "TFLOPS", "n_gpus": world,

@@ -98,6 +98,15 @@ typedef struct b200dq_gemm_args {
   int64_t group_weight_stride;
   int32_t num_groups;
   int32_t total_tiles;
+  /* Copies of the output on other GPUs of the node (0 for none): num_peers device pointers
+   * into peer memory that this process can write (peer access enabled, an IPC or symmetric
+   * mapping), each the base of a tensor laid out exactly like c. Every output element is stored
+   * to c and at the same offset behind every c_peers[i], from the kernel's epilogue: a
+   * column-sharded GEMM fills every rank's gathered tensor without a separate all-gather.
+   * The stores are complete when the launch is; the ranks still need their own barrier
+   * before anyone reads a gathered tensor. The reference is single-GPU and has no counterpart. */
+  void* c_peers[7];
+  int32_t num_peers;
 } b200dq_gemm_args;
 
 /* Replaces call(...) of the kernels generated from

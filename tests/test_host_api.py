@@ -50,7 +50,7 @@ def test_gemm_args_struct_matches_header_field_order():
         if not decl:
             continue
         parts = [p.strip().lstrip("*") for p in decl.split(",")]
-        names.append(parts[0].split()[-1].lstrip("*"))
+        names.append(re.sub(r"\[\d+\]$", "", parts[0].split()[-1].lstrip("*")))     # array fields: name[7]
         names.extend(parts[1:])
     assert names == [f[0] for f in _lib.GemmArgs._fields_]
 

@@ -43,6 +43,9 @@ EXPORTED_SYMBOLS = (
 )
 
 
+ABI_VERSION = 4      # b200dq_version(): layout of struct b200dq_gemm_args
+
+
 class GemmArgs(ctypes.Structure):
     """``struct b200dq_gemm_args``."""
 
@@ -72,6 +75,8 @@ class GemmArgs(ctypes.Structure):
         ("group_weight_stride", ctypes.c_int64),
         ("num_groups", ctypes.c_int32),
         ("total_tiles", ctypes.c_int32),
+        ("c_peers", ctypes.c_void_p * 7),
+        ("num_peers", ctypes.c_int32),
     ]
 
 
@@ -138,6 +143,9 @@ def load(path: str | None = None):
                 )
             lib = ctypes.CDLL(p)
             _declare(lib)
+            if lib.b200dq_version() != ABI_VERSION:
+                raise B200dqError(f"{p} has ABI version {lib.b200dq_version()}, this package expects {ABI_VERSION}: "
+                                  "rebuild it with `python -m tilelang_b200.build`")
             _lib = lib
         return _lib
 

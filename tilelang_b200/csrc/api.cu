@@ -30,7 +30,7 @@ namespace {
 using namespace b200dq;
 
 constexpr int kMaxDevices = 32;
-constexpr int kAbiVersion = 3;
+constexpr int kAbiVersion = 4;
 constexpr int kMinSpan = 8;   // fewest k-blocks worth giving a CTA of its own
 
 thread_local char g_err[1024] = "";
@@ -346,6 +346,12 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   if ((a->flags & GF_HAS_BIAS) && a->bias == nullptr) return fail("%s: HAS_BIAS set but bias is null", who);
   if ((a->flags & GF_ROW_SCALE) && a->row_scale == nullptr) return fail("%s: ROW_SCALE set but row_scale is null", who);
   if ((reinterpret_cast<uintptr_t>(a->wp) & 15) != 0) return fail("%s: packed weights must be 16-byte aligned", who);
+  if (a->num_peers < 0 || a->num_peers > 7) return fail("%s: num_peers=%d outside [0, 7]", who, a->num_peers);
+  for (int d = 0; d < a->num_peers; ++d) {
+    if (a->c_peers[d] == nullptr) return fail("%s: c_peers[%d] is null", who, d);
+    if ((reinterpret_cast<uintptr_t>(a->c_peers[d]) & 15) != (reinterpret_cast<uintptr_t>(a->c) & 15))
+      return fail("%s: c_peers[%d] must have the alignment of c (same layout behind every base)", who, d);
+  }
 
   const bool grouped = a->num_groups > 0;
   if (grouped) {
@@ -373,6 +379,8 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
     p.flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
     p.out_type = a->out_type;
     p.status = status;
+    p.n_peers = a->num_peers;
+    for (int d = 0; d < a->num_peers; ++d) p.c_peer[d] = a->c_peers[d];
     CUDA_OK(launch_int8_skinny_gemm(wf, p, stream));
     return 0;
   }
@@ -425,6 +433,8 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   p.tn = s.tn;
   p.num_groups = grouped ? a->num_groups : 0;
   p.dyn_grid = dyn ? s.grid : 0;
+  p.n_peers = a->num_peers;
+  for (int d = 0; d < a->num_peers; ++d) p.c_peer[d] = a->c_peers[d];
   p.grp_row_prefix = grouped ? a->group_row_prefix : nullptr;
   p.grp_tile_prefix = grouped ? a->group_tile_prefix : nullptr;
   p.grp_w_stride = grouped ? a->group_weight_stride : 0;

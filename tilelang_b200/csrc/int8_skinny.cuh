@@ -182,10 +182,10 @@ __global__ void __launch_bounds__(NT <= 2 ? kInt8SkinnyMaxThreads : kInt8SkinnyM
     const uint32_t raw = static_cast<uint32_t>(red[m][o % kRows] - bias * asum[m]);
     const size_t idx = trans ? static_cast<size_t>(n) * p.ldc + m : static_cast<size_t>(m) * p.ldc + n;
     switch (p.out_type) {
-      case OUT_I32: reinterpret_cast<int*>(p.c)[idx] = finish_value<int, true>(p, raw, m, n); break;
-      case OUT_F16: reinterpret_cast<__half*>(p.c)[idx] = finish_value<__half, true>(p, raw, m, n); break;
-      case OUT_BF16: reinterpret_cast<__nv_bfloat16*>(p.c)[idx] = finish_value<__nv_bfloat16, true>(p, raw, m, n); break;
-      default: reinterpret_cast<float*>(p.c)[idx] = finish_value<float, true>(p, raw, m, n); break;
+      case OUT_I32: store_everywhere(p, idx, finish_value<int, true>(p, raw, m, n)); break;
+      case OUT_F16: store_everywhere(p, idx, finish_value<__half, true>(p, raw, m, n)); break;
+      case OUT_BF16: store_everywhere(p, idx, finish_value<__nv_bfloat16, true>(p, raw, m, n)); break;
+      default: store_everywhere(p, idx, finish_value<float, true>(p, raw, m, n)); break;
     }
   }
 }

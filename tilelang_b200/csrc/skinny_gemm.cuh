@@ -149,9 +149,9 @@ __device__ __forceinline__ void skinny_store(const GemmParams& p, const Segment&
   const bool trans = (p.flags & GF_TRANS_C) != 0;
   const size_t idx = trans ? static_cast<size_t>(n) * p.ldc + m : static_cast<size_t>(m) * p.ldc + n;
   switch (p.out_type) {
-    case OUT_F16: reinterpret_cast<__half*>(p.c)[idx] = finish_value<__half, false>(p, bits, m, n); break;
-    case OUT_BF16: reinterpret_cast<__nv_bfloat16*>(p.c)[idx] = finish_value<__nv_bfloat16, false>(p, bits, m, n); break;
-    default: reinterpret_cast<float*>(p.c)[idx] = finish_value<float, false>(p, bits, m, n); break;
+    case OUT_F16: store_everywhere(p, idx, finish_value<__half, false>(p, bits, m, n)); break;
+    case OUT_BF16: store_everywhere(p, idx, finish_value<__nv_bfloat16, false>(p, bits, m, n)); break;
+    default: store_everywhere(p, idx, finish_value<float, false>(p, bits, m, n)); break;
   }
 }
 

@@ -100,6 +100,11 @@ struct GemmParams {
   const int* grp_tile_prefix;    // num_groups + 1 entries, device memory
   long long grp_w_stride;
   int num_groups;
+  // Copies of the output on other GPUs (peer memory mapped into this process): every output
+  // element is also stored at the same offset behind each of these bases, so a column shard
+  // lands in every rank's gathered tensor straight from the epilogue (no separate all-gather).
+  void* c_peer[7];
+  int n_peers;
   int dyn_grid;                  // > 0: grouped mode planned on the device -- the tile total is read from
                                  // grp_tile_prefix[num_groups] and cut evenly over dyn_grid CTAs (span, units unused)
   int tn;                        // tokens per tile (the kernel's TN)
@@ -273,6 +278,13 @@ __device__ __forceinline__ OutT finish_value(const GemmParams& p, uint32_t raw, 
   }
 }
 
+// One output element to the local output and to every peer copy.
+template <typename OutT>
+__device__ __forceinline__ void store_everywhere(const GemmParams& p, size_t idx, OutT v) {
+  reinterpret_cast<OutT*>(p.c)[idx] = v;
+  for (int d = 0; d < p.n_peers; ++d) reinterpret_cast<OutT*>(p.c_peer[d])[idx] = v;
+}
+
 // Slow path: direct, predicated global stores (unaligned pitch or transposed output).
 template <typename OutT, bool kIntAcc, int NV>
 __device__ __forceinline__ void store_values_direct(const GemmParams& p, const uint32_t* acc, int m0, int m_end, int n) {
@@ -283,7 +295,9 @@ __device__ __forceinline__ void store_values_direct(const GemmParams& p, const u
     const int m = m0 + j;
     if (m < m_end) {
       const size_t idx = trans ? static_cast<size_t>(n) * p.ldc + m : static_cast<size_t>(m) * p.ldc + n;
-      c[idx] = finish_value<OutT, kIntAcc>(p, acc[j], m, n);
+      const OutT v = finish_value<OutT, kIntAcc>(p, acc[j], m, n);
+      c[idx] = v;
+      for (int d = 0; d < p.n_peers; ++d) reinterpret_cast<OutT*>(p.c_peer[d])[idx] = v;
     }
   }
 }
@@ -329,7 +343,9 @@ __device__ __forceinline__ void store_values_vec(const GemmParams& p, const uint
       const int m = m0 + pass * RPP + r;
       if (m < m_end && ncol < p.N) {
         const uint4 v = *reinterpret_cast<const uint4*>(sbuf + r * 32 * ES + vcol * 16);
-        *reinterpret_cast<uint4*>(c + static_cast<size_t>(m) * p.ldc + ncol) = v;
+        const size_t off = static_cast<size_t>(m) * p.ldc + ncol;
+        *reinterpret_cast<uint4*>(c + off) = v;
+        for (int d = 0; d < p.n_peers; ++d) *reinterpret_cast<uint4*>(reinterpret_cast<OutT*>(p.c_peer[d]) + off) = v;
       }
     }
   }
@@ -779,7 +795,9 @@ streamk_fixup_kernel(const GemmParams p) {
       if constexpr (kIntAcc) bits = static_cast<uint32_t>(iacc[jj]);
       else bits = __float_as_uint(facc[jj]);
       const size_t idx = trans ? static_cast<size_t>(n) * p.ldc + m : static_cast<size_t>(m) * p.ldc + n;
-      c[idx] = finish_value<OutT, kIntAcc>(p, bits, m, n);
+      const OutT v = finish_value<OutT, kIntAcc>(p, bits, m, n);
+      c[idx] = v;
+      for (int d = 0; d < p.n_peers; ++d) reinterpret_cast<OutT*>(p.c_peer[d])[idx] = v;
     }
   }
 }

@@ -33,9 +33,11 @@ def sort_by_expert(experts: torch.Tensor, num_experts: int):
     """Flatten (token, slot) pairs and order them by expert (stable). Returns the
     permutation, the token of every sorted row and the per-expert counts."""
     flat = experts.reshape(-1)
-    order = torch.argsort(flat, stable=True)
+    sorted_ids, order = torch.sort(flat, stable=True)
     token_of_row = order // experts.shape[1]
-    counts = torch.bincount(flat, minlength=num_experts)
+    # counts from the sorted ids (bincount would make the host wait for the largest id)
+    edges = torch.searchsorted(sorted_ids, torch.arange(num_experts + 1, device=flat.device, dtype=flat.dtype))
+    counts = edges[1:] - edges[:-1]
     return order, token_of_row, counts
 
 
@@ -125,8 +127,9 @@ def moe_forward_ep(x_local: torch.Tensor, logits_local: torch.Tensor, top_k: int
     regroup = torch.argsort(src_expert, stable=True)
     local_counts = mine_dev.sum(0)
     y_grouped = local_mlp(recv.index_select(0, regroup), local_counts if local_counts.is_cuda else local_counts.tolist())
-    y = torch.empty_like(y_grouped)
-    y.index_copy_(0, regroup, y_grouped)                                   # back to (source rank, expert) order
+    ungroup = torch.empty_like(regroup)
+    ungroup[regroup] = torch.arange(regroup.numel(), device=regroup.device)
+    y = y_grouped.index_select(0, ungroup)                                 # back to (source rank, expert) order
 
     back = y.new_empty((x_sorted.shape[0], y.shape[1]))
     dist.all_to_all_single(back, y.contiguous(), send_rows, recv_rows, group=group)

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 from dataclasses import dataclass
-from typing import Optional
+from typing import Optional, Sequence
 
 import torch
 
@@ -211,8 +211,11 @@ def workspace_for(device: torch.device, nbytes: int) -> torch.Tensor:
 def gemm(A: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None,
          out_dtype: Optional[torch.dtype] = None, bias: Optional[torch.Tensor] = None,
          row_scale: Optional[torch.Tensor] = None, tensor_scale: float = 1.0, trans_c: bool = False,
-         token_tile: int = 0, max_ctas: int = 0, workspace: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """C = A @ dequant(W)^T on the current stream; returns (and, if given, fills) ``out``."""
+         token_tile: int = 0, max_ctas: int = 0, workspace: Optional[torch.Tensor] = None,
+         peer_outs: Sequence[int] = ()) -> torch.Tensor:
+    """C = A @ dequant(W)^T on the current stream; returns (and, if given, fills) ``out``.
+    ``peer_outs``: up to seven device addresses in other GPUs' memory, each the base of a tensor
+    laid out like ``out``; the kernel's epilogue stores every element there as well."""
     lib = _lib.load()
     _check_cuda_contig("A", A)
     dev = A.device
@@ -262,6 +265,12 @@ def gemm(A: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None,
         M=M, N=w.N, K=w.K, group_size=w.group_size, weight_format=w.weight_format, act_type=w.act_type,
         out_type=_OUT_OF[out.dtype], flags=flags, tensor_scale=float(tensor_scale), code_bias=w.code_bias,
         fp4_exp_bias=w.fp4_exp_bias, token_tile=token_tile, max_ctas=max_ctas)
+    if peer_outs:
+        if len(peer_outs) > 7:
+            raise ValueError("at most seven peer outputs")
+        for i, ptr in enumerate(peer_outs):
+            args.c_peers[i] = int(ptr)
+        args.num_peers = len(peer_outs)
     with torch.cuda.device(dev):
         _lib.check(lib.b200dq_gemm(ctypes.byref(args), _stream_ptr(dev)), "b200dq_gemm")
     return out

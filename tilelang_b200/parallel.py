@@ -97,3 +97,47 @@ class ColumnParallelDequantLinear:
             for s in self.shards:
                 out[:, s.start:s.stop] = buf[s.rank, :, :s.size]
         return out
+
+
+class PeerGatheredOutput:
+    """The gathered output of a column-parallel GEMM, filled by the GEMM kernels themselves.
+
+    Every rank allocates one ``(world, M, n_local)`` buffer in symmetric memory (equal shards);
+    rank r's kernel stores its ``(M, n_local)`` block to slot r of its own buffer and, through
+    peer pointers over NVLink, to slot r of every other rank's buffer, tile by tile from the
+    epilogue, so the transfer runs under the rest of the GEMM and there is no separate
+    all-gather. ``gemm(A, packed)`` launches the local GEMM; ``wait()`` is the exchange step
+    that is left: a barrier after which every slot of ``buffer`` is complete on every rank.
+    ``buffer[r]`` is ``C[:, shard r]``; a consumer that wants ``(M, N)`` permutes the view.
+
+    The reference is single-GPU and has no counterpart; this replaces the one
+    ``all_gather_into_tensor`` of :class:`ColumnParallelDequantLinear.forward`.
+    """
+
+    def __init__(self, M: int, n_local: int, dtype: torch.dtype, device: torch.device,
+                 group: Optional[dist.ProcessGroup] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        if self.world > 8:
+            raise ValueError("peer stores reach the GPUs of one node (at most 8)")
+        self.M, self.n_local = M, n_local
+        self.buffer = symm_mem.empty((self.world, M, n_local), dtype=dtype, device=device)
+        self._handle = symm_mem.rendezvous(self.buffer, self.group.group_name)
+        block_bytes = M * n_local * self.buffer.element_size()
+        ptrs = list(self._handle.buffer_ptrs)
+        # my block's address inside every other rank's buffer
+        self.peer_ptrs = [ptrs[r] + self.rank * block_bytes for r in range(self.world) if r != self.rank]
+        self._token = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def gemm(self, A: torch.Tensor, packed, **kwargs) -> torch.Tensor:
+        from . import ops
+        return ops.gemm(A, packed, out=self.buffer[self.rank], peer_outs=self.peer_ptrs, **kwargs)
+
+    def wait(self) -> torch.Tensor:
+        """Every rank's kernel has finished (its peer stores with it): one tiny all-reduce on
+        the current stream orders the ranks. Returns the gathered buffer."""
+        dist.all_reduce(self._token, group=self.group)
+        return self.buffer
+
