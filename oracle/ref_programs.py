@@ -348,6 +348,32 @@ def mxfp4_act_quant(x: torch.Tensor, block_size: int = 32, ties: str = "down"):
     return torch.where(y < 0, idx + 8, idx).to(torch.uint8), scale
 
 
+def ref_low_bits_a16(A: torch.Tensor, qB: torch.Tensor, bits: int, scales, zeros, group_size: int, signed: bool,
+                     out_dtype=torch.float16) -> torch.Tensor:
+    """1- or 2-bit integer weights on 16-bit activations: codes little-endian in each byte
+    (general_compress, quantize/utils.py:50-67); weight = q (unsigned), q - 2 (signed 2-bit) or
+    2 q - 1 (signed 1-bit) as the reference's decoders produce it (quantize/lop3.py:424-463,
+    679-745: sub 1024 [+ add, add -1]), then ``* scale`` (:465-530, 748-810) or
+    ``(q - zeros) * scale`` (:532-590 "original"); the weight is rounded to the activation dtype
+    before the fp32 matmul, as in the 4-bit ref_programs."""
+    N = qB.shape[0]
+    per = 8 // bits
+    q = qB.to(torch.int32)
+    codes = torch.stack([(q >> (bits * i)) & ((1 << bits) - 1) for i in range(per)], dim=-1).reshape(N, -1).float()
+    K = codes.shape[1]
+    if signed:
+        codes = codes - 2.0 if bits == 2 else 2.0 * codes - 1.0
+    if scales is not None:
+        s = scales.float().repeat_interleave(group_size, dim=1)
+        if zeros is not None:
+            codes = (codes - zeros.float().repeat_interleave(group_size, dim=1)) * s
+        else:
+            codes = codes * s
+    W = codes.to(A.dtype).float()
+    assert K == A.shape[1]
+    return torch.matmul(A.float(), W.T).to(out_dtype)
+
+
 def ref_mxfp4_native(A: torch.Tensor, qB: torch.Tensor, scale_bytes: torch.Tensor, out_dtype=torch.bfloat16):
     """Both operands MXFP4: the activation is re-quantised per row and 32-block the way the
     reference's kernel does (:func:`mxfp4_act_quant`, ties to even), then

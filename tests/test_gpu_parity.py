@@ -303,6 +303,37 @@ def test_bitlinear_module_forward_matches_the_reference_layer():
 
 # ------------------------------- small-M entry point ------------------------------------
 
+@pytest.mark.parametrize("bits,signed", [(2, False), (2, True), (1, False), (1, True)])
+@pytest.mark.parametrize("M,N,K,dtype", [(3, 256, 256, torch.float16), (200, 384, 1024, torch.bfloat16),
+                                         (64, 130, 640, torch.float16)])
+def test_int2_and_int1_weights_on_16_bit_activations(bits, signed, M, N, K, dtype):
+    """The int2 -> f16 and int1 -> f16 rules of the reference's LOP3 decoders: raw codes (exact:
+    integer weights, checked with one-hot rows too), with group scales, and with scales and
+    real-valued zero-points."""
+    A = torch.randn(M, K, generator=gen(1)).to(dtype)
+    qB = torch.randint(0, 256, (N, K * bits // 8), generator=gen(2), dtype=torch.uint8)
+    fmt = "int" if signed else "uint"
+    name = {torch.float16: "float16", torch.bfloat16: "bfloat16"}[dtype]
+    # raw codes: the dequantised weights are small integers, read back exactly by one-hot rows
+    kernel = tb.matmul(M, N, K, name, name, "float32", num_bits=bits, source_format=fmt)
+    eye = torch.zeros(M, K, dtype=dtype)
+    eye[torch.arange(M), torch.arange(M) * 7 % K] = 1.0
+    W_rows = kernel(eye.to(DEV), qB.to(DEV)).cpu()
+    assert torch.equal(W_rows, R.ref_low_bits_a16(eye, qB, bits, None, None, K, signed, dtype))
+    check_float(kernel(A.to(DEV), qB.to(DEV)), R.ref_low_bits_a16(A, qB, bits, None, None, K, signed, dtype))
+    # group scales
+    group = 128
+    s = (torch.rand(N, K // group, generator=gen(3)) * 0.05 + 0.01).to(dtype)
+    kernel = tb.matmul(M, N, K, name, name, "float32", num_bits=bits, group_size=group, source_format=fmt)
+    check_float(kernel(A.to(DEV), qB.to(DEV), s.to(DEV)), R.ref_low_bits_a16(A, qB, bits, s, None, group, signed, dtype))
+    if not signed:
+        z = (torch.rand(N, K // group, generator=gen(4)) * (2 ** bits - 1)).to(dtype)
+        kernel = tb.matmul(M, N, K, name, name, "float32", num_bits=bits, group_size=group, with_zeros=True)
+        check_float(kernel(A.to(DEV), qB.to(DEV), s.to(DEV), z.to(DEV)),
+                    R.ref_low_bits_a16(A, qB, bits, s, z, group, False, dtype), strict=2e-2)
+    tb.check_status()
+
+
 def test_dequantize_gemv_reference_flow():
     # example_dequant_gemv_fp16xint4.py:158-217: weights pre-permuted by interleave_weight
     M, N, K = 1, 1024, 1024

@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200dq.so")
 
 # enum values of include/b200dq.h
-WF_U4_SZ, WF_U4_RAW, WF_S4_RAW, WF_FP4_E8M0, WF_I2_I8, WF_I4_I8 = range(6)
+WF_U4_SZ, WF_U4_RAW, WF_S4_RAW, WF_FP4_E8M0, WF_I2_I8, WF_I4_I8, WF_U2_SZ = range(7)
 ACT_F16, ACT_BF16, ACT_I8 = range(3)
 OUT_F16, OUT_BF16, OUT_F32, OUT_I32 = range(4)
 GF_TRANS_C, GF_HAS_BIAS, GF_ROW_SCALE, GF_FP4_SIMPLE = 1, 2, 4, 16

@@ -116,7 +116,7 @@ int stages_for(int K, int act_type) {
 
 // scale words per row and stage
 int nsz_for(int weight_format, int group_size) {
-  if (weight_format == WF_U4_SZ) return group_size == 64 ? 2 : 1;
+  if (weight_format == WF_U4_SZ || weight_format == WF_U2_SZ) return group_size == 64 ? 2 : 1;
   if (weight_format == WF_FP4_E8M0) return 1;
   return 0;
 }
@@ -336,12 +336,12 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   const int wf = a->weight_format, act = a->act_type;
   const bool int_act = (act == ACT_I8);
   const bool wf_int = (wf == WF_I2_I8 || wf == WF_I4_I8);
-  if (wf < WF_U4_SZ || wf > WF_I4_I8) return fail("%s: unknown weight format %d", who, wf);
+  if (wf < WF_U4_SZ || wf > kLastWeightFormat) return fail("%s: unknown weight format %d", who, wf);
   if (act < ACT_F16 || act > ACT_I8) return fail("%s: unknown activation type %d", who, act);
   if (a->out_type < OUT_F16 || a->out_type > OUT_I32) return fail("%s: unknown output type %d", who, a->out_type);
   if (wf_int != int_act) return fail("%s: weight format %d and activation type %d do not go together", who, wf, act);
   if (wf == WF_FP4_E8M0 && act == ACT_I8) return fail("%s: fp4 weights need f16 or bf16 activations", who);
-  if (wf == WF_U4_SZ && (a->group_size <= 0 || a->K % a->group_size != 0))
+  if ((wf == WF_U4_SZ || wf == WF_U2_SZ) && (a->group_size <= 0 || a->K % a->group_size != 0))
     return fail("%s: group_size=%d must divide K=%d", who, a->group_size, a->K);
   if ((a->flags & GF_HAS_BIAS) && a->bias == nullptr) return fail("%s: HAS_BIAS set but bias is null", who);
   if ((a->flags & GF_ROW_SCALE) && a->row_scale == nullptr) return fail("%s: ROW_SCALE set but row_scale is null", who);
@@ -426,7 +426,7 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   p.n_tiles = s.n_tiles; p.m_tiles = s.m_tiles; p.st_total = s.st_total;
   p.span = s.span; p.units = s.units;
   p.stage_bytes = stage_bytes_for(wf, a->group_size);
-  p.sz_per_kb = (wf == WF_U4_SZ && a->group_size == 64) ? 1 : 0;
+  p.sz_per_kb = ((wf == WF_U4_SZ || wf == WF_U2_SZ) && a->group_size == 64) ? 1 : 0;
   p.ldc = (a->flags & GF_TRANS_C) ? a->M : a->N;
   p.flags = flags;
   p.out_type = a->out_type;
@@ -498,7 +498,7 @@ size_t b200dq_gemm_workspace_bytes_for(const b200dq_gemm_args* a) {
 }
 
 size_t b200dq_packed_weight_bytes(int32_t N, int32_t K, int32_t group_size, int32_t weight_format) {
-  if (N <= 0 || K <= 0 || weight_format < WF_U4_SZ || weight_format > WF_I4_I8) return 0;
+  if (N <= 0 || K <= 0 || weight_format < WF_U4_SZ || weight_format > kLastWeightFormat) return 0;
   const int n_tiles = (N + kTileRows - 1) / kTileRows;
   const bool int8_target = (weight_format == WF_I2_I8 || weight_format == WF_I4_I8);
   const int st_total = stages_for(K, int8_target ? ACT_I8 : ACT_BF16);
@@ -508,9 +508,9 @@ size_t b200dq_packed_weight_bytes(int32_t N, int32_t K, int32_t group_size, int3
 int b200dq_pack_weights(const void* q_natural, const void* scales, const void* zeros, void* wp, int32_t N, int32_t K,
                         int32_t group_size, int32_t weight_format, int32_t act_type, void* cuda_stream) {
   if (q_natural == nullptr || wp == nullptr) return fail("pack_weights: null pointer");
-  if (weight_format < WF_U4_SZ || weight_format > WF_I4_I8) return fail("pack_weights: unknown weight format %d", weight_format);
+  if (weight_format < WF_U4_SZ || weight_format > kLastWeightFormat) return fail("pack_weights: unknown weight format %d", weight_format);
   const bool int8_target = (weight_format == WF_I2_I8 || weight_format == WF_I4_I8);
-  const int bits = weight_format == WF_I2_I8 ? 2 : 4;
+  const int bits = (weight_format == WF_I2_I8 || weight_format == WF_U2_SZ) ? 2 : 4;
   if (N <= 0 || K <= 0) return fail("pack_weights: N and K must be positive");
   if (K % (128 / bits) != 0) return fail("pack_weights: K=%d must be a multiple of %d for %d-bit codes", K, 128 / bits, bits);
   if ((reinterpret_cast<uintptr_t>(q_natural) & 3) != 0 || (reinterpret_cast<uintptr_t>(wp) & 15) != 0)
@@ -525,7 +525,7 @@ int b200dq_pack_weights(const void* q_natural, const void* scales, const void* z
   p.st_total = stages_for(K, int8_target ? ACT_I8 : ACT_BF16);
   p.code_words_per_kb = codes_per_kblock_bytes(weight_format) / 4;
   p.elems_per_kblock = int8_target ? 128 : 64;
-  if (weight_format == WF_U4_SZ) {
+  if (weight_format == WF_U4_SZ || weight_format == WF_U2_SZ) {
     if (scales == nullptr) return fail("pack_weights: this weight format needs scales");
     if (act_type != ACT_F16 && act_type != ACT_BF16) return fail("pack_weights: scales must be f16 or bf16");
     if (group_size <= 0 || K % group_size != 0) return fail("pack_weights: group_size=%d must divide K=%d", group_size, K);

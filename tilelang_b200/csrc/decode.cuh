@@ -15,6 +15,7 @@
 //
 // Offline layouts expected in each 32-bit word (produced by pack_weight):
 //   u4 -> 16 bit : element e at bit (e % 2) * 16 + (e / 2) * 4        (8 per word)
+//   u2 -> 16 bit : element e at bit (e % 2) * 16 + (e / 2) * 2        (16 per word)
 //   u2/u4 -> 8 bit: element e at bit (e % 4) * 8 + (e / 4) * nbits    (16 or 8 per word)
 //   e2m1 -> bf16 : see decode_fp4_chunk
 #pragma once
@@ -84,6 +85,45 @@ __device__ __forceinline__ void decode_u4_chunk(const uint4& packed, uint32_t sz
   decode_u4_word<kBf16>(packed.y, s2, nz2, &out[4]);
   decode_u4_word<kBf16>(packed.z, s2, nz2, &out[8]);
   decode_u4_word<kBf16>(packed.w, s2, nz2, &out[12]);
+}
+
+// 2-bit codes with per-group scale and zero-point, weight = (q - z) * s: the same subnormal
+// trick as decode_u4_word. A word holds 16 codes, element e at bit (e % 2) * 16 + (e / 2) * 2;
+// the pair (2i, 2i + 1) is masked in place at bits [2 (i % 4), +2) of the word or of the word
+// shifted down by 8 (a 16-bit pattern is linear in its low 8 bits for bf16 -- 7 mantissa bits and
+// the lowest exponent bit -- so the field may sit at bits 0, 2, 4 or 6), and the fma's
+// power-of-two factor takes out the field's position: 2^(127 - 2 (i % 4)) in bf16,
+// 2^(15 - 2 (i % 4)) in fp16. Restates what the reference's decode_i2u_to_f16 / decode_i2s_to_f16
+// and their scale / zeros variants compute (quantize/lop3.py:424-677); z = 2 is its signed form.
+template <bool kBf16>
+__device__ __forceinline__ void decode_u2_word(uint32_t w, uint32_t s2, uint32_t nz2, uint32_t* out) {
+  const uint32_t wh = w >> 8;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const uint32_t src = (i & 4) ? wh : w;
+    const int pos = i & 3;
+    const uint32_t x = src & (0x00030003u << (2 * pos));
+    if constexpr (kBf16) {
+      const uint32_t pw2 = 0x7f007f00u - 0x01000100u * pos;       // 2^(127 - 2 pos) in both halves
+      const __nv_bfloat162 t = __hfma2(u32_as_bf162(x), u32_as_bf162(pw2), u32_as_bf162(nz2));
+      out[i] = bf162_as_u32(__hmul2(t, u32_as_bf162(s2)));
+    } else {
+      const uint32_t pw2 = 0x78007800u - 0x08000800u * pos;       // 2^(15 - 2 pos)
+      const __half2 t = __hfma2(u32_as_h2(x), u32_as_h2(pw2), u32_as_h2(nz2));
+      out[i] = h2_as_u32(__hmul2(t, u32_as_h2(s2)));
+    }
+  }
+}
+
+// One 16-byte chunk = 64 codes of one row = a whole k-block: 32 registers.
+template <bool kBf16>
+__device__ __forceinline__ void decode_u2_chunk(const uint4& packed, uint32_t sz, uint32_t (&out)[32]) {
+  const uint32_t s2 = __byte_perm(sz, 0, 0x1010);
+  const uint32_t nz2 = __byte_perm(sz, 0, 0x3232);
+  decode_u2_word<kBf16>(packed.x, s2, nz2, &out[0]);
+  decode_u2_word<kBf16>(packed.y, s2, nz2, &out[8]);
+  decode_u2_word<kBf16>(packed.z, s2, nz2, &out[16]);
+  decode_u2_word<kBf16>(packed.w, s2, nz2, &out[24]);
 }
 
 // No scale at all: weight = q (unsigned) or q - 8 (signed storage), as in the

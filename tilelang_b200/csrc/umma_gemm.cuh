@@ -60,7 +60,9 @@ enum WeightFormat : int {
   WF_FP4_E8M0 = 3,    // e2m1 + e8m0 block scale per 32 (bf16 activations; fp16 without block scale)
   WF_I2_I8 = 4,       // 2-bit codes -> int8, minus `code_bias` (int8 activations)
   WF_I4_I8 = 5,       // 4-bit codes -> int8, minus `code_bias` (int8 activations)
+  WF_U2_SZ = 6,       // 2-bit codes + per-group scale and zero-point -> f16/bf16: (q - z) * s
 };
+constexpr int kLastWeightFormat = WF_U2_SZ;
 
 enum ActType : int { ACT_F16 = 0, ACT_BF16 = 1, ACT_I8 = 2 };
 enum OutType : int { OUT_F16 = 0, OUT_BF16 = 1, OUT_F32 = 2, OUT_I32 = 3 };
@@ -117,9 +119,13 @@ constexpr int kStageBufBytes = 2048;                    // one epilogue staging 
 constexpr int kStagingBytesPerWarp = kStageBufBytes;      // one 32 x 32 x 2-byte transpose buffer per epilogue warp
 constexpr int kMaxSlots = 16;
 
-__host__ __device__ constexpr int codes_per_kblock_bytes(int wf) { return wf == WF_I4_I8 ? 8192 : 4096; }
+__host__ __device__ constexpr int codes_per_kblock_bytes(int wf) {
+  return wf == WF_I4_I8 ? 8192 : (wf == WF_U2_SZ ? 2048 : 4096);
+}
 // scale words carried by one stage in shared memory (upper bound, bytes)
-__host__ __device__ constexpr int sz_smem_bytes(int wf) { return wf == WF_U4_SZ ? 1024 : (wf == WF_FP4_E8M0 ? 512 : 0); }
+__host__ __device__ constexpr int sz_smem_bytes(int wf) {
+  return (wf == WF_U4_SZ || wf == WF_U2_SZ) ? 1024 : (wf == WF_FP4_E8M0 ? 512 : 0);
+}
 
 // TMEM plan: accumulators of the NI issuers in columns [0, kAccCols), then a ring
 // of kSlots dequantised k-blocks (32 columns each).
@@ -559,7 +565,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
         constexpr int RPC = 32 / CH;              // TMEM columns produced by one chunk
         if (mine) {
           uint32_t sz0 = 0, sz1 = 0;
-          if constexpr (WF == WF_U4_SZ) {
+          if constexpr (WF == WF_U4_SZ || WF == WF_U2_SZ) {
             const uint32_t* szp = reinterpret_cast<const uint32_t*>(stage + Ring::kCodeBytes);
             sz0 = szp[row_in_tile];
             sz1 = p.sz_per_kb ? szp[128 + row_in_tile] : sz0;
@@ -581,6 +587,8 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
             uint32_t regs[RPC];
             if constexpr (WF == WF_I4_I8) {
               decode_i4_chunk(cq, p.code_bias, regs);
+            } else if constexpr (WF == WF_U2_SZ) {
+              decode_u2_chunk<kBf16>(cq, h == 0 ? sz0 : sz1, regs);
             } else if constexpr (WF == WF_U4_SZ) {
               decode_u4_chunk<kBf16>(cq, h == 0 ? sz0 : sz1, regs);
             } else if constexpr (WF == WF_U4_RAW) {
@@ -601,7 +609,8 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
               tc_fence_after_sync();
             }
             const uint32_t dst = tmem_base + lane_addr + kAccCols + sa * 32 + q * RPC;
-            if constexpr (RPC == 16) tmem_st_32x32b_x16(dst, regs);
+            if constexpr (RPC == 32) tmem_st_32x32b_x32(dst, regs);
+            else if constexpr (RPC == 16) tmem_st_32x32b_x16(dst, regs);
             else tmem_st_32x32b_x8(dst, regs);
             if (it == 2 * CH - 1) {
               // both k-blocks of the stage are stored: one hand-off per stage, on the

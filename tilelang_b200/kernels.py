@@ -145,8 +145,11 @@ def matmul(M: int, N: int, K: int, in_dtype, out_dtype, accum_dtype, num_bits: i
     example_dequant_gemm_fine_grained.py:427-428: C = A_int8 @ unpack_u4(qB)^T, exact.
     """
     in_t, out_t, acc_t = as_torch_dtype(in_dtype), as_torch_dtype(out_dtype), as_torch_dtype(accum_dtype)
+    if num_bits in (1, 2) and as_torch_dtype(in_dtype) in (torch.float16, torch.bfloat16):
+        return _matmul_low_bits(M, N, K, in_t, out_t, acc_t, num_bits, group_size, with_scaling, with_zeros, zeros_mode,
+                                str(source_format).lower(), with_bias, trans_c)
     if num_bits != 4:
-        raise ValueError("matmul: only num_bits=4 weights are supported on the 16-bit activation path")
+        raise ValueError("matmul: num_bits must be 4 (or 1 / 2 with float16 / bfloat16 activations)")
     if in_t == torch.int8:
         return _matmul_int8_unsigned(M, N, K, out_t, acc_t, group_size or with_scaling or with_zeros or with_bias)
     if in_t not in (torch.float16, torch.bfloat16):
@@ -241,6 +244,49 @@ def matmul_mxfp4_native(M: int, N: int, K: int, in_dtype="bfloat16", out_dtype="
                            f"b200dq kind::mxf4.block_scale: M={M} N={N} K={K} in={in_t} out={out_t}")
     kernel.quantized = quantized
     return kernel
+
+
+def _matmul_low_bits(M, N, K, in_t, out_t, acc_t, num_bits, group_size, with_scaling, with_zeros, zeros_mode,
+                     source_format, with_bias, trans_c) -> DequantKernel:
+    """1- and 2-bit integer weights on 16-bit activations: the int2 -> f16 and int1 -> f16 decode
+    rules of quantize/lop3.py:424-891. ``source_format`` "uint" reads the codes unsigned, "int"
+    the reference's signed forms (q - 2; 2 q - 1). Inputs ``(A, qB[, Scale[, Zeros]][, Bias])``
+    with qB (N, K * num_bits / 8)."""
+    if acc_t != torch.float32:
+        raise ValueError("matmul: accumulation is float32")
+    if source_format not in ("uint", "int"):
+        raise ValueError("matmul: 1- and 2-bit weights are 'uint' or 'int'")
+    if with_scaling is None:
+        with_scaling = bool(group_size)
+    if with_zeros and not with_scaling:
+        raise ValueError("matmul: zero-points need scales")
+    if with_zeros and source_format == "int":
+        raise ValueError("matmul: explicit zero-points go with unsigned codes")
+    g = K if group_size in (None, -1, 0) else group_size
+    params = [Param("A", (M, K), in_t), Param("B", (N, K * num_bits // 8), torch.uint8)]
+    if with_scaling:
+        params.append(Param("Scale", (N, K // g), in_t))
+        if with_zeros:
+            params.append(Param("Zeros", (N, K // g), torch.uint8 if zeros_mode == "quantized" else in_t))
+    if with_bias:
+        params.append(Param("Bias", (M, N), out_t))
+    params.append(Param("C", (N, M) if trans_c else (M, N), out_t))
+
+    def pack_fn(qB, scale=None, zeros=None):
+        return ops.pack_w2a16(qB.view(torch.uint8), scale, zeros, N, K, g, in_t, bits=num_bits,
+                              signed=(source_format == "int"), zeros_mode=zeros_mode)
+
+    def impl(kernel: DequantKernel, A, qB, *rest):
+        rest = list(rest)
+        scale = rest.pop(0) if with_scaling else None
+        zeros = rest.pop(0) if with_zeros else None
+        bias = rest.pop(0) if with_bias else None
+        _check(A, params[0])
+        _check(qB, params[1], any_int8=True)
+        return ops.gemm(A, kernel._packed(qB, scale, zeros), out_dtype=out_t, bias=bias, trans_c=trans_c)
+
+    return DequantKernel("matmul", params, [-1], impl, pack_fn,
+                         f"b200dq umma_dequant_gemm: M={M} N={N} K={K} in={in_t} out={out_t} int{num_bits} group={group_size}")
 
 
 def _matmul_int8_unsigned(M: int, N: int, K: int, out_t: torch.dtype, acc_t: torch.dtype, extras) -> DequantKernel:

@@ -16,7 +16,7 @@ import torch
 
 from . import _lib
 from ._lib import (ACT_BF16, ACT_F16, ACT_I8, GF_FP4_SIMPLE, GF_HAS_BIAS, GF_ROW_SCALE, GF_TRANS_C, OUT_BF16, OUT_F16,
-                   OUT_F32, OUT_I32, WF_FP4_E8M0, WF_I2_I8, WF_I4_I8, WF_S4_RAW, WF_U4_RAW, WF_U4_SZ)
+                   OUT_F32, OUT_I32, WF_FP4_E8M0, WF_I2_I8, WF_I4_I8, WF_S4_RAW, WF_U2_SZ, WF_U4_RAW, WF_U4_SZ)
 
 _ACT_OF = {torch.float16: ACT_F16, torch.bfloat16: ACT_BF16, torch.int8: ACT_I8}
 _OUT_OF = {torch.float16: OUT_F16, torch.bfloat16: OUT_BF16, torch.float32: OUT_F32, torch.int32: OUT_I32}
@@ -153,6 +153,48 @@ def pack_w4a16(qweight: torch.Tensor, scales: Optional[torch.Tensor], zeros: Opt
             raise ValueError(f"{name} must be {dtype} of shape {(N, groups)}, got {t.dtype} {tuple(t.shape)}")
     wp = _pack(qweight, scales, zeros, N, K, 4, group_size, WF_U4_SZ, act)
     return PackedWeight(wp, N, K, WF_U4_SZ, act, group_size=group_size)
+
+
+def pack_w2a16(qweight: torch.Tensor, scales: Optional[torch.Tensor], zeros: Optional[torch.Tensor], N: int, K: int,
+               group_size: int, dtype: torch.dtype, bits: int = 2, signed: bool = False,
+               zeros_mode: str = "original") -> PackedWeight:
+    """2-bit codes (N, K/4) or 1-bit codes (N, K/8), little-endian in each byte, for 16-bit
+    activations: weight = ``(q - z) * s`` with (N, K/group) scales and zero-points in ``dtype``.
+    Without ``zeros`` the zero-point is 0, or with ``signed`` the reference's signed forms:
+    ``q - 2`` for 2-bit codes and ``2 q - 1`` for 1-bit codes (quantize/lop3.py:424-463, 679-745);
+    without ``scales`` the scale is 1. The image holds 2-bit fields in either case: 1-bit codes
+    are widened on the device once, at pack time (a signed bit b becomes the field 2 b with
+    zero-point 1), so a 1-bit weight streams 2 bits per element."""
+    if dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("16-bit activations only")
+    if bits not in (1, 2):
+        raise ValueError("pack_w2a16 takes 1- or 2-bit codes")
+    if zeros is not None and signed:
+        raise ValueError("explicit zero-points go with unsigned codes")
+    from . import quantize
+    _check_cuda_contig("packed weight codes", qweight)
+    dev = qweight.device
+    if bits == 1:
+        codes = quantize.decompress_codes(qweight.view(torch.uint8), 1)
+        if signed:
+            codes = codes * 2
+        qweight = quantize.compress_codes(codes, 2).contiguous()
+    if group_size in (-1, 0, None) or scales is None and zeros is None:
+        group_size = K
+    groups = K // group_size
+    if scales is None:
+        scales = torch.ones((N, groups), dtype=dtype, device=dev)
+    if zeros is None:
+        zeros = torch.full((N, groups), (1.0 if bits == 1 else 2.0) if signed else 0.0, dtype=dtype, device=dev)
+    elif zeros_mode != "original":
+        zeros = zeros_for_original_mode(scales, zeros, zeros_mode).contiguous()
+    for name, t in (("scales", scales), ("zeros", zeros)):
+        _check_cuda_contig(name, t, dev)
+        if t.dtype != dtype or tuple(t.shape) != (N, groups):
+            raise ValueError(f"{name} must be {dtype} of shape {(N, groups)}, got {t.dtype} {tuple(t.shape)}")
+    act = _ACT_OF[dtype]
+    wp = _pack(qweight.view(torch.uint8), scales, zeros, N, K, 2, group_size, WF_U2_SZ, act)
+    return PackedWeight(wp, N, K, WF_U2_SZ, act, group_size=group_size)
 
 
 def pack_mxfp4(qweight: torch.Tensor, scale_bytes: Optional[torch.Tensor], N: int, K: int, exp_bias: int = 127,
