@@ -303,6 +303,22 @@ def test_bitlinear_module_forward_matches_the_reference_layer():
 
 # ------------------------------- small-M entry point ------------------------------------
 
+@pytest.mark.parametrize("bits,signed", [(4, True), (2, False), (2, True), (1, False), (1, True)])
+@pytest.mark.parametrize("M", [2, 100])
+def test_int4_int2_int1_codes_on_int8_activations(bits, signed, M):
+    """int2 -> int8 and int1 -> int8 (quantize/lop3.py:893-1047) and signed 4-bit codes through
+    matmul(..., "int8", "int32", "int32", num_bits=...): exact."""
+    N, K = 384, 512
+    A = torch.randint(-128, 128, (M, K), generator=gen(1), dtype=torch.int8)
+    qB = torch.randint(0, 256, (N, K * bits // 8), generator=gen(2), dtype=torch.uint8)
+    codes = quantize.decompress_codes(qB, bits).to(torch.int64)
+    W = codes if not signed else (codes - 8 if bits == 4 else codes - 2 if bits == 2 else 2 * codes - 1)
+    kernel = tb.matmul(M, N, K, "int8", "int32", "int32", num_bits=bits, source_format="int" if signed else "uint")
+    C = kernel(A.to(DEV), qB.to(DEV))
+    tb.check_status()
+    assert torch.equal(C.cpu(), torch.matmul(A.to(torch.int64), W.T).to(torch.int32))
+
+
 @pytest.mark.parametrize("bits,signed", [(2, False), (2, True), (1, False), (1, True)])
 @pytest.mark.parametrize("M,N,K,dtype", [(3, 256, 256, torch.float16), (200, 384, 1024, torch.bfloat16),
                                          (64, 130, 640, torch.float16)])

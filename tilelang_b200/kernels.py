@@ -145,13 +145,14 @@ def matmul(M: int, N: int, K: int, in_dtype, out_dtype, accum_dtype, num_bits: i
     example_dequant_gemm_fine_grained.py:427-428: C = A_int8 @ unpack_u4(qB)^T, exact.
     """
     in_t, out_t, acc_t = as_torch_dtype(in_dtype), as_torch_dtype(out_dtype), as_torch_dtype(accum_dtype)
+    if in_t == torch.int8:
+        return _matmul_int8_unsigned(M, N, K, out_t, acc_t, group_size or with_scaling or with_zeros or with_bias,
+                                     num_bits, str(source_format).lower() == "int")
     if num_bits in (1, 2) and as_torch_dtype(in_dtype) in (torch.float16, torch.bfloat16):
         return _matmul_low_bits(M, N, K, in_t, out_t, acc_t, num_bits, group_size, with_scaling, with_zeros, zeros_mode,
                                 str(source_format).lower(), with_bias, trans_c)
     if num_bits != 4:
         raise ValueError("matmul: num_bits must be 4 (or 1 / 2 with float16 / bfloat16 activations)")
-    if in_t == torch.int8:
-        return _matmul_int8_unsigned(M, N, K, out_t, acc_t, group_size or with_scaling or with_zeros or with_bias)
     if in_t not in (torch.float16, torch.bfloat16):
         raise ValueError("matmul: in_dtype must be float16, bfloat16 or int8")
     if acc_t != torch.float32:
@@ -289,17 +290,32 @@ def _matmul_low_bits(M, N, K, in_t, out_t, acc_t, num_bits, group_size, with_sca
                          f"b200dq umma_dequant_gemm: M={M} N={N} K={K} in={in_t} out={out_t} int{num_bits} group={group_size}")
 
 
-def _matmul_int8_unsigned(M: int, N: int, K: int, out_t: torch.dtype, acc_t: torch.dtype, extras) -> DequantKernel:
-    """``C[M, N] int32 = A_int8 @ unpack_u4(qB)^T`` with the raw unsigned codes: the int8 -> int32
-    variant of example_dequant_gemm_fine_grained.py (:427-428 run it with accum int32)."""
+def _matmul_int8_unsigned(M: int, N: int, K: int, out_t: torch.dtype, acc_t: torch.dtype, extras, num_bits: int = 4,
+                          signed: bool = False) -> DequantKernel:
+    """``C[M, N] int32 = A_int8 @ unpack(qB)^T`` with raw integer codes: the int8 -> int32 variant of
+    example_dequant_gemm_fine_grained.py (:427-428 run it with accum int32) for 4-bit codes, and
+    the int2 -> int8 and int1 -> int8 decode rules of quantize/lop3.py:893-1047 for 2- and 1-bit
+    codes. Unsigned codes are the weight; ``signed`` reads them as q - 8, q - 2 or 2 q - 1.
+    1-bit codes are widened to 2-bit fields once, at pack time."""
     if out_t != torch.int32 or acc_t != torch.int32:
         raise ValueError("matmul: int8 activations accumulate and return int32")
     if extras:
         raise ValueError("matmul: the int8 variant takes raw codes only (no scale, zeros or bias)")
-    params = [Param("A", (M, K), torch.int8), Param("B", (N, K // 2), torch.uint8), Param("C", (M, N), torch.int32)]
+    if num_bits not in (1, 2, 4):
+        raise ValueError("matmul: num_bits must be 1, 2 or 4")
+    params = [Param("A", (M, K), torch.int8), Param("B", (N, K * num_bits // 8), torch.uint8),
+              Param("C", (M, N), torch.int32)]
 
     def pack_fn(qB):
-        return ops.pack_int4_for_int8(qB.view(torch.uint8), N, K, code_offset=0)
+        q = qB.view(torch.uint8)
+        if num_bits == 4:
+            return ops.pack_int4_for_int8(q, N, K, code_offset=8 if signed else 0)
+        if num_bits == 2:
+            return ops.pack_int2(q, N, K, code_offset=2 if signed else 0)
+        from . import quantize
+        codes = quantize.decompress_codes(q, 1)
+        return ops.pack_int2(quantize.compress_codes(codes * 2 if signed else codes, 2).contiguous(), N, K,
+                             code_offset=1 if signed else 0)
 
     def impl(kernel: DequantKernel, A, qB):
         _check(A, params[0])
