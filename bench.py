@@ -746,9 +746,48 @@ def run_moe(args, rank, world, local_rank):
     }))
 
 
+def run_mxfp4(args, local_rank):
+    """Secondary workload: the MXFP4 shape (N = 14336, K = 4096) on the block-scaled fp4
+    instruction, activation quantiser included, at ``--m`` tokens. One GPU."""
+    from tilelang_b200 import ops
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    N, K, M = 14336, 4096, args.m
+    gen = torch.Generator().manual_seed(5)
+    ws = []
+    for _ in range(5):
+        q = torch.randint(0, 256, (N, K // 2), generator=gen, dtype=torch.uint8).to(dev)
+        e = (torch.randint(-8, 1, (N, K // 32), generator=gen) + 127).to(torch.uint8)
+        ws.append((q, ops.block_mxfp4_scales(e).to(dev)))
+    a = torch.randn(M, K, generator=gen).to(torch.bfloat16).to(dev)
+    c = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+
+    def step(i):
+        codes, sf = ops.quant_mxfp4(a, blocked_scales=True)
+        ops.gemm_mxfp4_native(codes, sf, ws[i][0], ws[i][1], out=c)
+
+    for i in range(max(args.warmup, 3)):
+        step(i % len(ws))
+    with ClockSampler(local_rank) as clocks:
+        ms = time_rotating(step, len(ws), rounds=max(1, args.steps // len(ws)))
+        time.sleep(0.25)
+    ops.check_status(dev)
+    peak = ops.tensor_peak("mxfp4") / 1e12
+    tf = 2.0 * M * N * K / ms / 1e9
+    print(json.dumps({
+        "metric": "mxfp4_native_tflops", "value": tf, "unit": "TFLOPS", "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "fp4 (e2m1 x e2m1, e8m0 scales per 32, fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": f"MXFP4 native: M={M}, N={N}, K={K}, bf16 activations quantised to MXFP4 in the step",
+                   "l2": "five weight copies round-robin (inputs larger than L2)"},
+        "roofline": {"bound": "tensor", "achieved": tf, "peak": peak, "unit": "TFLOP/s", "frac": tf / peak,
+                     "peak_source": "b200dq_tensor_peak(mxfp4) in this run", "traffic": None},
+        "gpu_launches": 2 * args.steps, "clocks": clocks.summary()}))
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", default="dense", choices=["dense", "moe"])
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe", "mxfp4"])
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
@@ -770,7 +809,11 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local_rank))
     try:
-        (run_moe if args.workload == "moe" else run_ours)(args, rank, world, local_rank)
+        if args.workload == "mxfp4":
+            if rank == 0:
+                run_mxfp4(args, local_rank)
+        else:
+            (run_moe if args.workload == "moe" else run_ours)(args, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist
