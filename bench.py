@@ -205,15 +205,19 @@ def workload_config(M, gpus, allgather):
                   "use inputs larger than L2 (several packed weight copies, round-robin)"}
 
 
-# DRAM bytes of one launch of the dominant kernel at M=4096: dram__bytes_read.sum 631,474,432 +
-# dram__bytes_write.sum 243,267,584 of one ncu --set full capture; the algorithmic figure is
-# 426,770,432.
-TRAFFIC_M4096 = {"dram_bytes_per_launch": 874742016,
-                 "source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch of the same command"}
+# DRAM traffic of the dominant kernel per launch, from one ncu --set full capture of this
+# command at the given M (dram__bytes_read.sum + dram__bytes_write.sum): M = 4096
+# 658,700,800 + 243,296,768 (algorithmic 426,770,432); M = 16 125,076,480 + 4,282,112 and
+# M = 1 124,828,160 + 4,124,672 (algorithmic 125,960,192 / 125,656,066: the weight is read once,
+# the writes are stream-K partial tiles).
+TRAFFIC = {4096: 901997568, 16: 129358592, 1: 128952832}
 
 
 def load_traffic_note(M):
-    return TRAFFIC_M4096 if M == 4096 else {}
+    if M not in TRAFFIC:
+        return {}
+    return {"dram_bytes_per_launch": TRAFFIC[M],
+            "source": "ncu dram__bytes_read.sum + dram__bytes_write.sum, one launch of the same command"}
 
 
 def other_configs(dev, peaks):
