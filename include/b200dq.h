@@ -33,7 +33,11 @@ enum b200dq_weight_format {
   B200DQ_WF_FP4_E8M0 = 3, /* fp4 codes + one e8m0 exponent byte per 32 K elements (bf16
                            * activations; with fp16 activations the exponent bytes are ignored) */
   B200DQ_WF_I2_I8 = 4,    /* 2-bit codes -> int8 (minus code_bias); int8 activations    */
-  B200DQ_WF_I4_I8 = 5     /* 4-bit codes -> int8 (minus code_bias); int8 activations    */
+  B200DQ_WF_I4_I8 = 5,    /* 4-bit codes -> int8 (minus code_bias); int8 activations    */
+  B200DQ_WF_U2_SZ = 6,    /* 2-bit codes + per-group scale and zero-point; fp16/bf16 activations
+                           * (the int2 / int1 -> f16 decoders of quantize/lop3.py:424-891) */
+  B200DQ_WF_LUT4_S = 7    /* 4-bit index into code_table[16] * per-group scale (NF4 and other
+                           * codebooks); fp16/bf16 activations                            */
 };
 enum b200dq_act_type { B200DQ_ACT_F16 = 0, B200DQ_ACT_BF16 = 1, B200DQ_ACT_I8 = 2 };
 enum b200dq_out_type { B200DQ_OUT_F16 = 0, B200DQ_OUT_BF16 = 1, B200DQ_OUT_F32 = 2, B200DQ_OUT_I32 = 3 };
@@ -107,6 +111,9 @@ typedef struct b200dq_gemm_args {
    * before anyone reads a gathered tensor. The reference is single-GPU and has no counterpart. */
   void* c_peers[7];
   int32_t num_peers;
+  /* B200DQ_WF_LUT4_S only: the value of each of the 16 codes (NF4 or any other 4-bit codebook);
+   * weight = code_table[q] * scale[row, group], the table rounded to the activation dtype. */
+  float code_table[16];
 } b200dq_gemm_args;
 
 /* Replaces call(...) of the kernels generated from

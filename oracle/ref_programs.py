@@ -374,6 +374,25 @@ def ref_low_bits_a16(A: torch.Tensor, qB: torch.Tensor, bits: int, scales, zeros
     return torch.matmul(A.float(), W.T).to(out_dtype)
 
 
+NF4_LEVELS = (-1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748809814453, -0.28444138169288635,
+              -0.18477343022823334, -0.09105003625154495, 0.0, 0.07958029955625534, 0.16093020141124725,
+              0.24611230194568634, 0.33791524171829224, 0.44070982933044434, 0.5626170039176941,
+              0.7229568362236023, 1.0)
+
+
+def ref_lut4(A: torch.Tensor, qB: torch.Tensor, scales: torch.Tensor, group_size: int, table=NF4_LEVELS,
+             out_dtype=torch.bfloat16) -> torch.Tensor:
+    """Codebook weights (NF4): weight = table[q] * scale, both rounded to the activation dtype and
+    the product rounded once more, as a dequantise-then-matmul ref_program in that dtype does
+    (the structure of example_dequant_gemm_fine_grained.py:84-90; the reference has no NF4 code).
+    Codes two per byte, even k in the low nibble."""
+    q = qB.to(torch.int64)
+    codes = torch.stack((q & 15, q >> 4), dim=-1).reshape(qB.shape[0], -1)
+    t = torch.tensor(table, dtype=torch.float32).to(A.dtype)
+    W = (t[codes].float() * scales.float().repeat_interleave(group_size, dim=1)).to(A.dtype)
+    return torch.matmul(A.float(), W.float().T).to(out_dtype)
+
+
 def ref_mxfp4_native(A: torch.Tensor, qB: torch.Tensor, scale_bytes: torch.Tensor, out_dtype=torch.bfloat16):
     """Both operands MXFP4: the activation is re-quantised per row and 32-block the way the
     reference's kernel does (:func:`mxfp4_act_quant`, ties to even), then

@@ -350,6 +350,24 @@ def test_int2_and_int1_weights_on_16_bit_activations(bits, signed, M, N, K, dtyp
     tb.check_status()
 
 
+@pytest.mark.parametrize("M,N,K,dtype", [(2, 256, 256, torch.bfloat16), (150, 384, 1024, torch.float16),
+                                         (300, 130, 512, torch.bfloat16)])
+def test_nf4_codebook_weights(M, N, K, dtype):
+    """NF4: 4-bit indices into the 16-level table times a per-block absmax. One-hot rows read the
+    dequantised weights back bit for bit (all 16 codes), then the GEMM against the oracle."""
+    group = 64 if K == 512 else 128
+    name = {torch.float16: "float16", torch.bfloat16: "bfloat16"}[dtype]
+    A = torch.randn(M, K, generator=gen(1)).to(dtype)
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(2), dtype=torch.uint8)
+    s = (torch.rand(N, K // group, generator=gen(3)) * 0.05 + 0.01).to(dtype)
+    kernel = tb.matmul(M, N, K, name, name, "float32", num_bits=4, group_size=group, source_format="nf4")
+    eye = torch.zeros(M, K, dtype=dtype)
+    eye[torch.arange(M), torch.arange(M) * 5 % K] = 1.0
+    assert torch.equal(kernel(eye.to(DEV), qB.to(DEV), s.to(DEV)).cpu(), R.ref_lut4(eye, qB, s, group, out_dtype=dtype))
+    check_float(kernel(A.to(DEV), qB.to(DEV), s.to(DEV)), R.ref_lut4(A, qB, s, group, out_dtype=dtype))
+    tb.check_status()
+
+
 def test_dequantize_gemv_reference_flow():
     # example_dequant_gemv_fp16xint4.py:158-217: weights pre-permuted by interleave_weight
     M, N, K = 1, 1024, 1024

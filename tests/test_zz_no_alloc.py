@@ -84,13 +84,14 @@ def test_static_scratch_size_check_accepts_and_rejects():
     """The size check the entry point applies, through the helper that needs no GPU."""
     lib = _lib.load()
     need, cap = ctypes.c_size_t(0), ctypes.c_size_t(0)
-    # the benchmark weight at 4096 tokens on a 148-SM part: 148 CTAs x 2 slots x 256 x 128 x 4 B
+    # the benchmark weight at 4096 tokens on a 148-SM part: 148 CTAs x 2 slots x 256 x 128 x 4 B of partial
+    # tiles and one 8-byte arrival counter per tile (16 x 224 tiles)
     a = _sized_args(4096, 28672, 8192)
     assert lib.b200dq_static_scratch_check(ctypes.byref(a), 148, ctypes.byref(need), ctypes.byref(cap)) == 0
-    assert cap.value == 40 << 20 and need.value == 148 * 2 * 256 * 128 * 4
+    assert cap.value == 40 << 20 and need.value == 148 * 2 * 256 * 128 * 4 + 16 * 224 * 8
     # a part with more SMs plans more CTAs, whose partial tiles no longer fit the array
     assert lib.b200dq_static_scratch_check(ctypes.byref(a), 192, ctypes.byref(need), ctypes.byref(cap)) == -1
-    assert need.value == 192 * 2 * 256 * 128 * 4 > cap.value
+    assert need.value == 192 * 2 * 256 * 128 * 4 + 16 * 224 * 8 > cap.value
     msg = _lib.last_error()
     assert "static array holds" in msg and "max_ctas" in msg
     # ... unless the caller bounds the grid
@@ -101,7 +102,7 @@ def test_static_scratch_size_check_accepts_and_rejects():
     assert lib.b200dq_static_scratch_check(ctypes.byref(a), 148, ctypes.byref(need), None) == 0 and need.value == 0
     a = _sized_args(8, 28672, 8192)
     assert lib.b200dq_static_scratch_check(ctypes.byref(a), 148, ctypes.byref(need), None) == 0
-    assert need.value == 148 * 2 * 16 * 128 * 4
+    assert need.value == 148 * 2 * 16 * 128 * 4 + 224 * 8
 
 
 def test_static_scratch_rejects_bad_arguments():

@@ -15,7 +15,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libb200dq.so")
 
 # enum values of include/b200dq.h
-WF_U4_SZ, WF_U4_RAW, WF_S4_RAW, WF_FP4_E8M0, WF_I2_I8, WF_I4_I8, WF_U2_SZ = range(7)
+WF_U4_SZ, WF_U4_RAW, WF_S4_RAW, WF_FP4_E8M0, WF_I2_I8, WF_I4_I8, WF_U2_SZ, WF_LUT4_S = range(8)
 ACT_F16, ACT_BF16, ACT_I8 = range(3)
 OUT_F16, OUT_BF16, OUT_F32, OUT_I32 = range(4)
 GF_TRANS_C, GF_HAS_BIAS, GF_ROW_SCALE, GF_FP4_SIMPLE = 1, 2, 4, 16
@@ -43,7 +43,7 @@ EXPORTED_SYMBOLS = (
 )
 
 
-ABI_VERSION = 4      # b200dq_version(): layout of struct b200dq_gemm_args
+ABI_VERSION = 5      # b200dq_version(): layout of struct b200dq_gemm_args
 
 
 class GemmArgs(ctypes.Structure):
@@ -77,6 +77,7 @@ class GemmArgs(ctypes.Structure):
         ("total_tiles", ctypes.c_int32),
         ("c_peers", ctypes.c_void_p * 7),
         ("num_peers", ctypes.c_int32),
+        ("code_table", ctypes.c_float * 16),
     ]
 
 

@@ -30,7 +30,7 @@ namespace {
 using namespace b200dq;
 
 constexpr int kMaxDevices = 32;
-constexpr int kAbiVersion = 4;
+constexpr int kAbiVersion = 5;
 constexpr int kMinSpan = 8;   // fewest k-blocks worth giving a CTA of its own
 
 thread_local char g_err[1024] = "";
@@ -102,7 +102,7 @@ int token_tile_for(int M) {
 struct Schedule {
   int tn, m_tiles, n_tiles, st_total, grid, span;
   long long units;
-  size_t workspace_bytes;
+  size_t workspace_bytes, slot_bytes;
   bool needs_scratch;   // some tile is cut between CTAs
 };
 
@@ -116,7 +116,7 @@ int stages_for(int K, int act_type) {
 
 // scale words per row and stage
 int nsz_for(int weight_format, int group_size) {
-  if (weight_format == WF_U4_SZ || weight_format == WF_U2_SZ) return group_size == 64 ? 2 : 1;
+  if (weight_format == WF_U4_SZ || weight_format == WF_U2_SZ || weight_format == WF_LUT4_S) return group_size == 64 ? 2 : 1;
   if (weight_format == WF_FP4_E8M0) return 1;
   return 0;
 }
@@ -143,7 +143,9 @@ int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_cta
   if (g > cap) g = cap;
   s->span = static_cast<int>((s->units + g - 1) / g);
   s->grid = static_cast<int>((s->units + s->span - 1) / s->span);
-  s->workspace_bytes = static_cast<size_t>(s->grid) * 2 * s->tn * kTileRows * sizeof(uint32_t);
+  // two partial-tile slots per CTA, then one 64-bit arrival counter per tile (small-M kernel)
+  s->slot_bytes = static_cast<size_t>(s->grid) * 2 * s->tn * kTileRows * sizeof(uint32_t);
+  s->workspace_bytes = s->slot_bytes + static_cast<size_t>(tiles) * sizeof(unsigned long long);
   s->needs_scratch = (s->span % s->st_total != 0) && s->grid > 1;
   return 0;
 }
@@ -341,7 +343,7 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   if (a->out_type < OUT_F16 || a->out_type > OUT_I32) return fail("%s: unknown output type %d", who, a->out_type);
   if (wf_int != int_act) return fail("%s: weight format %d and activation type %d do not go together", who, wf, act);
   if (wf == WF_FP4_E8M0 && act == ACT_I8) return fail("%s: fp4 weights need f16 or bf16 activations", who);
-  if ((wf == WF_U4_SZ || wf == WF_U2_SZ) && (a->group_size <= 0 || a->K % a->group_size != 0))
+  if ((wf == WF_U4_SZ || wf == WF_U2_SZ || wf == WF_LUT4_S) && (a->group_size <= 0 || a->K % a->group_size != 0))
     return fail("%s: group_size=%d must divide K=%d", who, a->group_size, a->K);
   if ((a->flags & GF_HAS_BIAS) && a->bias == nullptr) return fail("%s: HAS_BIAS set but bias is null", who);
   if ((a->flags & GF_ROW_SCALE) && a->row_scale == nullptr) return fail("%s: ROW_SCALE set but row_scale is null", who);
@@ -426,13 +428,28 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   p.n_tiles = s.n_tiles; p.m_tiles = s.m_tiles; p.st_total = s.st_total;
   p.span = s.span; p.units = s.units;
   p.stage_bytes = stage_bytes_for(wf, a->group_size);
-  p.sz_per_kb = ((wf == WF_U4_SZ || wf == WF_U2_SZ) && a->group_size == 64) ? 1 : 0;
+  p.sz_per_kb = ((wf == WF_U4_SZ || wf == WF_U2_SZ || wf == WF_LUT4_S) && a->group_size == 64) ? 1 : 0;
   p.ldc = (a->flags & GF_TRANS_C) ? a->M : a->N;
   p.flags = flags;
   p.out_type = a->out_type;
   p.tn = s.tn;
   p.num_groups = grouped ? a->num_groups : 0;
   p.dyn_grid = dyn ? s.grid : 0;
+  if (wf == WF_LUT4_S) {
+    // the table in the activation dtype, low and high bytes apart
+    for (int i = 0; i < 16; ++i) {
+      const float v = a->code_table[i];
+      const uint16_t bits = act == ACT_BF16 ? __bfloat16_as_ushort(__float2bfloat16_rn(v)) : __half_as_ushort(__float2half_rn(v));
+      p.lut_lo[i >> 2] |= static_cast<uint32_t>(bits & 0xffu) << (8 * (i & 3));
+      p.lut_hi[i >> 2] |= static_cast<uint32_t>(bits >> 8) << (8 * (i & 3));
+    }
+  }
+  if (s.needs_scratch) {
+    // unique per launch in this process; a counter word left by another launch never matches
+    static std::atomic<unsigned long long> launch_epoch{0x5bd1e995ull};
+    p.tile_ctr = reinterpret_cast<unsigned long long*>(static_cast<uint8_t*>(scratch) + s.slot_bytes);
+    p.epoch = launch_epoch.fetch_add(1, std::memory_order_relaxed) & 0x00ffffffffffffffull;
+  }
   p.n_peers = a->num_peers;
   for (int d = 0; d < a->num_peers; ++d) p.c_peer[d] = a->c_peers[d];
   p.grp_row_prefix = grouped ? a->group_row_prefix : nullptr;
@@ -520,18 +537,18 @@ int b200dq_pack_weights(const void* q_natural, const void* scales, const void* z
   p.q = static_cast<const uint32_t*>(q_natural);
   p.wp = static_cast<uint32_t*>(wp);
   p.N = N; p.K = K; p.bits = bits;
-  p.mode = int8_target ? 1 : (weight_format == WF_FP4_E8M0 ? 2 : 0);
+  p.mode = int8_target ? 1 : (weight_format == WF_FP4_E8M0 ? 2 : (weight_format == WF_LUT4_S ? 3 : 0));
   p.n_tiles = (N + kTileRows - 1) / kTileRows;
   p.st_total = stages_for(K, int8_target ? ACT_I8 : ACT_BF16);
   p.code_words_per_kb = codes_per_kblock_bytes(weight_format) / 4;
   p.elems_per_kblock = int8_target ? 128 : 64;
-  if (weight_format == WF_U4_SZ || weight_format == WF_U2_SZ) {
+  if (weight_format == WF_U4_SZ || weight_format == WF_U2_SZ || weight_format == WF_LUT4_S) {
     if (scales == nullptr) return fail("pack_weights: this weight format needs scales");
     if (act_type != ACT_F16 && act_type != ACT_BF16) return fail("pack_weights: scales must be f16 or bf16");
     if (group_size <= 0 || K % group_size != 0) return fail("pack_weights: group_size=%d must divide K=%d", group_size, K);
     if (!(group_size == 64 || group_size % 128 == 0 || group_size == K))
       return fail("pack_weights: group_size=%d must be 64, a multiple of 128, or K", group_size);
-    p.sz_kind = 1;
+    p.sz_kind = weight_format == WF_LUT4_S ? 3 : 1;
     p.scales = static_cast<const uint16_t*>(scales);
     p.zeros = static_cast<const uint16_t*>(zeros);
     p.bf16 = (act_type == ACT_BF16);

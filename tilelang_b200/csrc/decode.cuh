@@ -126,6 +126,45 @@ __device__ __forceinline__ void decode_u2_chunk(const uint4& packed, uint32_t sz
   decode_u2_word<kBf16>(packed.w, s2, nz2, &out[24]);
 }
 
+// 4-bit index into a 16-entry table of 16-bit floats, times a per-group scale (NF4 and other
+// codebooks; the reference names NF4 among its benchmarked formats but ships no decoder).
+// Codes are in natural nibble order (element e at bit 4 e). The table lives in eight registers,
+// low bytes and high bytes apart; four codes are looked up at once with byte permutes: the low
+// three bits of each nibble select among entries 0-7 and among entries 8-15, bit 3 (turned into
+// a byte mask by the permute's sign replication) picks between the two, and two more permutes
+// interleave low and high bytes into two registers of two elements each.
+template <bool kBf16>
+__device__ __forceinline__ void decode_lut4_word(uint32_t w, uint32_t s2, const uint32_t (&lo)[4],
+                                                 const uint32_t (&hi)[4], uint32_t* out) {
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const uint32_t x = k ? (w >> 16) : w;
+    const uint32_t sel = x & 0x7777u;
+    uint32_t m;                                            // byte j = 0xff if bit 3 of nibble j is set
+    asm("prmt.b32 %0, %1, %2, 0xD9C8;" : "=r"(m) : "r"(x << 4), "r"(x));   // selector bit 3: replicate the byte's sign
+    const uint32_t l = (__byte_perm(lo[0], lo[1], sel) & ~m) | (__byte_perm(lo[2], lo[3], sel) & m);
+    const uint32_t h = (__byte_perm(hi[0], hi[1], sel) & ~m) | (__byte_perm(hi[2], hi[3], sel) & m);
+    const uint32_t v0 = __byte_perm(l, h, 0x5140), v1 = __byte_perm(l, h, 0x7362);
+    if constexpr (kBf16) {
+      out[2 * k] = bf162_as_u32(__hmul2(u32_as_bf162(v0), u32_as_bf162(s2)));
+      out[2 * k + 1] = bf162_as_u32(__hmul2(u32_as_bf162(v1), u32_as_bf162(s2)));
+    } else {
+      out[2 * k] = h2_as_u32(__hmul2(u32_as_h2(v0), u32_as_h2(s2)));
+      out[2 * k + 1] = h2_as_u32(__hmul2(u32_as_h2(v1), u32_as_h2(s2)));
+    }
+  }
+}
+
+template <bool kBf16>
+__device__ __forceinline__ void decode_lut4_chunk(const uint4& packed, uint32_t sz, const uint32_t (&lo)[4],
+                                                  const uint32_t (&hi)[4], uint32_t (&out)[16]) {
+  const uint32_t s2 = __byte_perm(sz, 0, 0x1010);
+  decode_lut4_word<kBf16>(packed.x, s2, lo, hi, &out[0]);
+  decode_lut4_word<kBf16>(packed.y, s2, lo, hi, &out[4]);
+  decode_lut4_word<kBf16>(packed.z, s2, lo, hi, &out[8]);
+  decode_lut4_word<kBf16>(packed.w, s2, lo, hi, &out[12]);
+}
+
 // No scale at all: weight = q (unsigned) or q - 8 (signed storage), as in the
 // reference's fine-grained example (example_dequant_gemm_fine_grained.py:11-13).
 template <bool kBf16, bool kSigned>

@@ -66,8 +66,8 @@ struct PackParams {
   const uint8_t* exps;      // FP4_E8M0: (N, K/32) exponent bytes
   uint32_t* wp;             // packed image
   int N, K, bits;
-  int mode;                 // 0 integer codes -> 16-bit, 1 integer codes -> 8-bit, 2 e2m1 -> bf16
-  int sz_kind;              // 0 none, 1 u4 scale/zero words, 2 e8m0 byte quads
+  int mode;                 // 0 integer codes -> 16-bit, 1 integer codes -> 8-bit, 2 e2m1 -> bf16, 3 natural order
+  int sz_kind;              // 0 none, 1 u4 scale/zero words, 2 e8m0 byte quads, 3 plain scale in the low half
   int bf16;                 // activation dtype of the scale words
   int n_tiles, st_total;
   int code_words_per_kb;    // 1024 or 2048
@@ -103,20 +103,24 @@ __global__ void pack_image_kernel(const PackParams p) {
     if (n < p.N && k0 < p.K) w = p.q[(static_cast<long long>(n) * p.K + k0) / elems_per_word];
     if (p.mode == 0) out = interleave_word(w, p.bits, 16);
     else if (p.mode == 1) out = interleave_word(w, p.bits, 8);
-    else out = twiddle_fp4_word(w);
+    else if (p.mode == 2) out = twiddle_fp4_word(w);
+    else out = w;
   } else {
     const int r = wi - 2 * p.code_words_per_kb;
     const int si = r >> 7;
     const int row = r & 127;
     const int n = nt * 128 + row;
     if (n < p.N) {
-      if (p.sz_kind == 1) {
+      if (p.sz_kind == 1 || p.sz_kind == 3) {
         const int k_start = (stg * 2 + (p.nsz == 2 ? si : 0)) * 64;
         if (k_start < p.K) {
           const int g = min(k_start / p.group_size, p.groups - 1);
           const uint16_t s_raw = p.scales[static_cast<size_t>(n) * p.groups + g];
           uint16_t lo, hi;
-          if (p.bf16) {
+          if (p.sz_kind == 3) {
+            lo = s_raw;
+            hi = 0;
+          } else if (p.bf16) {
             const float s = __bfloat162float(__ushort_as_bfloat16(s_raw));
             const float z = p.zeros ? __bfloat162float(__ushort_as_bfloat16(p.zeros[static_cast<size_t>(n) * p.groups + g])) : 8.f;
             lo = __bfloat16_as_ushort(__float2bfloat16_rn(s * 64.f));

@@ -13,7 +13,9 @@
 // and e2m1 weights with e8m0 block scales take this path.
 //
 // Work split: the same stream-K schedule, segments and scratch format as the tcgen05
-// kernel (token tile 16), so the same fix-up pass finishes tiles cut between CTAs. A ring
+// kernel (token tile 16). A tile cut between CTAs is finished inside the kernel: every CTA
+// writes its partial sums, counts itself in on the tile's counter, and the last one adds the
+// partial sums in ascending CTA order (no second launch). A ring
 // slot holds one stage (128 rows x 128 k of codes, their scale words, and the tokens'
 // 128 k). The consumer warps form four teams of four; team t takes the slots whose
 // CTA-wide index is t modulo 4, warp r of the team the weight rows [32 r, +32). The four
@@ -81,6 +83,9 @@ struct SkinnyCtl {
   uint64_t full[kSkinnyMaxSlots];
   uint64_t empty[kSkinnyMaxSlots];
   int abort_flag;
+  int finish_tile;   // this CTA brought the last partial sum of a cut tile
+  int others_done;   // the other CTAs' sums of this CTA's cut tile were published before it got there
+  long long pending[2];
 };
 static_assert(sizeof(SkinnyCtl) <= kSkinnyCtlBytes, "control block must fit its slot");
 
@@ -135,6 +140,18 @@ __device__ __forceinline__ void skinny_decode(const GemmParams& p, const uint4& 
                                (p.flags & GF_FP4_SIMPLE) != 0, out);
 }
 
+// Registers one more finished partial sum of a cut tile; true for the CTA that brings the last
+// of `expected`. The counter word carries the launch's epoch, a stale word counts as zero.
+__device__ __forceinline__ bool skinny_tile_arrive(unsigned long long* ctr, unsigned long long epoch, int expected) {
+  unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(ctr);
+  while (true) {
+    const unsigned long long want = ((old >> 8) == epoch) ? old + 1ull : ((epoch << 8) | 1ull);
+    const unsigned long long prev = atomicCAS(ctr, old, want);
+    if (prev == old) return static_cast<int>(want & 0xffull) == expected;
+    old = prev;
+  }
+}
+
 // One summed output of a segment: a raw partial into the CTA's scratch slot, or the
 // finished value into C.
 __device__ __forceinline__ void skinny_store(const GemmParams& p, const Segment& w, int tok, int row, float v) {
@@ -152,6 +169,30 @@ __device__ __forceinline__ void skinny_store(const GemmParams& p, const Segment&
     case OUT_F16: store_everywhere(p, idx, finish_value<__half, false>(p, bits, m, n)); break;
     case OUT_BF16: store_everywhere(p, idx, finish_value<__nv_bfloat16, false>(p, bits, m, n)); break;
     default: store_everywhere(p, idx, finish_value<float, false>(p, bits, m, n)); break;
+  }
+}
+
+// Adds every CTA's published partial sums of a cut tile in ascending CTA order and stores the
+// outputs (all consumer threads; the sums come from L2).
+template <int kTok>
+__device__ __forceinline__ void skinny_finish_tile(const GemmParams& p, long long tile) {
+  __threadfence();
+  const long long t_begin = tile * p.st_total;
+  const int c_first = static_cast<int>(t_begin / p.span);
+  const int c_last = static_cast<int>((t_begin + p.st_total - 1) / p.span);
+  Segment whole;
+  locate_tile(p, tile, whole);
+  whole.slot = -1;
+  for (int o = threadIdx.x; o < kTok * kTileRows; o += kSkinnyConsumers) {
+    const int tok = o >> 7;
+    const int row = o & (kTileRows - 1);
+    float v = 0.f;
+    for (int cta = c_first; cta <= c_last; ++cta) {
+      // slot 0 if the tile holds the first segment of that CTA's span, else slot 1
+      const int slot = cta * 2 + ((static_cast<long long>(cta) * p.span >= t_begin) ? 0 : 1);
+      v += __uint_as_float(__ldcg(p.partial + (static_cast<size_t>(slot) * kSkinnyTokens + tok) * kTileRows + row));
+    }
+    skinny_store(p, whole, tok, row, v);
   }
 }
 
@@ -249,6 +290,7 @@ skinny_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const Gem
     uint32_t cnt0 = 0;                 // slots of this CTA before the current segment
     bool ok = true;
 
+    long long pending0 = -1, pending1 = -1;   // thread 0: cut tiles this CTA completed by surprise
     SegmentWalk walk(p);
     Segment w;
     while (walk.next(p, w)) {
@@ -312,7 +354,41 @@ skinny_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const Gem
       cnt0 += nst;
 
       // ---- add the teams' partial sums of every output in a fixed order
-      skinny_consumer_sync();   // the previous segment's readers are done with the buffer
+      // A tile cut between CTAs is the sum of the CTAs' partial sums in ascending CTA order
+      // (the same order in every launch: deterministic). The CTA that holds the tile's first
+      // stages works on them at the END of its span, the others at the START of theirs, so it
+      // almost always finds their sums published already: it then adds them to its own straight
+      // from L2 and stores the outputs, with nothing of its own written to scratch and no wait.
+      // Otherwise every contributor publishes its sums, counts itself in, and whoever counts
+      // last adds them all.
+      constexpr int kOuts = kTok * kTileRows / kSkinnyConsumers;     // outputs per thread
+      constexpr int kFast = 4;                                       // contributions held in registers
+      const bool cut = w.slot >= 0;
+      const long long t_begin = w.tile * p.st_total;
+      const int c_first = static_cast<int>(t_begin / p.span);
+      const int c_last = static_cast<int>((t_begin + p.st_total - 1) / p.span);
+      const int nc = c_last - c_first + 1;
+      // slot 0 if the tile holds the first segment of that CTA's span, else slot 1
+      auto slot_of = [&](int cta) { return cta * 2 + ((static_cast<long long>(cta) * p.span >= t_begin) ? 0 : 1); };
+      if (cut && threadIdx.x == 0) {
+        const unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(p.tile_ctr + w.tile);
+        ctl->others_done = (static_cast<int>(blockIdx.x) == c_first && nc <= kFast &&
+                            seen == ((p.epoch << 8) | static_cast<unsigned long long>(nc - 1))) ? 1 : 0;
+      }
+      skinny_consumer_sync();   // the previous segment's readers are done with the buffer; the flag is set
+      const bool others_done = cut && ctl->others_done != 0;
+      uint32_t raw[kOuts][kFast];
+      if (others_done) {
+        __threadfence();
+#pragma unroll
+        for (int jj = 1; jj < kFast; ++jj) {
+          if (jj < nc) {
+            const uint32_t* src = p.partial + static_cast<size_t>(slot_of(c_first + jj)) * kSkinnyTokens * kTileRows;
+#pragma unroll
+            for (int i = 0; i < kOuts; ++i) raw[i][jj] = __ldcg(src + threadIdx.x + i * kSkinnyConsumers);
+          }
+        }
+      }
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -324,15 +400,56 @@ skinny_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const Gem
             red[(team * kTok + tok) * kSkinnyRedStride + row] = acc[mt][nt][c];
           }
       skinny_consumer_sync();
-      for (int o = threadIdx.x; o < kTok * kTileRows; o += kSkinnyConsumers) {
+      Segment whole = w;
+      whole.slot = -1;
+#pragma unroll
+      for (int i = 0; i < kOuts; ++i) {
+        const int o = threadIdx.x + i * kSkinnyConsumers;
         const int tok = o >> 7;
         const int row = o & (kTileRows - 1);
         float v = 0.f;
 #pragma unroll
         for (int t = 0; t < kSkinnyTeams; ++t) v += red[(t * kTok + tok) * kSkinnyRedStride + row];
-        skinny_store(p, w, tok, row, v);
+        if (others_done) {
+          v = 0.f + v;      // the general path starts its sum at zero: keep the same roundings
+#pragma unroll
+          for (int jj = 1; jj < kFast; ++jj)
+            if (jj < nc) v += __uint_as_float(raw[i][jj]);
+          skinny_store(p, whole, tok, row, v);
+        } else {
+          skinny_store(p, w, tok, row, v);
+        }
+      }
+      if (cut && !others_done) {
+        // Everyone's partial sums are stored; thread 0 makes them visible device-wide (the barrier
+        // orders the others' stores before its fence) and counts this CTA in.
+        skinny_consumer_sync();
+        if (static_cast<int>(blockIdx.x) != c_first) {
+          // Not the CTA that normally finishes the tile: nobody waits for the count. Should this
+          // CTA turn out to be the last all the same, it finishes the tile when its span is done.
+          if (threadIdx.x == 0) {
+            __threadfence();
+            if (skinny_tile_arrive(p.tile_ctr + w.tile, p.epoch, nc)) {
+              if (pending0 < 0) pending0 = w.tile; else pending1 = w.tile;
+            }
+          }
+        } else {
+          if (threadIdx.x == 0) {
+            __threadfence();
+            ctl->finish_tile = skinny_tile_arrive(p.tile_ctr + w.tile, p.epoch, nc) ? 1 : 0;
+          }
+          skinny_consumer_sync();
+          if (ctl->finish_tile == 1) skinny_finish_tile<kTok>(p, w.tile);
+        }
       }
     }
+    // tiles this CTA happened to complete without being their usual finisher
+    skinny_consumer_sync();
+    if (threadIdx.x == 0) { ctl->pending[0] = pending0; ctl->pending[1] = pending1; }
+    skinny_consumer_sync();
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+      if (ctl->pending[i] >= 0) skinny_finish_tile<kTok>(p, ctl->pending[i]);
   }
 
   // ---------------- teardown ----------------

@@ -38,15 +38,6 @@ template <int WF, int ACT>
 cudaError_t launch_format(const CUtensorMap& tmap_a, const GemmParams& p, int grid, cudaStream_t stream) {
   if (p.M <= 8) SKINNY_OK((launch_one<1, WF, ACT>(tmap_a, p, grid, stream)));
   else SKINNY_OK((launch_one<2, WF, ACT>(tmap_a, p, grid, stream)));
-  if (p.span % p.st_total != 0 && grid > 1) {
-    const dim3 fgrid(grid - 1, kSkinnyTokens / fixup_tokens_per_block(kSkinnyTokens));
-    switch (p.out_type) {
-      case OUT_F16: streamk_fixup_kernel<__half, kSkinnyTokens, false><<<fgrid, kTileRows, 0, stream>>>(p); break;
-      case OUT_BF16: streamk_fixup_kernel<__nv_bfloat16, kSkinnyTokens, false><<<fgrid, kTileRows, 0, stream>>>(p); break;
-      default: streamk_fixup_kernel<float, kSkinnyTokens, false><<<fgrid, kTileRows, 0, stream>>>(p); break;
-    }
-    SKINNY_OK(cudaGetLastError());
-  }
   return cudaSuccess;
 }
 

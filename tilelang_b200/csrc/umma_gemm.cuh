@@ -61,8 +61,9 @@ enum WeightFormat : int {
   WF_I2_I8 = 4,       // 2-bit codes -> int8, minus `code_bias` (int8 activations)
   WF_I4_I8 = 5,       // 4-bit codes -> int8, minus `code_bias` (int8 activations)
   WF_U2_SZ = 6,       // 2-bit codes + per-group scale and zero-point -> f16/bf16: (q - z) * s
+  WF_LUT4_S = 7,      // 4-bit index into a 16-entry table (NF4 and other codebooks) * per-group scale
 };
-constexpr int kLastWeightFormat = WF_U2_SZ;
+constexpr int kLastWeightFormat = WF_LUT4_S;
 
 enum ActType : int { ACT_F16 = 0, ACT_BF16 = 1, ACT_I8 = 2 };
 enum OutType : int { OUT_F16 = 0, OUT_BF16 = 1, OUT_F32 = 2, OUT_I32 = 3 };
@@ -107,6 +108,14 @@ struct GemmParams {
   // lands in every rank's gathered tensor straight from the epilogue (no separate all-gather).
   void* c_peer[7];
   int n_peers;
+  // Small-M kernel only: tiles cut between CTAs are finished inside the kernel. tile_ctr holds one
+  // 64-bit word per weight tile, (epoch << 8) | arrivals; a word whose epoch is not this launch's
+  // counts as zero, so the array needs no clearing (the epoch is unique per launch).
+  // WF_LUT4_S: the 16 table entries in the activation dtype, split into their low and high bytes
+  // (entry i's low byte is byte i % 4 of lut_lo[i / 4]) for the byte-permute lookup.
+  uint32_t lut_lo[4], lut_hi[4];
+  unsigned long long* tile_ctr;
+  unsigned long long epoch;
   int dyn_grid;                  // > 0: grouped mode planned on the device -- the tile total is read from
                                  // grp_tile_prefix[num_groups] and cut evenly over dyn_grid CTAs (span, units unused)
   int tn;                        // tokens per tile (the kernel's TN)
@@ -124,7 +133,7 @@ __host__ __device__ constexpr int codes_per_kblock_bytes(int wf) {
 }
 // scale words carried by one stage in shared memory (upper bound, bytes)
 __host__ __device__ constexpr int sz_smem_bytes(int wf) {
-  return (wf == WF_U4_SZ || wf == WF_U2_SZ) ? 1024 : (wf == WF_FP4_E8M0 ? 512 : 0);
+  return (wf == WF_U4_SZ || wf == WF_U2_SZ || wf == WF_LUT4_S) ? 1024 : (wf == WF_FP4_E8M0 ? 512 : 0);
 }
 
 // TMEM plan: accumulators of the NI issuers in columns [0, kAccCols), then a ring
@@ -190,6 +199,7 @@ struct Segment {
   int row_end;   // one past the last valid row (M, or the end of the tile's group)
   size_t wp_off; // byte offset of the tile's packed image (group) inside wp
   int slot;      // -1: the segment is a whole tile and stores to C; else scratch slot index
+  long long tile;  // index of the tile in the (tile, stage) space
 };
 
 // Tile index -> rows, weight tile and image. Dense: tiles are ordered n-fastest so
@@ -246,6 +256,7 @@ struct SegmentWalk {
     const long long left = end - pos;
     s.st_end = static_cast<int>(min(static_cast<long long>(p.st_total), s.st_begin + left));
     locate_tile(p, tile, s);
+    s.tile = tile;
     const bool whole = (s.st_begin == 0 && s.st_end == p.st_total);
     s.slot = whole ? -1 : (static_cast<int>(blockIdx.x) * 2 + (first ? 0 : 1));
     first = false;
@@ -565,7 +576,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
         constexpr int RPC = 32 / CH;              // TMEM columns produced by one chunk
         if (mine) {
           uint32_t sz0 = 0, sz1 = 0;
-          if constexpr (WF == WF_U4_SZ || WF == WF_U2_SZ) {
+          if constexpr (WF == WF_U4_SZ || WF == WF_U2_SZ || WF == WF_LUT4_S) {
             const uint32_t* szp = reinterpret_cast<const uint32_t*>(stage + Ring::kCodeBytes);
             sz0 = szp[row_in_tile];
             sz1 = p.sz_per_kb ? szp[128 + row_in_tile] : sz0;
@@ -589,6 +600,8 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
               decode_i4_chunk(cq, p.code_bias, regs);
             } else if constexpr (WF == WF_U2_SZ) {
               decode_u2_chunk<kBf16>(cq, h == 0 ? sz0 : sz1, regs);
+            } else if constexpr (WF == WF_LUT4_S) {
+              decode_lut4_chunk<kBf16>(cq, h == 0 ? sz0 : sz1, p.lut_lo, p.lut_hi, regs);
             } else if constexpr (WF == WF_U4_SZ) {
               decode_u4_chunk<kBf16>(cq, h == 0 ? sz0 : sz1, regs);
             } else if constexpr (WF == WF_U4_RAW) {

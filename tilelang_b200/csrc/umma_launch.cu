@@ -10,6 +10,8 @@ cudaError_t launch_umma_gemm(int wf, int act, int tn, const CUtensorMap& tmap, c
   if (wf == WF_U4_SZ && act == ACT_BF16) return launch_umma_u4sz_bf16(tn, tmap, p, grid, stream);
   if (wf == WF_U2_SZ && act == ACT_F16) return launch_umma_u2sz_f16(tn, tmap, p, grid, stream);
   if (wf == WF_U2_SZ && act == ACT_BF16) return launch_umma_u2sz_bf16(tn, tmap, p, grid, stream);
+  if (wf == WF_LUT4_S && act == ACT_F16) return launch_umma_lut4_f16(tn, tmap, p, grid, stream);
+  if (wf == WF_LUT4_S && act == ACT_BF16) return launch_umma_lut4_bf16(tn, tmap, p, grid, stream);
   if (wf == WF_U4_RAW && act == ACT_F16) return launch_umma_u4raw_f16(tn, tmap, p, grid, stream);
   if (wf == WF_U4_RAW && act == ACT_BF16) return launch_umma_u4raw_bf16(tn, tmap, p, grid, stream);
   if (wf == WF_S4_RAW && act == ACT_F16) return launch_umma_s4raw_f16(tn, tmap, p, grid, stream);

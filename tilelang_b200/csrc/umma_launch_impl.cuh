@@ -60,6 +60,8 @@ cudaError_t launch_umma_u4sz_f16(int, const CUtensorMap&, const GemmParams&, int
 cudaError_t launch_umma_u4sz_bf16(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
 cudaError_t launch_umma_u2sz_f16(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
 cudaError_t launch_umma_u2sz_bf16(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
+cudaError_t launch_umma_lut4_f16(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
+cudaError_t launch_umma_lut4_bf16(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
 cudaError_t launch_umma_u4raw_f16(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
 cudaError_t launch_umma_u4raw_bf16(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);
 cudaError_t launch_umma_s4raw_f16(int, const CUtensorMap&, const GemmParams&, int, cudaStream_t);

@@ -159,6 +159,8 @@ def matmul(M: int, N: int, K: int, in_dtype, out_dtype, accum_dtype, num_bits: i
         raise ValueError("matmul: accumulation is float32 (tcgen05 kind::f16 accumulates in fp32)")
     if zeros_mode not in ops.ZEROS_MODES:
         raise ValueError(f"matmul: zeros_mode must be one of {ops.ZEROS_MODES}")
+    if str(source_format).lower() == "nf4":
+        return _matmul_nf4(M, N, K, in_t, out_t, group_size, with_bias, trans_c)
     is_fp4 = str(source_format).lower() in ("fp4", "e2m1", "mxfp4", "uint32", "fp")
     if with_scaling is None:
         with_scaling = bool(group_size) or is_fp4
@@ -245,6 +247,29 @@ def matmul_mxfp4_native(M: int, N: int, K: int, in_dtype="bfloat16", out_dtype="
                            f"b200dq kind::mxf4.block_scale: M={M} N={N} K={K} in={in_t} out={out_t}")
     kernel.quantized = quantized
     return kernel
+
+
+def _matmul_nf4(M, N, K, in_t, out_t, group_size, with_bias, trans_c) -> DequantKernel:
+    """NF4 weights: inputs ``(A, qB, Scale[, Bias])`` with qB (N, K/2) 4-bit indices into the NF4
+    table and Scale (N, K/group) the per-block absmax. The reference benchmarks the format
+    (W_NF4 A_FP16 in its dequantize_gemm chart) but ships no decoder; ``ops.pack_lut4`` takes any
+    16-entry table."""
+    g = K if group_size in (None, -1, 0) else group_size
+    params = [Param("A", (M, K), in_t), Param("B", (N, K // 2), torch.uint8), Param("Scale", (N, K // g), in_t)]
+    if with_bias:
+        params.append(Param("Bias", (M, N), out_t))
+    params.append(Param("C", (N, M) if trans_c else (M, N), out_t))
+
+    def pack_fn(qB, scale):
+        return ops.pack_lut4(qB.view(torch.uint8), scale, N, K, g, in_t)
+
+    def impl(kernel: DequantKernel, A, qB, scale, *rest):
+        _check(A, params[0])
+        _check(qB, params[1], any_int8=True)
+        return ops.gemm(A, kernel._packed(qB, scale), out_dtype=out_t, bias=rest[0] if with_bias else None,
+                        trans_c=trans_c)
+
+    return DequantKernel("matmul", params, [-1], impl, pack_fn, f"b200dq umma_dequant_gemm: M={M} N={N} K={K} nf4 group={g}")
 
 
 def _matmul_low_bits(M, N, K, in_t, out_t, acc_t, num_bits, group_size, with_scaling, with_zeros, zeros_mode,

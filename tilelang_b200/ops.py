@@ -16,7 +16,7 @@ import torch
 
 from . import _lib
 from ._lib import (ACT_BF16, ACT_F16, ACT_I8, GF_FP4_SIMPLE, GF_HAS_BIAS, GF_ROW_SCALE, GF_TRANS_C, OUT_BF16, OUT_F16,
-                   OUT_F32, OUT_I32, WF_FP4_E8M0, WF_I2_I8, WF_I4_I8, WF_S4_RAW, WF_U2_SZ, WF_U4_RAW, WF_U4_SZ)
+                   OUT_F32, OUT_I32, WF_FP4_E8M0, WF_I2_I8, WF_I4_I8, WF_LUT4_S, WF_S4_RAW, WF_U2_SZ, WF_U4_RAW, WF_U4_SZ)
 
 _ACT_OF = {torch.float16: ACT_F16, torch.bfloat16: ACT_BF16, torch.int8: ACT_I8}
 _OUT_OF = {torch.float16: OUT_F16, torch.bfloat16: OUT_BF16, torch.float32: OUT_F32, torch.int32: OUT_I32}
@@ -197,6 +197,36 @@ def pack_w2a16(qweight: torch.Tensor, scales: Optional[torch.Tensor], zeros: Opt
     return PackedWeight(wp, N, K, WF_U2_SZ, act, group_size=group_size)
 
 
+# The 16 levels of NF4 (quantiles of a standard normal, normalised to [-1, 1]; Dettmers et al.,
+# "QLoRA", 2023, appendix E), index 0..15.
+NF4_TABLE = (-1.0, -0.6961928009986877, -0.5250730514526367, -0.39491748809814453, -0.28444138169288635,
+             -0.18477343022823334, -0.09105003625154495, 0.0, 0.07958029955625534, 0.16093020141124725,
+             0.24611230194568634, 0.33791524171829224, 0.44070982933044434, 0.5626170039176941,
+             0.7229568362236023, 1.0)
+
+
+def pack_lut4(qweight: torch.Tensor, scales: torch.Tensor, N: int, K: int, group_size: int, dtype: torch.dtype,
+              table=NF4_TABLE) -> PackedWeight:
+    """4-bit codes (N, K/2), even k in the low nibble, that index a 16-entry ``table``:
+    weight = ``table[q] * scale[n, k // group_size]`` (NF4 by default; any 4-bit codebook).
+    ``scales`` (N, K/group) in ``dtype`` (the per-block absmax of an NF4 checkpoint)."""
+    if dtype not in (torch.float16, torch.bfloat16):
+        raise TypeError("16-bit activations only")
+    if len(table) != 16:
+        raise ValueError("the table has 16 entries")
+    if group_size in (-1, 0, None):
+        group_size = K
+    groups = K // group_size
+    _check_cuda_contig("scales", scales, qweight.device)
+    if scales.dtype != dtype or tuple(scales.shape) != (N, groups):
+        raise ValueError(f"scales must be {dtype} of shape {(N, groups)}")
+    act = _ACT_OF[dtype]
+    wp = _pack(qweight, scales, None, N, K, 4, group_size, WF_LUT4_S, act)
+    out = PackedWeight(wp, N, K, WF_LUT4_S, act, group_size=group_size)
+    out.code_table = tuple(float(v) for v in table)
+    return out
+
+
 def pack_mxfp4(qweight: torch.Tensor, scale_bytes: Optional[torch.Tensor], N: int, K: int, exp_bias: int = 127,
                fp4_format: str = "e2m1", dtype: torch.dtype = torch.bfloat16) -> PackedWeight:
     """fp4 codes (N, K/2) (even k in the low nibble) + one exponent byte per 32 K.
@@ -307,6 +337,10 @@ def gemm(A: torch.Tensor, w: PackedWeight, out: Optional[torch.Tensor] = None,
         M=M, N=w.N, K=w.K, group_size=w.group_size, weight_format=w.weight_format, act_type=w.act_type,
         out_type=_OUT_OF[out.dtype], flags=flags, tensor_scale=float(tensor_scale), code_bias=w.code_bias,
         fp4_exp_bias=w.fp4_exp_bias, token_tile=token_tile, max_ctas=max_ctas)
+    table = getattr(w, "code_table", None)
+    if table is not None:
+        for i, v in enumerate(table):
+            args.code_table[i] = v
     if peer_outs:
         if len(peer_outs) > 7:
             raise ValueError("at most seven peer outputs")
