@@ -172,6 +172,15 @@ __device__ __forceinline__ void skinny_store(const GemmParams& p, const Segment&
   }
 }
 
+constexpr int kSkinnyFastParts = 4;   // partial sums of a cut tile the finishing CTA holds in registers
+
+// The CTAs that share a tile: the first one and how many.
+__device__ __forceinline__ void skinny_cut_plan(const GemmParams& p, long long tile, int& c_first, int& nc) {
+  const long long t_begin = tile * p.st_total;
+  c_first = static_cast<int>(t_begin / p.span);
+  nc = static_cast<int>((t_begin + p.st_total - 1) / p.span) - c_first + 1;
+}
+
 // Adds every CTA's published partial sums of a cut tile in ascending CTA order and stores the
 // outputs (all consumer threads; the sums come from L2).
 template <int kTok>
@@ -302,6 +311,25 @@ skinny_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const Gem
 #pragma unroll
           for (int c = 0; c < 4; ++c) acc[mt][nt][c] = 0.f;
 
+      // A tile cut between CTAs is the sum of the CTAs' partial sums in ascending CTA order
+      // (the same order in every launch: deterministic). The CTA that holds the tile's first
+      // stages works on them at the END of its span, the others at the START of theirs, so
+      // their sums are published before it even begins: thread 0 looks at the tile's counter
+      // now (only its own warp waits for the answer) and leaves the verdict for the segment's end.
+      // (No thread can still be reading the flag: thread 0 has passed the previous segment's
+      // second barrier, which every thread reaches after its read.)
+      if (w.slot >= 0 && threadIdx.x == 0) {
+        int c_first, nc;
+        skinny_cut_plan(p, w.tile, c_first, nc);
+        bool done = false;
+        if (static_cast<int>(blockIdx.x) == c_first && nc <= kSkinnyFastParts) {
+          const unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(p.tile_ctr + w.tile);
+          done = seen == ((p.epoch << 8) | static_cast<unsigned long long>(nc - 1));
+          if (done) __threadfence();   // order the look at the counter before the CTA's reads of the sums
+        }
+        ctl->others_done = done ? 1 : 0;
+      }
+
       const uint32_t nst = static_cast<uint32_t>(w.st_end - w.st_begin);
       for (; my_cnt < cnt0 + nst; my_cnt += kSkinnyTeams) {
         ok &= skinny_wait(&ctl->full[slot], phase, abort_flag, st_word, 13, lane);
@@ -353,33 +381,23 @@ skinny_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const Gem
       }
       cnt0 += nst;
 
-      // ---- add the teams' partial sums of every output in a fixed order
-      // A tile cut between CTAs is the sum of the CTAs' partial sums in ascending CTA order
-      // (the same order in every launch: deterministic). The CTA that holds the tile's first
-      // stages works on them at the END of its span, the others at the START of theirs, so it
-      // almost always finds their sums published already: it then adds them to its own straight
-      // from L2 and stores the outputs, with nothing of its own written to scratch and no wait.
-      // Otherwise every contributor publishes its sums, counts itself in, and whoever counts
-      // last adds them all.
+      // ---- add the teams' partial sums of every output in a fixed order. If the other CTAs'
+      // sums of a cut tile were published when this segment began, they are added to this CTA's
+      // own straight from L2 and the outputs are stored, with nothing of its own written to
+      // scratch and no wait. Otherwise every contributor publishes its sums, counts itself in,
+      // and whoever counts last adds them all.
       constexpr int kOuts = kTok * kTileRows / kSkinnyConsumers;     // outputs per thread
-      constexpr int kFast = 4;                                       // contributions held in registers
+      constexpr int kFast = kSkinnyFastParts;
       const bool cut = w.slot >= 0;
       const long long t_begin = w.tile * p.st_total;
-      const int c_first = static_cast<int>(t_begin / p.span);
-      const int c_last = static_cast<int>((t_begin + p.st_total - 1) / p.span);
-      const int nc = c_last - c_first + 1;
+      int c_first, nc;
+      skinny_cut_plan(p, w.tile, c_first, nc);
       // slot 0 if the tile holds the first segment of that CTA's span, else slot 1
       auto slot_of = [&](int cta) { return cta * 2 + ((static_cast<long long>(cta) * p.span >= t_begin) ? 0 : 1); };
-      if (cut && threadIdx.x == 0) {
-        const unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(p.tile_ctr + w.tile);
-        ctl->others_done = (static_cast<int>(blockIdx.x) == c_first && nc <= kFast &&
-                            seen == ((p.epoch << 8) | static_cast<unsigned long long>(nc - 1))) ? 1 : 0;
-      }
-      skinny_consumer_sync();   // the previous segment's readers are done with the buffer; the flag is set
+      skinny_consumer_sync();   // the previous segment's readers are done with the buffer
       const bool others_done = cut && ctl->others_done != 0;
       uint32_t raw[kOuts][kFast];
       if (others_done) {
-        __threadfence();
 #pragma unroll
         for (int jj = 1; jj < kFast; ++jj) {
           if (jj < nc) {
