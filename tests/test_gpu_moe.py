@@ -47,6 +47,37 @@ def test_grouped_w4a16_matches_per_group_oracle(counts, N, K, tile):
         start += c
 
 
+def test_many_one_row_groups_in_a_fresh_process():
+    """Eight groups of one row each round up to eight token tiles: the grouped schedule plans more
+    CTAs (and more scratch) than a dense call with the same eight rows would. Run in a fresh
+    process so that no earlier call has grown the cached workspace; host and device counts."""
+    import os
+    import subprocess
+    import sys
+    code = """
+import torch
+from tilelang_b200 import ops
+from oracle import ref_programs as R
+E, N, K, group = 8, 256, 2048, 128
+g = torch.Generator().manual_seed(3)
+q = torch.randint(0, 256, (E, N, K // 2), generator=g, dtype=torch.uint8)
+s = (torch.rand(E, N, K // group, generator=g) * 0.015 + 0.005).to(torch.bfloat16)
+packed = ops.stack_packed([ops.pack_w4a16(q[e].cuda(), s[e].cuda(), None, N, K, group, torch.bfloat16) for e in range(E)])
+A = torch.randn(E, K, generator=g).to(torch.bfloat16)
+for counts in ([1] * E, torch.ones(E, dtype=torch.int64, device="cuda")):
+    out = ops.gemm_grouped(A.cuda(), packed, counts, token_tile=256).cpu()
+    ops.check_status(torch.device("cuda", 0))
+    for e in range(E):
+        ref = R.ref_w4a16(A[e:e + 1], q[e], s[e], None, group, torch.bfloat16)
+        assert R.max_rel_error(out[e:e + 1], ref) <= 1e-2, e
+print("GROUPS_OK")
+"""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600, cwd=root,
+                         env=dict(os.environ, PYTHONPATH=root))
+    assert res.returncode == 0 and "GROUPS_OK" in res.stdout, res.stdout[-1500:] + res.stderr[-3000:]
+
+
 def test_silu_mul_matches_fp32_reference():
     h = torch.randn(77, 2 * 1408, generator=gen(1)).to(torch.bfloat16)
     out = ops.silu_mul(h.to(DEV)).cpu()
