@@ -140,18 +140,6 @@ __device__ __forceinline__ void skinny_decode(const GemmParams& p, const uint4& 
                                (p.flags & GF_FP4_SIMPLE) != 0, out);
 }
 
-// Registers one more finished partial sum of a cut tile; true for the CTA that brings the last
-// of `expected`. The counter word carries the launch's epoch, a stale word counts as zero.
-__device__ __forceinline__ bool skinny_tile_arrive(unsigned long long* ctr, unsigned long long epoch, int expected) {
-  unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(ctr);
-  while (true) {
-    const unsigned long long want = ((old >> 8) == epoch) ? old + 1ull : ((epoch << 8) | 1ull);
-    const unsigned long long prev = atomicCAS(ctr, old, want);
-    if (prev == old) return static_cast<int>(want & 0xffull) == expected;
-    old = prev;
-  }
-}
-
 // One summed output of a segment: a raw partial into the CTA's scratch slot, or the
 // finished value into C.
 __device__ __forceinline__ void skinny_store(const GemmParams& p, const Segment& w, int tok, int row, float v) {
@@ -447,14 +435,14 @@ skinny_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const Gem
           // CTA turn out to be the last all the same, it finishes the tile when its span is done.
           if (threadIdx.x == 0) {
             __threadfence();
-            if (skinny_tile_arrive(p.tile_ctr + w.tile, p.epoch, nc)) {
+            if (tile_arrive(p.tile_ctr + w.tile, p.epoch, nc)) {
               if (pending0 < 0) pending0 = w.tile; else pending1 = w.tile;
             }
           }
         } else {
           if (threadIdx.x == 0) {
             __threadfence();
-            ctl->finish_tile = skinny_tile_arrive(p.tile_ctr + w.tile, p.epoch, nc) ? 1 : 0;
+            ctl->finish_tile = tile_arrive(p.tile_ctr + w.tile, p.epoch, nc) ? 1 : 0;
           }
           skinny_consumer_sync();
           if (ctl->finish_tile == 1) skinny_finish_tile<kTok>(p, w.tile);

@@ -189,6 +189,7 @@ struct SharedCtl {
   uint64_t turn[2];   // the two issuers hand the shared accumulator back and forth
   uint32_t tmem_base;
   int abort_flag;
+  int others_done[2];   // epilogue: the other CTA's sums of this segment's cut tile are already published
 };
 static_assert(sizeof(SharedCtl) <= 1024, "control block must fit its slot");
 
@@ -235,6 +236,27 @@ __device__ __forceinline__ void plan_of(const GemmParams& p, long long& units, l
     units = p.units;
     span = p.span;
   }
+}
+
+// Registers one more published partial tile of a cut tile; true for the CTA that brings the last of
+// `expected`. The counter word carries the launch's epoch, a stale word counts as zero.
+__device__ __forceinline__ bool tile_arrive(unsigned long long* ctr, unsigned long long epoch, int expected) {
+  unsigned long long old = *reinterpret_cast<volatile unsigned long long*>(ctr);
+  while (true) {
+    const unsigned long long want = ((old >> 8) == epoch) ? old + 1ull : ((epoch << 8) | 1ull);
+    const unsigned long long prev = atomicCAS(ctr, old, want);
+    if (prev == old) return static_cast<int>(want & 0xffull) == expected;
+    old = prev;
+  }
+}
+
+// The CTAs that share a tile: the first one and how many.
+__device__ __forceinline__ void cut_plan(const GemmParams& p, long long tile, int& c_first, int& nc, long long& span) {
+  long long units;
+  plan_of(p, units, span);
+  const long long t_begin = tile * p.st_total;
+  c_first = static_cast<int>(t_begin / span);
+  nc = static_cast<int>((t_begin + p.st_total - 1) / span) - c_first + 1;
 }
 
 // Walks the segments of this CTA's span; every warp role runs the same walk.
@@ -666,9 +688,41 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
       (void)nkb;
       ok &= mbar_wait(&ctl->acc_full, tc & 1, abort_flag, st, 8);
       tc_fence_after_sync();
+      // A tile cut between two CTAs: the one that holds its first stages works on them at the end
+      // of its span, the other at the start of its own, so the other's partial tile is almost
+      // always published by now. Then this CTA adds it to its accumulator on the way out and
+      // stores the finished outputs (the fix-up pass skips the tile); otherwise it publishes its
+      // own partial tile as every contributor does, and the fix-up pass adds them.
+      // (Only at the 256-token tile: with two accumulators per tile the extra registers spill and
+      // the narrow tiles' short epilogues do not hide the L2 reads -- measured slower there.)
+      constexpr bool kFinishInKernel = (TN == 256);
+      const bool cut = w.slot >= 0;
+      bool finish_here = false;
+      const uint32_t* other = nullptr;
+      int nc_e = 1;
+      if (kFinishInKernel && cut && p.tile_ctr != nullptr) {
+        int c_first;
+        long long span;
+        cut_plan(p, w.tile, c_first, nc_e, span);
+        if (warp == 12 && lane == 0) {
+          bool done = false;
+          if (static_cast<int>(blockIdx.x) == c_first && nc_e == 2) {
+            const unsigned long long seen = *reinterpret_cast<volatile unsigned long long*>(p.tile_ctr + w.tile);
+            done = seen == ((p.epoch << 8) | 1ull);
+            if (done) __threadfence();
+          }
+          ctl->others_done[tc & 1] = done ? 1 : 0;
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");     // the four epilogue warps
+        finish_here = ctl->others_done[tc & 1] != 0;
+        if (finish_here) {
+          // the other contributor is CTA c_first + 1, and the tile holds the first segment of its span
+          other = p.partial + static_cast<size_t>((c_first + 1) * 2) * TN * kTileRows + row_in_tile;
+        }
+      }
       auto store_chunk = [&](const uint32_t (&acc)[NV], int c) {
         const int m0 = w.row0 + c * NV;
-        if (w.slot >= 0) {
+        if (cut && !finish_here) {
           // partial tile: raw accumulator values, [token][row] so lanes coalesce
           uint32_t* dst = p.partial + (static_cast<size_t>(w.slot) * TN + c * NV) * kTileRows + row_in_tile;
 #pragma unroll
@@ -698,7 +752,50 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
         __syncwarp();
         if (lane == 0) mbar_arrive(&ctl->acc_empty);
       };
-      if constexpr (NI == 1 && NV == 32 && (TN / NV) % 2 == 0) {
+      if (kFinishInKernel && finish_here) {
+        // own sums from tensor memory plus the other CTA's from L2 (requested one chunk ahead),
+        // added in ascending CTA order like the fix-up pass: own first
+        uint32_t oth[NV];
+#pragma unroll
+        for (int j = 0; j < NV; ++j) oth[j] = __ldcg(other + static_cast<size_t>(j) * kTileRows);
+#pragma unroll 1
+        for (int c = 0; c < TN / NV; ++c) {
+          uint32_t acc[NV];
+          bool have = false;
+#pragma unroll
+          for (int i = 0; i < NI; ++i) {
+            if (!(valid & (1u << i))) continue;
+            uint32_t part[NV];
+            if constexpr (NV == 32) tmem_ld_32x32b_x32(tmem_base + lane_addr + i * TN + c * NV, part);
+            else tmem_ld_32x32b_x16(tmem_base + lane_addr + i * TN + c * NV, part);
+            tc_wait_ld();
+            if (!have) {
+#pragma unroll
+              for (int j = 0; j < NV; ++j) acc[j] = part[j];
+              have = true;
+            } else {
+#pragma unroll
+              for (int j = 0; j < NV; ++j) {
+                if constexpr (kInt) acc[j] = static_cast<uint32_t>(static_cast<int>(acc[j]) + static_cast<int>(part[j]));
+                else acc[j] = __float_as_uint(__uint_as_float(acc[j]) + __uint_as_float(part[j]));
+              }
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < NV; ++j) {
+            if constexpr (kInt) acc[j] = static_cast<uint32_t>(static_cast<int>(acc[j]) + static_cast<int>(oth[j]));
+            else acc[j] = __float_as_uint((0.f + __uint_as_float(acc[j])) + __uint_as_float(oth[j]));
+          }
+          if (c + 1 < TN / NV) {
+#pragma unroll
+            for (int j = 0; j < NV; ++j)
+              oth[j] = __ldcg(other + (static_cast<size_t>(c + 1) * NV + j) * kTileRows);
+          } else {
+            release_acc();
+          }
+          store_chunk(acc, c);
+        }
+      } else if constexpr (NI == 1 && NV == 32 && (TN / NV) % 2 == 0) {
         // one accumulator, an even number of 32-column chunks: the load of the next chunk
         // flies under the stores of the current one (two register buffers, loop unrolled by 2)
         uint32_t buf_a[NV], buf_b[NV];
@@ -739,6 +836,14 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
           }
           if (c == TN / NV - 1) release_acc();
           store_chunk(acc, c);
+        }
+      }
+      if (kFinishInKernel && cut && !finish_here && p.tile_ctr != nullptr) {
+        // this CTA's partial tile is stored: make it visible device-wide and count it (nobody waits)
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (warp == 12 && lane == 0) {
+          __threadfence();
+          tile_arrive(p.tile_ctr + w.tile, p.epoch, nc_e);
         }
       }
       ++tc;
@@ -783,6 +888,12 @@ streamk_fixup_kernel(const GemmParams p) {
   const int c_first = static_cast<int>(t_begin / span);
   if (static_cast<int>(blockIdx.x) != c_first) return;      // an earlier cut owns this tile
   const int c_last = static_cast<int>((t_end - 1) / span);
+  if (TN == 256 && p.tile_ctr != nullptr && c_last - c_first == 1) {
+    // one arrival out of two: the CTA holding the tile's first stages added the other's partial
+    // tile itself and stored the outputs
+    const unsigned long long seen = p.tile_ctr[tile];
+    if (seen == ((p.epoch << 8) | 1ull)) return;
+  }
   Segment seg;
   locate_tile(p, tile, seg);
   const int row = threadIdx.x;
