@@ -233,10 +233,10 @@ def workload_config(M, gpus, allgather):
 
 # DRAM traffic of the dominant kernel per launch, from one ncu --set full capture of this
 # command at the given M (dram__bytes_read.sum + dram__bytes_write.sum): M = 4096
-# 658,700,800 + 243,296,768 (algorithmic 426,770,432); M = 16 125,729,280 + 4,781,056 and
+# 664,374,784 + 244,163,584 (algorithmic 426,770,432); M = 16 125,729,280 + 4,781,056 and
 # M = 1 124,979,200 + 4,661,760 (algorithmic 125,960,192 / 125,656,066: the weight is read once,
 # the writes are stream-K partial tiles).
-TRAFFIC = {4096: 901997568, 16: 130510336, 1: 129640960}
+TRAFFIC = {4096: 908538368, 16: 130510336, 1: 129640960}
 
 
 def load_traffic_note(M):
