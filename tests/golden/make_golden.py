@@ -1,8 +1,7 @@
 """Generates the golden fixtures in this folder from the reference's own helpers.
 
-Runs only where the reference checkout is mounted (default /root/reference, or
-``REFERENCE_ROOT``); the tests read the committed ``.npz`` files and never the
-reference. Modules are loaded by file path because the example package's
+Runs only where a checkout of the reference is at hand (``REFERENCE_ROOT`` names it); the
+tests read the committed ``.npz`` files and never the reference. Modules are loaded by file path because the example package's
 ``__init__`` needs a full TileLang build:
   examples/dequantize_gemm/dequantize_utils.py  (torch_convert, torch_convert_bit_twiddling)
   examples/dequantize_gemm/quantize/utils.py    (general_compress, interleave_weight, gen_quant4)
@@ -11,7 +10,7 @@ reference. Modules are loaded by file path because the example package's
   examples/deepseek_v4/act_quant.py             (fp4_act_quant_ref, the bf16 -> MXFP4 quantiser)
   examples/deepseek_v4/fp8_fp4_gemm_1d1d_sm100.py (quantize_mxfp4_with_packed_ue8m0, group-major words)
 
-    python tests/golden/make_golden.py
+    REFERENCE_ROOT=<reference checkout> python tests/golden/make_golden.py
 """
 import importlib.util
 import os
@@ -20,7 +19,9 @@ import sys
 import numpy as np
 import torch
 
-REF = os.environ.get("REFERENCE_ROOT", "/root/reference")
+REF = os.environ.get("REFERENCE_ROOT")
+if not REF or not os.path.isdir(REF):
+    sys.exit("set REFERENCE_ROOT to a checkout of the reference")
 HERE = os.path.dirname(os.path.abspath(__file__))
 
 
