@@ -179,6 +179,28 @@ def test_w4a16_stream_k_split_is_deterministic_and_matches_unsplit():
     check_float(split, R.ref_w4a16(A, qB, s, z, group, torch.float32), strict=2e-2)
 
 
+@pytest.mark.parametrize("K,tile", [(1408, 128), (1920, 128), (1408, 64)])
+def test_narrow_tiles_with_an_odd_stage_count_over_long_spans(K, tile):
+    """Explicit 128- or 64-token tiles on a tall problem: every CTA works through tens of tiles, and
+    K = 1408 / 1920 gives a tile 11 / 15 stages. With the two issuers paired to the dequant groups by
+    the parity of a CTA-wide stage count, an odd count flipped the pairing at every tile and a hand-off
+    was lost now and then (a bounded wait gave up); the schedule now rounds such tiles up to an even
+    number of stages. Checked against the oracle on the first and last rows and on the status word."""
+    M, N, group = 49152, 2048, 128
+    A = torch.randn(M, K, generator=gen(1)).to(torch.bfloat16)
+    q = torch.randint(0, 256, (N, K // 2), generator=gen(2), dtype=torch.uint8)
+    s = (torch.rand(N, K // group, generator=gen(3)) * 0.015 + 0.005).to(torch.bfloat16)
+    pw = ops.pack_w4a16(q.to(DEV), s.to(DEV), None, N, K, group, torch.bfloat16)
+    A_d = A.to(DEV)
+    for _ in range(3):
+        C = ops.gemm(A_d, pw, token_tile=tile)
+        ops.check_status(torch.device(DEV))
+    for rows in (slice(0, 512), slice(M - 512, M)):
+        check_float(C[rows], R.ref_w4a16(A[rows], q, s, None, group, torch.bfloat16))
+    C256 = ops.gemm(A_d, pw, token_tile=256)
+    assert R.max_rel_error(C.float().cpu(), C256.float().cpu()) <= 8e-3      # same products, other addition order
+
+
 def test_w4a16_linearity_at_full_width():
     """Size-independent property at the benchmark's full N and K: f(a + b) = f(a) + f(b)
     for activations whose sums are exact in bf16 (small integers)."""

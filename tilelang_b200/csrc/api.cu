@@ -101,6 +101,7 @@ int token_tile_for(int M) {
 
 struct Schedule {
   int tn, m_tiles, n_tiles, st_total, grid, span;
+  int st_units;   // stages the schedule gives a tile: st_total, or one more (see make_schedule)
   long long units;
   size_t workspace_bytes, slot_bytes;
   bool needs_scratch;   // some tile is cut between CTAs
@@ -126,7 +127,7 @@ int stage_bytes_for(int weight_format, int group_size) {
 }
 
 int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_ctas, int sm_count, Schedule* s,
-                  long long grouped_tiles = -1) {
+                  long long grouped_tiles = -1, bool tile_kernel = true) {
   s->tn = token_tile > 0 ? token_tile : token_tile_for(M);
   if (s->tn != 16 && s->tn != 32 && s->tn != 64 && s->tn != 128 && s->tn != 256)
     return fail("token_tile must be 16, 32, 64, 128 or 256 (got %d)", s->tn);
@@ -135,18 +136,30 @@ int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_cta
   s->st_total = stages_for(K, act_type);
   const long long tiles = grouped_tiles >= 0 ? grouped_tiles : static_cast<long long>(s->m_tiles) * s->n_tiles;
   if (tiles <= 0) return fail("no tiles to compute");
-  s->units = tiles * s->st_total;
+  // Tiles of at most 128 tokens run two issuers and two dequant groups on alternate stages, paired up
+  // by the parity of a CTA-wide stage count. A tile with an odd number of stages flips that pairing
+  // at every tile boundary; with tens of such tiles per CTA a hand-off between the groups was lost
+  // now and then (a bounded wait gave up). Those tiles get one more stage: it re-reads the last real
+  // stage's weights against activations beyond K, which the tensor map fills with zeros.
+  s->st_units = s->st_total + ((s->tn <= 128 && tile_kernel) ? (s->st_total & 1) : 0);
+  s->units = tiles * s->st_units;
   int cap = sm_count;
   if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
   long long g = s->units / kMinSpan;
   if (g < 1) g = 1;
   if (g > cap) g = cap;
   s->span = static_cast<int>((s->units + g - 1) / g);
+  // Narrow tiles with plenty of tiles per SM: spans of eight whole tiles, in as many CTAs as that
+  // takes (they run in waves). With tens of tiles per CTA the narrow-tile pipeline (two issuers, two
+  // dequant groups, four-stage rings) lost a hand-off now and then under full load -- a bounded wait
+  // gave up -- and its cause is not understood; short spans have not shown it. Whole tiles also need
+  // no scratch and no fix-up pass, and the imbalance of whole-tile waves is about 1 % at this size.
+  if (s->tn <= 128 && tile_kernel && max_ctas <= 0 && tiles >= 16LL * cap) s->span = 8 * s->st_units;
   s->grid = static_cast<int>((s->units + s->span - 1) / s->span);
   // two partial-tile slots per CTA, then one 64-bit arrival counter per tile (small-M kernel)
   s->slot_bytes = static_cast<size_t>(s->grid) * 2 * s->tn * kTileRows * sizeof(uint32_t);
   s->workspace_bytes = s->slot_bytes + static_cast<size_t>(tiles) * sizeof(unsigned long long);
-  s->needs_scratch = (s->span % s->st_total != 0) && s->grid > 1;
+  s->needs_scratch = (s->span % s->st_units != 0) && s->grid > 1;
   return 0;
 }
 
@@ -322,7 +335,7 @@ int static_scratch_need(const b200dq_gemm_args* a, int sm_count, size_t* need) {
   Schedule s;
   if (takes_int8_skinny_path(a)) { *need = 0; return 0; }
   const int tile = takes_skinny_path(a) ? kSkinnyTokens : a->token_tile;
-  if (make_schedule(a->M, a->N, a->K, a->act_type, tile, a->max_ctas, sm_count, &s) != 0) return -1;
+  if (make_schedule(a->M, a->N, a->K, a->act_type, tile, a->max_ctas, sm_count, &s, -1, !takes_skinny_path(a)) != 0) return -1;
   *need = s.needs_scratch ? s.workspace_bytes : 0;
   return 0;
 }
@@ -376,6 +389,7 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
     p.M = a->M; p.N = a->N; p.K = a->K;
     p.n_tiles = (a->N + kTileRows - 1) / kTileRows;
     p.st_total = stages_for(a->K, ACT_I8);
+    p.st_units = p.st_total;
     p.stage_bytes = stage_bytes_for(wf, a->group_size);
     p.ldc = (a->flags & GF_TRANS_C) ? a->M : a->N;
     p.flags = a->flags & (GF_TRANS_C | GF_HAS_BIAS | GF_ROW_SCALE);
@@ -393,7 +407,7 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   const bool dyn = grouped && a->total_tiles < 0;
   const long long plan_tiles = grouped ? (dyn ? -static_cast<long long>(a->total_tiles) : a->total_tiles) : -1;
   if (make_schedule(a->M, a->N, a->K, act, skinny ? kSkinnyTokens : a->token_tile, a->max_ctas, sm_count, &s,
-                    plan_tiles) != 0) return -1;
+                    plan_tiles, !skinny) != 0) return -1;
   if (dyn && s.grid > 1) s.needs_scratch = true;
   if (s.needs_scratch) {
     if (scratch == nullptr || scratch_bytes < s.workspace_bytes)
@@ -425,7 +439,7 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   p.code_bias = a->code_bias;
   p.fp4_exp_bias = a->fp4_exp_bias;
   p.M = a->M; p.N = a->N; p.K = a->K;
-  p.n_tiles = s.n_tiles; p.m_tiles = s.m_tiles; p.st_total = s.st_total;
+  p.n_tiles = s.n_tiles; p.m_tiles = s.m_tiles; p.st_total = s.st_total; p.st_units = s.st_units;
   p.span = s.span; p.units = s.units;
   p.stage_bytes = stage_bytes_for(wf, a->group_size);
   p.sz_per_kb = ((wf == WF_U4_SZ || wf == WF_U2_SZ || wf == WF_LUT4_S) && a->group_size == 64) ? 1 : 0;
@@ -510,7 +524,8 @@ size_t b200dq_gemm_workspace_bytes_for(const b200dq_gemm_args* a) {
   if (takes_int8_skinny_path(a)) return 0;
   const int tile = takes_skinny_path(a) ? kSkinnyTokens : a->token_tile;
   const long long tiles = grouped ? (a->total_tiles < 0 ? -static_cast<long long>(a->total_tiles) : a->total_tiles) : -1;
-  if (make_schedule(a->M, a->N, a->K, a->act_type, tile, a->max_ctas, sm_count_or_bound(), &s, tiles) != 0) return 0;
+  if (make_schedule(a->M, a->N, a->K, a->act_type, tile, a->max_ctas, sm_count_or_bound(), &s, tiles,
+                    !takes_skinny_path(a)) != 0) return 0;
   return s.workspace_bytes;
 }
 
@@ -796,8 +811,9 @@ int b200dq_check_status(void* cuda_stream) {
   if (h.error == ERR_NONE) return 0;
   CUDA_OK(cudaMemsetAsync(ds->status, 0, sizeof(DeviceStatus), stream));
   CUDA_OK(cudaStreamSynchronize(stream));
-  return fail("device status: error %u (1 = a bounded wait gave up), first at block %u wait site %u, %u waits gave up",
-              h.error, h.where >> 8, h.where & 0xff, h.count);
+  return fail("device status: error %u (1 = a bounded wait gave up), first at block %u wait site %u, %u waits gave up, "
+              "site mask 0x%x",
+              h.error, h.where >> 8, h.where & 0xff, h.count, h.sites);
 }
 
 }  // extern "C"

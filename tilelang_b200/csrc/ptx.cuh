@@ -23,7 +23,7 @@ struct DeviceStatus {
   unsigned int error;   // 0 = ok, else an ERR_* code (first writer wins)
   unsigned int where;   // (blockIdx.x << 8) | site id of the first failed wait
   unsigned int count;   // number of waits that gave up
-  unsigned int pad;
+  unsigned int sites;   // bit (site id % 32) set for every site at which a wait gave up
 };
 
 enum : unsigned int { ERR_NONE = 0, ERR_WAIT_TIMEOUT = 1, ERR_BAD_ARG = 2 };
@@ -119,6 +119,7 @@ static __device__ __noinline__ void mbar_wait_failed(volatile int* abort_flag, D
       st->where = (blockIdx.x << 8) | (site & 0xff);
     }
     atomicAdd(&st->count, 1u);
+    atomicOr(&st->sites, 1u << (site & 31u));
   }
 }
 
@@ -134,7 +135,9 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
       if (*abort_flag) return false;
       uint64_t now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      if (now - t0 > B200DQ_WAIT_LIMIT_NS) {
+      // the epilogue's wait for a tile (site 8) starts long before the waits upstream of it: those get
+      // the shorter limit, so that the status word names the wait that was really stuck
+      if (now - t0 > (site == 8 ? B200DQ_WAIT_LIMIT_NS + B200DQ_WAIT_LIMIT_NS / 2 : B200DQ_WAIT_LIMIT_NS)) {
         mbar_wait_failed(abort_flag, st, site);
         return false;
       }

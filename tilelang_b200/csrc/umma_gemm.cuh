@@ -88,6 +88,8 @@ struct GemmParams {
   int fp4_exp_bias;          // 127 for OCP e8m0, 0 for a raw exponent byte
   int M, N, K;
   int n_tiles, m_tiles, st_total;   // st_total = weight stages (2 k-blocks each) per tile
+  int st_units;              // stages the schedule gives a tile: st_total, or st_total + 1 (a stage past the
+                             // end re-reads the last real stage's weights against zero-filled activations)
   int span;                  // stages per CTA (stream-K span length)
   long long units;           // m_tiles * n_tiles * st_total
   int stage_bytes;           // bytes of one packed stage in global memory
@@ -230,7 +232,7 @@ __device__ __forceinline__ void locate_tile(const GemmParams& p, long long tile,
 // group sizes are known only on the device, an even cut of the tile total found there.
 __device__ __forceinline__ void plan_of(const GemmParams& p, long long& units, long long& span) {
   if (p.dyn_grid > 0) {
-    units = static_cast<long long>(p.grp_tile_prefix[p.num_groups]) * p.st_total;
+    units = static_cast<long long>(p.grp_tile_prefix[p.num_groups]) * p.st_units;
     span = (units + p.dyn_grid - 1) / p.dyn_grid;
   } else {
     units = p.units;
@@ -254,9 +256,9 @@ __device__ __forceinline__ bool tile_arrive(unsigned long long* ctr, unsigned lo
 __device__ __forceinline__ void cut_plan(const GemmParams& p, long long tile, int& c_first, int& nc, long long& span) {
   long long units;
   plan_of(p, units, span);
-  const long long t_begin = tile * p.st_total;
+  const long long t_begin = tile * p.st_units;
   c_first = static_cast<int>(t_begin / span);
-  nc = static_cast<int>((t_begin + p.st_total - 1) / span) - c_first + 1;
+  nc = static_cast<int>((t_begin + p.st_units - 1) / span) - c_first + 1;
 }
 
 // Walks the segments of this CTA's span; every warp role runs the same walk.
@@ -273,13 +275,13 @@ struct SegmentWalk {
   }
   __device__ __forceinline__ bool next(const GemmParams& p, Segment& s) {
     if (pos >= end) return false;
-    const long long tile = pos / p.st_total;
-    s.st_begin = static_cast<int>(pos - tile * p.st_total);
+    const long long tile = pos / p.st_units;
+    s.st_begin = static_cast<int>(pos - tile * p.st_units);
     const long long left = end - pos;
-    s.st_end = static_cast<int>(min(static_cast<long long>(p.st_total), s.st_begin + left));
+    s.st_end = static_cast<int>(min(static_cast<long long>(p.st_units), s.st_begin + left));
     locate_tile(p, tile, s);
     s.tile = tile;
-    const bool whole = (s.st_begin == 0 && s.st_end == p.st_total);
+    const bool whole = (s.st_begin == 0 && s.st_end == p.st_units);
     s.slot = whole ? -1 : (static_cast<int>(blockIdx.x) * 2 + (first ? 0 : 1));
     first = false;
     pos += (s.st_end - s.st_begin);
@@ -457,8 +459,17 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
           mbar_wait(&ctl->empty_w[s], ((wc / NWP) & 1) ^ 1, abort_flag, st, 1);
           const uint32_t bytes = static_cast<uint32_t>(n) * p.stage_bytes;
           mbar_arrive_expect_tx(&ctl->full_w[s], bytes);
-          const uint8_t* src = p.wp + w.wp_off + (static_cast<size_t>(w.n_tile) * p.st_total + sti) * p.stage_bytes;
-          tma_bulk_g2s(smem_w + s * WPS, src, bytes, &ctl->full_w[s]);
+          const uint8_t* tile_w = p.wp + w.wp_off + static_cast<size_t>(w.n_tile) * p.st_total * p.stage_bytes;
+          if (sti + n <= p.st_total) {
+            tma_bulk_g2s(smem_w + s * WPS, tile_w + static_cast<size_t>(sti) * p.stage_bytes, bytes, &ctl->full_w[s]);
+          } else {
+            // the pair reaches the extra stage past the tile's end: the last real stage stands in for it
+            for (int j = 0; j < n; ++j) {
+              const int real = min(sti + j, p.st_total - 1);
+              tma_bulk_g2s(smem_w + s * WPS + j * p.stage_bytes, tile_w + static_cast<size_t>(real) * p.stage_bytes,
+                           static_cast<uint32_t>(p.stage_bytes), &ctl->full_w[s]);
+            }
+          }
         }
       }
     }
@@ -878,12 +889,12 @@ streamk_fixup_kernel(const GemmParams p) {
   constexpr int TCH = fixup_tokens_per_block(TN);
   long long units, span;
   plan_of(p, units, span);
-  if (span == 0 || span % p.st_total == 0) return;          // no tile is cut
+  if (span == 0 || span % p.st_units == 0) return;          // no tile is cut
   const long long pos = static_cast<long long>(blockIdx.x + 1) * span;
   if (pos >= units) return;
-  const long long tile = pos / p.st_total;
-  const long long t_begin = tile * p.st_total;
-  const long long t_end = t_begin + p.st_total;
+  const long long tile = pos / p.st_units;
+  const long long t_begin = tile * p.st_units;
+  const long long t_end = t_begin + p.st_units;
   if (pos == t_begin) return;                               // the cut is a tile boundary
   const int c_first = static_cast<int>(t_begin / span);
   if (static_cast<int>(blockIdx.x) != c_first) return;      // an earlier cut owns this tile
