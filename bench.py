@@ -537,7 +537,23 @@ def run_ours(args, rank, world, local_rank):
             for _ in range(n):
                 one()
             us = (time.perf_counter() - t0) / n * 1e6
-            e2e_small[f"M={m}"] = {"us_per_call": us, "gbs": algorithmic_bytes(m, N_FULL, K_FULL, GROUP) / us / 1e3,
+            # the same step (copy in, GEMM, copy out) as one CUDA graph launch per call
+            replay, _ = km.capture(a_dev, qB, s, z, before=lambda: a_dev.copy_(a_pin, non_blocking=True),
+                                   after=lambda o: c_pin.copy_(o, non_blocking=True))
+
+            def one_graph():
+                replay()
+                torch.cuda.current_stream(dev).synchronize()
+                return float(c_pin[0, 0])
+
+            for _ in range(5):
+                one_graph()
+            t0 = time.perf_counter()
+            for _ in range(n):
+                one_graph()
+            us_graph = (time.perf_counter() - t0) / n * 1e6
+            e2e_small[f"M={m}"] = {"us_per_call": us, "us_per_call_cuda_graph": us_graph,
+                                   "gbs": algorithmic_bytes(m, N_FULL, K_FULL, GROUP) / us / 1e3,
                                    "h2d_bytes": m * K_FULL * 2, "d2h_bytes": m * n_local * 2,
                                    "note": "one synchronous call at a time: host launch path and copies included"}
 

@@ -390,6 +390,27 @@ def test_nf4_codebook_weights(M, N, K, dtype):
     tb.check_status()
 
 
+def test_kernel_call_captured_in_a_cuda_graph():
+    """A decode step (copy in, GEMM, copy out) captured once and replayed on new input values."""
+    M, N, K, group = 4, 1024, 1024, 128
+    A = torch.randn(M, K, generator=gen(11)).to(torch.bfloat16)
+    qB = torch.randint(0, 256, (N, K // 2), generator=gen(12), dtype=torch.uint8)
+    s = (torch.rand(N, K // group, generator=gen(13)) * 0.015 + 0.005).to(torch.bfloat16)
+    z = (torch.rand(N, K // group, generator=gen(14)) * 4 + 6).to(torch.bfloat16)
+    kernel = tb.matmul(M, N, K, "bfloat16", "bfloat16", "float32", num_bits=4, group_size=group, with_zeros=True)
+    a_pin, c_pin = A.clone().pin_memory(), torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    a_dev = torch.empty(M, K, dtype=torch.bfloat16, device=DEV)
+    qB_d, s_d, z_d = qB.to(DEV), s.to(DEV), z.to(DEV)
+    replay, out = kernel.capture(a_dev, qB_d, s_d, z_d, before=lambda: a_dev.copy_(a_pin, non_blocking=True),
+                                 after=lambda o: c_pin.copy_(o, non_blocking=True))
+    for scale in (1.0, -2.0):
+        a_pin.copy_((A.float() * scale).to(torch.bfloat16))
+        replay()
+        torch.cuda.synchronize()
+        check_float(c_pin, R.ref_w4a16(a_pin, qB, s, z, group, torch.bfloat16))
+    tb.check_status()
+
+
 def test_dequantize_gemv_reference_flow():
     # example_dequant_gemv_fp16xint4.py:158-217: weights pre-permuted by interleave_weight
     M, N, K = 1, 1024, 1024

@@ -84,6 +84,34 @@ class DequantKernel:
         return self._description
 
     # -- library extras ------------------------------------------------------
+    def capture(self, *inputs, before=None, after=None, warmup: int = 2):
+        """One call on these (static) input tensors captured in a CUDA graph: returns
+        ``(replay, outputs)`` where ``replay()`` re-launches the captured work on the current
+        stream and ``outputs`` is what the call returned (the same tensors every replay).
+        ``before()`` / ``after(outputs)`` run inside the capture too -- e.g. the copies from and to
+        pinned host buffers of a decode step -- so a whole step is one graph launch instead of
+        several kernel launches behind the Python call path. The weights are packed and the
+        scratch is grown by the warm-up calls, outside the capture."""
+        def step():
+            if before is not None:
+                before()
+            out = self(*inputs)
+            if after is not None:
+                after(out)
+            return out
+
+        for _ in range(max(1, warmup)):
+            step()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                outputs = step()
+        torch.cuda.current_stream().wait_stream(side)
+        return graph.replay, outputs
+
     def pack(self, *weight_tensors) -> ops.PackedWeight:
         """Repack the weight tensors into the device layout now (otherwise done on first call)."""
         return self._packed(*weight_tensors)
