@@ -199,3 +199,30 @@ def test_bitlinear_is_a_module_with_the_reference_quantisers():
     W_t = (w * s).round().clamp(-1, 1)
     q, scale = R.bitnet_weight_quant(w)
     assert torch.equal(W_t.to(torch.int8), q.to(torch.int8)) and abs(float(scale) - float(s)) < 1e-6
+
+
+def test_scalar_decode_rules():
+    """The per-element helpers: fp8 against torch's own float8 dtypes (every byte), integer fields
+    against plain arithmetic."""
+    every = torch.arange(256, dtype=torch.uint8)
+    want = every.view(torch.float8_e4m3fn).to(torch.float16)
+    got = quantize.u8_to_f8_e4m3_to_f16(every)
+    nan = torch.isnan(want)
+    assert torch.equal(torch.isnan(got), nan) and torch.equal(got[~nan], want[~nan])
+    want = every.view(torch.float8_e5m2).to(torch.float16)
+    got = quantize.u8_to_f8_e5m2_to_f16(every)
+    nan = torch.isnan(want)
+    assert torch.equal(torch.isnan(got), nan) and torch.equal(got[~nan], want[~nan])
+    word = torch.tensor([0b11100100], dtype=torch.uint8)                    # fields 0, 1, 2, 3 of 2 bits
+    pos = torch.arange(4)
+    assert quantize.packed_to_unsigned(word, 2, pos, torch.int32).tolist() == [0, 1, 2, 3]
+    assert quantize.packed_to_signed(word, 2, pos, torch.int32).tolist() == [-2, -1, 0, 1]
+    assert quantize.packed_int_to_int(word, 2, pos, torch.int32).tolist() == [0, 1, -2, -1]
+    assert quantize.packed_to_unsigned_with_zeros(word, 2, pos, 1, torch.int32).tolist() == [-1, 0, 1, 2]
+    w32 = torch.tensor([0x76543210 - (1 << 32) if 0x76543210 >= 1 << 31 else 0x76543210], dtype=torch.int32)
+    assert quantize.packed_to_unsigned(w32, 4, torch.arange(8), torch.int32).tolist() == list(range(8))
+    assert quantize.packed_int_to_int(torch.tensor([-1], dtype=torch.int32), 4, torch.arange(8), torch.int32).tolist() == [-1] * 8
+    codes = torch.tensor([0x0F], dtype=torch.uint8)                          # low nibble s=1 e=7, high nibble 0
+    assert quantize.packed_to_fp4_e3m0_to_f16(codes, torch.arange(2)).tolist() == [-1.0, 0.0]
+    assert quantize.packed_to_fp4_e3m0_to_f16(torch.tensor([0x01], dtype=torch.uint8), 0).item() == 2.0 ** -6
+

@@ -159,3 +159,76 @@ def from_awq(qweight: torch.Tensor, scales: torch.Tensor, qzeros: torch.Tensor, 
     zeros = _unpack_int32_fields(qzeros, bits, _AWQ_ORDER)        # (groups, N)
     qB = compress_codes(codes.t().contiguous().to(torch.uint8), bits)
     return qB, scales.t().contiguous(), zeros.t().contiguous().to(torch.uint8)
+
+
+# ---------------------------------------------------------------------------
+# scalar decode rules: element-wise restatements, on torch tensors, of the per-element helpers
+# the reference's dequantise kernels are generated from
+# (examples/dequantize_gemm/quantize/quantization.py). ``val`` holds storage words (uint8 /
+# int8 / int32), ``pos`` the index of the field inside the word; every function is a pure tensor
+# expression (any device). The device kernels implement the same rules on whole chunks.
+# ---------------------------------------------------------------------------
+
+def _field(val: torch.Tensor, nbit: int, pos) -> torch.Tensor:
+    bits = val.element_size() * 8
+    word = val.to(torch.int64) & ((1 << bits) - 1)
+    return (word >> (torch.as_tensor(pos, device=val.device).to(torch.int64) * nbit)) & ((1 << nbit) - 1)
+
+
+def packed_to_unsigned(val: torch.Tensor, nbit: int, pos, dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """Field ``pos`` of ``nbit`` bits, read unsigned (``_tir_packed_to_unsigned_convert``, :310-318)."""
+    return _field(val, nbit, pos).to(dtype)
+
+
+def packed_to_unsigned_with_zeros(val: torch.Tensor, nbit: int, pos, zero, dtype: torch.dtype = torch.float16):
+    """The unsigned field minus an integer zero-point (``..._convert_with_zeros``, :321-330)."""
+    return (_field(val, nbit, pos) - torch.as_tensor(zero, device=val.device).to(torch.int64)).to(dtype)
+
+
+def packed_to_signed(val: torch.Tensor, nbit: int, pos, dtype: torch.dtype = torch.float16) -> torch.Tensor:
+    """The field minus 2^(nbit-1): offset-binary storage (``_tir_packed_to_signed_convert``, :298-307)."""
+    return (_field(val, nbit, pos) - (1 << (nbit - 1))).to(dtype)
+
+
+def packed_int_to_int(val: torch.Tensor, nbit: int, pos, dtype: torch.dtype = torch.int8) -> torch.Tensor:
+    """The field sign-extended: two's-complement storage (``_tir_packed_int_to_int_convert``,
+    :333-343; ``_tir_u32_to_int_to_float``, :111-117, is the same with a float target)."""
+    f = _field(val, nbit, pos)
+    return torch.where(f >= (1 << (nbit - 1)), f - (1 << nbit), f).to(dtype)
+
+
+def _f16_from_bits(bits: torch.Tensor) -> torch.Tensor:
+    b = bits.to(torch.int32) & 0xFFFF
+    return torch.where(b >= 0x8000, b - 0x10000, b).to(torch.int16).view(torch.float16)
+
+
+def u8_to_f8_e4m3_to_f16(val: torch.Tensor) -> torch.Tensor:
+    """A byte read as fp8 e4m3 (fn: no infinities, 0x7f / 0xff are NaN) -> float16, by the bit
+    manipulation of ``_tir_u8_to_f8_e4m3_to_f16`` (:250-275): the 7 low bits shifted into place
+    with the exponent re-biased (8 added), subnormals (mantissa * 2^-9) normalised by hand."""
+    v = val.view(torch.uint8).to(torch.int32)
+    sign = (v >> 7) << 15
+    e4 = v & 0x40
+    normal = ((((v & 63) << 7) | (e4 << 8) | (e4 << 7)) ^ 0x2000)
+    m = v & 7
+    sub = torch.where(m >= 4, 0x2000 | ((m & 3) << 8),
+                      torch.where(m >= 2, 0x1C00 | ((m & 1) << 9), torch.where(m == 1, torch.full_like(m, 0x1800),
+                                                                              torch.zeros_like(m))))
+    mag = torch.where((v & 0x78) == 0, sub, torch.where((v & 0x7F) == 0x7F, torch.full_like(v, 0x7E00), normal))
+    return _f16_from_bits(sign | mag)
+
+
+def u8_to_f8_e5m2_to_f16(val: torch.Tensor) -> torch.Tensor:
+    """A byte read as fp8 e5m2 -> float16: e5m2 is the high byte of the float16 with the same value
+    (``_tir_u8_to_f8_e5m2_to_f16``, :278-281)."""
+    return _f16_from_bits(val.view(torch.uint8).to(torch.int32) << 8)
+
+
+def packed_to_fp4_e3m0_to_f16(val: torch.Tensor, pos, nbit: int = 4) -> torch.Tensor:
+    """The reference's sign + 3-bit-exponent 4-bit float (``_tir_packed_to_fp4_to_f16``, :206-221):
+    0 for exponent 0, else +-2^(e - 7) (exponent field e + 8 of a float16 with zero mantissa)."""
+    f4 = _field(val, nbit, pos).to(torch.int32)
+    s, e = f4 >> 3, f4 & 7
+    bits = ((e | 8) | (s << 5)) << 10
+    return torch.where(e == 0, torch.zeros((), dtype=torch.float16, device=val.device), _f16_from_bits(bits))
+
