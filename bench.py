@@ -371,7 +371,7 @@ def other_configs(dev, peaks):
             packs.append(ops.pack_w4a16(q, sc, None, n, k, g, torch.bfloat16))
         return ops.stack_packed(packs)
 
-    mlp = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1), pack_experts(H, F, 2), token_tile=256)
+    mlp = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1), pack_experts(H, F, 2))
     x = torch.randn(cfg["tokens"], H, generator=gen(77)).to(torch.bfloat16).to(dev)
     logits = torch.randn(cfg["tokens"], E, generator=gen(78)).to(dev)
     ms = time_rotating(lambda i: moe.moe_forward(x, logits, cfg["top_k"], E, mlp), 1, rounds=10)
@@ -748,7 +748,7 @@ def moe_measure(steps, warmup, rank, world, local_rank, compare_single=False):
         return e0.elapsed_time(e1) / steps
 
     mine = moe.expert_ranges(E, world)[rank]
-    mlp = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1, mine), pack_experts(H, F, 2, mine), token_tile=256)
+    mlp = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1, mine), pack_experts(H, F, 2, mine))
     t_local = c["tokens"] // world
     gen = torch.Generator().manual_seed(77 + rank)
     x = torch.randn(t_local, H, generator=gen).to(torch.bfloat16).to(dev)
@@ -767,7 +767,7 @@ def moe_measure(steps, warmup, rank, world, local_rank, compare_single=False):
     ms_single = 0.0
     if compare_single and world > 1:
         del mlp
-        full = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1, range(E)), pack_experts(H, F, 2, range(E)), token_tile=256)
+        full = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1, range(E)), pack_experts(H, F, 2, range(E)))
         xf = torch.randn(c["tokens"], H, generator=gen).to(torch.bfloat16).to(dev)
         lf = torch.randn(c["tokens"], E, generator=gen).to(dev)
         ms_single = timed(lambda: moe.moe_forward(xf, lf, c["top_k"], E, full))

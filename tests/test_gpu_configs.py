@@ -222,7 +222,7 @@ def test_c5_moe_layer_64_experts_top6(c5_experts):
     T, k = 16384, 6
     x = torch.randn(T, H, generator=gen(5)).to(torch.bfloat16)
     logits = torch.randn(T, E, generator=gen(6))
-    mlp = moe.make_gpu_expert_mlp(w1_p, w2_p, token_tile=256)
+    mlp = moe.make_gpu_expert_mlp(w1_p, w2_p)
     out = moe.moe_forward(x.to(DEV), logits.to(DEV), k, E, mlp)
     tb.check_status()
     ref = R.ref_moe_w4a16(x, logits, k, w1_q, w1_s, w2_q, w2_s, group)

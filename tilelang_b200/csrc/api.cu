@@ -102,6 +102,7 @@ int token_tile_for(int M) {
 struct Schedule {
   int tn, m_tiles, n_tiles, st_total, grid, span;
   int st_units;   // stages the schedule gives a tile: st_total, or one more (see make_schedule)
+  bool whole_tiles;   // spans are whole tiles by construction (narrow tiles on tall problems)
   long long units;
   size_t workspace_bytes, slot_bytes;
   bool needs_scratch;   // some tile is cut between CTAs
@@ -154,7 +155,8 @@ int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_cta
   // dequant groups, four-stage rings) lost a hand-off now and then under full load -- a bounded wait
   // gave up -- and its cause is not understood; short spans have not shown it. Whole tiles also need
   // no scratch and no fix-up pass, and the imbalance of whole-tile waves is about 1 % at this size.
-  if (s->tn <= 128 && tile_kernel && max_ctas <= 0 && tiles >= 16LL * cap) s->span = 8 * s->st_units;
+  s->whole_tiles = s->tn <= 128 && tile_kernel && max_ctas <= 0 && tiles >= 16LL * cap;
+  if (s->whole_tiles) s->span = 8 * s->st_units;
   s->grid = static_cast<int>((s->units + s->span - 1) / s->span);
   // two partial-tile slots per CTA, then one 64-bit arrival counter per tile (small-M kernel)
   s->slot_bytes = static_cast<size_t>(s->grid) * 2 * s->tn * kTileRows * sizeof(uint32_t);
@@ -408,7 +410,9 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   const long long plan_tiles = grouped ? (dyn ? -static_cast<long long>(a->total_tiles) : a->total_tiles) : -1;
   if (make_schedule(a->M, a->N, a->K, act, skinny ? kSkinnyTokens : a->token_tile, a->max_ctas, sm_count, &s,
                     plan_tiles, !skinny) != 0) return -1;
-  if (dyn && s.grid > 1) s.needs_scratch = true;
+  // device-planned: the kernel cuts the real total evenly, so tiles are cut unless the spans are
+  // rounded up to whole tiles (the narrow-tile rule above; the grid was sized for the bound)
+  if (dyn && s.grid > 1) s.needs_scratch = !s.whole_tiles;
   if (s.needs_scratch) {
     if (scratch == nullptr || scratch_bytes < s.workspace_bytes)
       return fail("%s: workspace too small: need %zu bytes, got %zu", who, s.workspace_bytes, scratch_bytes);
@@ -449,6 +453,7 @@ int run_gemm(const char* who, const b200dq_gemm_args* a, void* scratch, size_t s
   p.tn = s.tn;
   p.num_groups = grouped ? a->num_groups : 0;
   p.dyn_grid = dyn ? s.grid : 0;
+  p.dyn_whole = (dyn && s.whole_tiles) ? 1 : 0;
   if (wf == WF_LUT4_S) {
     // the table in the activation dtype, low and high bytes apart
     for (int i = 0; i < 16; ++i) {

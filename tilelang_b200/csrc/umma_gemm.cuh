@@ -118,6 +118,7 @@ struct GemmParams {
   uint32_t lut_lo[4], lut_hi[4];
   unsigned long long* tile_ctr;
   unsigned long long epoch;
+  int dyn_whole;                 // device-planned spans are rounded up to whole tiles (no tile is cut)
   int dyn_grid;                  // > 0: grouped mode planned on the device -- the tile total is read from
                                  // grp_tile_prefix[num_groups] and cut evenly over dyn_grid CTAs (span, units unused)
   int tn;                        // tokens per tile (the kernel's TN)
@@ -234,6 +235,7 @@ __device__ __forceinline__ void plan_of(const GemmParams& p, long long& units, l
   if (p.dyn_grid > 0) {
     units = static_cast<long long>(p.grp_tile_prefix[p.num_groups]) * p.st_units;
     span = (units + p.dyn_grid - 1) / p.dyn_grid;
+    if (p.dyn_whole) span = (span + p.st_units - 1) / p.st_units * p.st_units;
   } else {
     units = p.units;
     span = p.span;

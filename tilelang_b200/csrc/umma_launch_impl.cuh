@@ -29,7 +29,7 @@ cudaError_t launch_umma_instance(const CUtensorMap& tmap, const GemmParams& p, i
   kernel<<<grid, kThreads, Ring::kSmemBytes, stream>>>(tmap, p);
   UMMA_OK(cudaGetLastError());
   // stream-K second pass: one block column per cut between neighbouring CTAs
-  if ((p.dyn_grid > 0 || p.span % p.st_units != 0) && grid > 1) {
+  if (((p.dyn_grid > 0 && !p.dyn_whole) || (p.dyn_grid == 0 && p.span % p.st_units != 0)) && grid > 1) {
     constexpr bool kInt = (ACT == ACT_I8);
     const dim3 fgrid(grid - 1, TN / fixup_tokens_per_block(TN));
     switch (p.out_type) {
