@@ -692,7 +692,11 @@ def multi_gpu_extras(args, rank, world, local_rank, A, pw, n_local, ms_plain):
                 "under the next chunk's GEMM with `spare` SMs left to NCCL's kernel. nvlink_floor_ms = bytes sent per "
                 "rank over the 770 GB/s measured per direction"}}
 
-    ms_step, ms_gemm, ms_single = moe_measure(max(5, steps // 3), 3, rank, world, local_rank, compare_single=True)
+    try:
+        ms_step, ms_gemm, ms_single = moe_measure(max(5, steps // 3), 3, rank, world, local_rank, compare_single=True)
+    except RuntimeError as e:           # raised on every rank together (see moe_measure: healthy())
+        out["moe_ep"] = {"unavailable": str(e)[:200]}
+        return out
     fl = moe_flops()
     out["moe_ep"] = {
         "value": fl / ms_step / 1e9, "unit": "TFLOPS", "ms_per_step": ms_step, "ms_grouped_gemms_only": ms_gemm,
@@ -735,8 +739,27 @@ def moe_measure(steps, warmup, rank, world, local_rank, compare_single=False):
             dist.barrier()
         torch.cuda.synchronize()
 
+    class DeviceFault(RuntimeError):
+        pass
+
+    def healthy():
+        """False on every rank as soon as any rank's status word reports a wait that gave up: a
+        measurement on a faulted pipeline would crawl from one 2-second limit to the next."""
+        ok = 1
+        try:
+            ops.check_status(dev)
+        except Exception:
+            ok = 0
+        flag = torch.tensor([ok], dtype=torch.int32, device=dev)
+        if world > 1:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        return int(flag.item()) == 1
+
     def timed(fn):
-        for _ in range(max(warmup, 3)):
+        fn()
+        if not healthy():
+            raise DeviceFault("a bounded wait gave up in the first call")
+        for _ in range(max(warmup, 3) - 1):
             fn()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         barrier()
@@ -748,7 +771,10 @@ def moe_measure(steps, warmup, rank, world, local_rank, compare_single=False):
         return e0.elapsed_time(e1) / steps
 
     mine = moe.expert_ranges(E, world)[rank]
-    mlp = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1, mine), pack_experts(H, F, 2, mine))
+    # expert-parallel runs keep the 256-token tile for every grouped GEMM of the measurement (a rank's
+    # share of the rows is too small for the whole-tile schedule of the 128-token tile)
+    tile = None if world == 1 else 256
+    mlp = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1, mine), pack_experts(H, F, 2, mine), token_tile=tile)
     t_local = c["tokens"] // world
     gen = torch.Generator().manual_seed(77 + rank)
     x = torch.randn(t_local, H, generator=gen).to(torch.bfloat16).to(dev)
@@ -757,7 +783,8 @@ def moe_measure(steps, warmup, rank, world, local_rank, compare_single=False):
         ms_step = timed(lambda: moe.moe_forward(x, logits, c["top_k"], E, mlp))
     else:
         ms_step = timed(lambda: moe.moe_forward_ep(x, logits, c["top_k"], E, mlp))
-    ops.check_status(dev)
+    if not healthy():
+        raise DeviceFault("a bounded wait gave up during the layer's timed steps")
 
     # the two grouped GEMMs alone, on this rank's share of evenly routed rows
     rows = c["tokens"] * c["top_k"] // world
@@ -767,10 +794,12 @@ def moe_measure(steps, warmup, rank, world, local_rank, compare_single=False):
     ms_single = 0.0
     if compare_single and world > 1:
         del mlp
-        full = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1, range(E)), pack_experts(H, F, 2, range(E)))
+        full = moe.make_gpu_expert_mlp(pack_experts(2 * F, H, 1, range(E)), pack_experts(H, F, 2, range(E)), token_tile=tile)
         xf = torch.randn(c["tokens"], H, generator=gen).to(torch.bfloat16).to(dev)
         lf = torch.randn(c["tokens"], E, generator=gen).to(dev)
         ms_single = timed(lambda: moe.moe_forward(xf, lf, c["top_k"], E, full))
+    if not healthy():
+        raise DeviceFault("a bounded wait gave up during the grouped-GEMM or single-GPU steps")
     t = torch.tensor([ms_step, ms_gemm, ms_single], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
