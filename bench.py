@@ -132,6 +132,44 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+EXTRAS_LIMIT_S = 300
+
+
+class LineGuard:
+    """Owns the one JSON line of a multi-rank run while optional measurements are still running.
+
+    ``emit`` prints a line once. If nothing has been emitted ``limit_s`` seconds after
+    construction, the timer prints ``fallback`` (the line measured so far, on the rank that
+    holds one) with ``missing`` merged in, and ends the process with exit code 0 on every rank:
+    a rank that waits in a collective for a peer that gave up would otherwise wait for the
+    process group's own timeout, far beyond the run's budget, and the run would report nothing."""
+
+    def __init__(self, limit_s, fallback, missing):
+        self._lock = threading.Lock()
+        self._emitted = False
+        self._fallback, self._missing = fallback, missing
+        self._timer = threading.Timer(limit_s, self._expire)
+        self._timer.daemon = True
+        self._timer.start()
+
+    def emit(self, line):
+        with self._lock:
+            if self._emitted:
+                return False
+            self._emitted = True
+            sys.stdout.write(json.dumps(line) + "\n")
+            sys.stdout.flush()
+            return True
+
+    def _expire(self):
+        if self._fallback is not None:
+            late = dict(self._fallback)
+            late.update(self._missing)
+            self.emit(late)
+        sys.stdout.flush()
+        os._exit(0)
+
+
 def time_rotating(call, n_variants, rounds=6):
     """Milliseconds per call of ``call(i)``, i cycling over ``n_variants`` input sets that
     together exceed the L2, timed as one back-to-back loop (CUDA events on the launching
@@ -488,12 +526,57 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_value = flops * args.steps / t.item() / 1e12
 
-    # ---- what the other ranks take part in: the gather of C and the expert-parallel layer ----
-    multi = {}
-    if world > 1:
-        multi = multi_gpu_extras(args, rank, world, local_rank, A, pw, n_local, ms_step)
+    def line(sweep, configs, e2e_small, cpu):
+        """The JSON line of this run from what has been measured so far."""
+        traffic = load_traffic_note(M)
+        if M <= 16:
+            # decode shapes: the small-M kernel streams every weight byte once, HBM-bound
+            gbs = algorithmic_bytes(M, N_FULL // world, K_FULL, GROUP) / ms_step / 1e6
+            roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                        "frac": gbs / peaks["hbm_gbs"], "traffic": traffic.get("dram_bytes_per_launch"),
+                        "peak_source": f"{peaks['source']} copy bandwidth",
+                        "frac_of_nominal_8tbs": gbs / 8000.0,
+                        "kernel": f"skinny_dequant_gemm_kernel<{1 if M <= 8 else 2}, U4_SZ, BF16>; "
+                                  "duration = step time (one launch: cut tiles are finished inside the kernel)",
+                        "traffic_source": traffic.get("source")}
+        else:
+            tile = 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+            roofline = {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                        "frac": value / world / peaks["bf16_tflops"], "traffic": traffic.get("dram_bytes_per_launch"),
+                        "peak_source": f"{peaks['source']} burst bf16 (sustained {peaks['bf16_tflops_sustained']})",
+                        "frac_of_sustained": value / world / peaks["bf16_tflops_sustained"],
+                        "kernel": f"umma_dequant_gemm_kernel<{tile}, U4_SZ, BF16>; duration = step time (GEMM + fix-up pass)",
+                        "traffic_source": traffic.get("source")}
+        return {
+            "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": workload_config(M, world, args.allgather),
+            "roofline": roofline,
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "TFLOPS", "h2d_bytes_per_step": M * K_FULL * 2 * world,
+                    "d2h_bytes_per_step": M * N_FULL * 2,
+                    "note": "activations from pinned host memory and result back to it every step; packed weights resident"},
+            "gpu_launches": launches_per_step * args.steps * world,
+            "clocks": clocks.summary(),
+            "sweep": sweep,
+            "configs": configs,
+            "e2e_small": e2e_small,
+        }
 
-    if rank != 0:
+    # ---- what the other ranks take part in: the gather of C and the expert-parallel layer ----
+    if world > 1:
+        # The headline is already measured: a collective that never returns must not lose it.
+        guard = LineGuard(EXTRAS_LIMIT_S, line({}, {}, {}, None) if rank == 0 else None,
+                          {"with_allgather": {"unavailable": f"the multi-GPU measurements did not return in {EXTRAS_LIMIT_S} s"}})
+        try:
+            multi = multi_gpu_extras(args, rank, world, local_rank, A, pw, n_local, ms_step)
+        except Exception as e:      # the headline stands; a rank left waiting for this one is ended by the guard
+            multi = {"with_allgather": {"unavailable": f"{type(e).__name__}: {e}"[:300]}}
+        if rank == 0:
+            out = line({}, {}, {}, None)
+            out.update(multi)
+            guard.emit(out)
         return
 
     # ---- the rest of the configuration's M sweep, single GPU numbers -----------------
@@ -563,43 +646,7 @@ def run_ours(args, rank, world, local_rank):
         v, _, sample = cpu_reference_run(M, threads, steps=5, warmup=1)
         cpu = {"value": v, "unit": "TFLOPS", "cores": threads, "kind": "port", "sample": sample}
 
-    traffic = load_traffic_note(M)
-    if M <= 16:
-        # decode shapes: the small-M kernel streams every weight byte once, HBM-bound
-        gbs = algorithmic_bytes(M, N_FULL // world, K_FULL, GROUP) / ms_step / 1e6
-        roofline = {"bound": "hbm", "achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": gbs / peaks["hbm_gbs"], "traffic": traffic.get("dram_bytes_per_launch"),
-                    "peak_source": f"{peaks['source']} copy bandwidth",
-                    "frac_of_nominal_8tbs": gbs / 8000.0,
-                    "kernel": f"skinny_dequant_gemm_kernel<{1 if M <= 8 else 2}, U4_SZ, BF16>; "
-                              "duration = step time (one launch: cut tiles are finished inside the kernel)",
-                    "traffic_source": traffic.get("source")}
-    else:
-        tile = 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
-        roofline = {"bound": "tensor", "achieved": value / world, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": value / world / peaks["bf16_tflops"], "traffic": traffic.get("dram_bytes_per_launch"),
-                    "peak_source": f"{peaks['source']} burst bf16 (sustained {peaks['bf16_tflops_sustained']})",
-                    "frac_of_sustained": value / world / peaks["bf16_tflops_sustained"],
-                    "kernel": f"umma_dequant_gemm_kernel<{tile}, U4_SZ, BF16>; duration = step time (GEMM + fix-up pass)",
-                    "traffic_source": traffic.get("source")}
-    out = {
-        "metric": METRIC, "value": value, "unit": "TFLOPS", "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(M, world, args.allgather),
-        "roofline": roofline,
-        "cpu_baseline": cpu,
-        "e2e": {"value": e2e_value, "unit": "TFLOPS", "h2d_bytes_per_step": M * K_FULL * 2 * world,
-                "d2h_bytes_per_step": M * N_FULL * 2,
-                "note": "activations from pinned host memory and result back to it every step; packed weights resident"},
-        "gpu_launches": launches_per_step * args.steps * world,
-        "clocks": clocks.summary(),
-        "sweep": sweep,
-        "configs": configs,
-        "e2e_small": e2e_small,
-    }
-    out.update(multi)
-    print(json.dumps(out))
+    print(json.dumps(line(sweep, configs, e2e_small, cpu)))
 
 
 def multi_gpu_extras(args, rank, world, local_rank, A, pw, n_local, ms_plain):
@@ -702,7 +749,9 @@ def multi_gpu_extras(args, rank, world, local_rank, A, pw, n_local, ms_plain):
         "value": fl / ms_step / 1e9, "unit": "TFLOPS", "ms_per_step": ms_step, "ms_grouped_gemms_only": ms_gemm,
         "ms_routing_and_all_to_all": ms_step - ms_gemm, "ms_same_layer_one_gpu": ms_single,
         "efficiency_vs_one_gpu": ms_single / (world * ms_step) if ms_step > 0 else None,
-        "config": "64 experts over the ranks, 16384 tokens, top-6; two all_to_all_single per step"}
+        "config": "64 experts over the ranks, 16384 tokens, top-6; two all_to_all_single per step; every grouped GEMM "
+                  "here, the one-GPU layer included, on 256-token tiles (--workload moe measures the one-GPU layer on "
+                  "the tile it picks itself)"}
     return out
 
 
