@@ -154,7 +154,10 @@ struct RingConfig {
   static constexpr int kNI = issuers_for(TN);
   static constexpr int kGB = group_kblocks_for(TN);
   static constexpr int kAccCols = ((kNI * TN + 31) / 32) * 32;
-  static constexpr int kSlots = (512 - kAccCols) / 32 > 14 ? 14 : (512 - kAccCols) / 32;
+  // Ring depth in stages (kSlots / 2) is even: stage g then always returns to a `cons` barrier that
+  // stages of its own parity -- its own issuer and dequant group -- used before, so both see every
+  // phase of the barriers they wait on.
+  static constexpr int kSlots = (512 - kAccCols) / 32 >= 12 ? 12 : 8;
   static constexpr int kBSlabBytes = TN * 128;                                // one k-block of activations
   static constexpr int kBGroupBytes = kGB * kBSlabBytes;
   // With two independent issuers (kNI == 2) the ring depth is even: when K is ragged the
@@ -171,7 +174,7 @@ struct RingConfig {
   static constexpr int kNWPfit = (232448 - kFixed) / kWPairSmem;
   static constexpr int kNWP = kNWPfit > 8 ? 8 : kNWPfit;
   static constexpr int kSmemBytes = kFixed + kNWP * kWPairSmem;
-  static_assert(kSlots >= 8 && kSlots <= kMaxSlots && kSlots % 2 == 0, "TMEM ring depth");
+  static_assert(kSlots >= 8 && kSlots <= kMaxSlots && kSlots % 4 == 0 && kAccCols + kSlots * 32 <= 512, "TMEM ring depth");
   static_assert(kGB > 1 || (kNI == 1 && kNBG <= kSlots), "single-k-block groups reuse the cons barriers");
   static_assert(kGB != 2 || 2 * kNBG <= kSlots, "two-k-block groups reuse the cons barriers");
   static_assert(kNI == 1 || kNBG % 2 == 0, "two issuers need an even activation ring");
@@ -541,11 +544,13 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
           ok &= mbar_wait(&ctl->a_full[sa], pa, abort_flag, st, 4);
           ok &= mbar_wait(&ctl->full_b[sb0], (grp0 / NBG) & 1u, abort_flag, st, 5);
           if (grp1 != grp0) ok &= mbar_wait(&ctl->full_b[sb1], (grp1 / NBG) & 1u, abort_flag, st, 5);
-          if (i < NI) ok &= mbar_wait(&ctl->acc_empty, (tc & 1u) ^ 1u, abort_flag, st, 3);   // my first stage here
+          // `turn` before `acc_empty`: with one-stage tiles an issuer looks at acc_empty only every other
+          // phase, and only the other issuer's hand-over tells it that the phase in between is complete
           if (NI == 1 && !first_ever) {
             ok &= mbar_wait(&ctl->turn[me], my_turns & 1u, abort_flag, st, 9);
             ++my_turns;
           }
+          if (i < NI) ok &= mbar_wait(&ctl->acc_empty, (tc & 1u) ^ 1u, abort_flag, st, 3);   // my first stage here
           tc_fence_after_sync();
           if (ok) {
 #pragma unroll
@@ -590,23 +595,32 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
       }
     }
   } else if (warp >= 4 && warp < 12) {
-    // ---------------- dequant warpgroups: group d takes stage d of every pair ----
+    // ---------------- dequant warpgroups: one stage of every pair each ----
+    // Group dg takes the stages whose CTA-wide index has parity dg, i.e. always the stages of
+    // issuer dg, whose `cons` barriers it therefore sees in every phase. (Taking "stage dg of
+    // the pair" instead swaps the groups between the issuers after every segment with an odd
+    // number of stages; a group then meets a `cons` barrier it last saw two phases ago, and
+    // if its new issuer is a stage behind, the parity test answers "complete" for the phase
+    // before the one it means: the group overwrites operands the MMA has not read.)
     const int dg = (warp - 4) >> 2;
     const int quarter = warp & 3;
     const int row_in_tile = quarter * 32 + lane;
     const uint32_t lane_addr = static_cast<uint32_t>(quarter * 32) << 16;
     uint32_t wc = 0;   // weight pairs seen by this CTA
     uint32_t kc0 = 0;  // global index of the first k-block of the current pair
+    uint32_t g0_d = 0; // stages of this CTA before the current segment
     bool ok = true;
     SegmentWalk walk(p);
     Segment w;
     while (walk.next(p, w)) {
+      const int d = dg ^ static_cast<int>(g0_d & 1u);   // my place in this segment's pairs
+      g0_d += static_cast<uint32_t>(w.st_end - w.st_begin);
       for (int sti = w.st_begin; sti < w.st_end; sti += 2, ++wc) {
         const int n = min(2, w.st_end - sti);
         const uint32_t sw = wc % NWP;
         ok &= mbar_wait(&ctl->full_w[sw], (wc / NWP) & 1, abort_flag, st, 6);
-        const bool mine = dg < n;
-        const uint8_t* stage = smem_w + sw * WPS + dg * p.stage_bytes;
+        const bool mine = d < n;
+        const uint8_t* stage = smem_w + sw * WPS + d * p.stage_bytes;
         constexpr int CH = CPK / 2048;            // 16-byte chunks per row and k-block
         constexpr int RPC = 32 / CH;              // TMEM columns produced by one chunk
         if (mine) {
@@ -622,7 +636,7 @@ umma_dequant_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const GemmP
 #pragma unroll
           for (int it = 0; it < 2 * CH; ++it) {
             const int h = it / CH, q = it % CH;
-            const uint32_t kc = kc0 + dg * 2 + h;
+            const uint32_t kc = kc0 + d * 2 + h;
             const uint32_t sa = kc % NS;
             const uint4 cq = codes[it * 128 + (row_in_tile ^ chunk_swizzle(it))];
             if (it == 2 * CH - 1) {
