@@ -56,6 +56,19 @@ def test_expert_ranges_and_sorting():
     assert counts.tolist() == [2, 2, 2] and tok.tolist() == [0, 1, 0, 2, 1, 2]
 
 
+def test_token_tile_rule_of_the_expert_gemms():
+    """128-token tiles only where the schedule hands out whole tiles (16 tiles per SM and more)."""
+    # the 64-expert, top-6 layer with 16384 tokens on one GPU: 98304 rows -> both GEMMs on 128
+    assert moe.expert_token_tile(98304, 64, 2 * 1408, sms=148) == 128
+    assert moe.expert_token_tile(98304, 64, 2048, sms=148) == 128
+    # one of eight ranks of the same layer: 12288 rows over 8 experts -> 256
+    assert moe.expert_token_tile(12288, 8, 2 * 1408, sms=148) == 256
+    assert moe.expert_token_tile(12288, 8, 2048, sms=148) == 256
+    # the threshold itself: (rows // 128 + groups) * ceil(N / 128) against 16 * sms
+    assert moe.expert_token_tile(128 * 147, 1, 128 * 16, sms=148) == 128
+    assert moe.expert_token_tile(128 * 146, 1, 128 * 16, sms=148) == 256
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))

@@ -70,11 +70,13 @@ def rows_of_tokens(order: torch.Tensor, top_k: int) -> torch.Tensor:
     return inv.view(-1, top_k)
 
 
-def expert_token_tile(rows: int, num_groups: int, N: int, device=None) -> int:
+def expert_token_tile(rows: int, num_groups: int, N: int, device=None, sms: Optional[int] = None) -> int:
     """Token tile of a grouped GEMM over ``rows`` rows: 128 when the problem has so many tiles that
     the schedule hands out whole tiles in short spans (at least 16 tiles per SM: no partial tiles,
-    no fix-up pass, and an expert's ragged row count wastes half as much padding), else 256."""
-    sms = torch.cuda.get_device_properties(device if device is not None else torch.cuda.current_device()).multi_processor_count
+    no fix-up pass, and an expert's ragged row count wastes half as much padding), else 256.
+    ``sms``: the SM count, read from ``device`` when not given."""
+    if sms is None:
+        sms = torch.cuda.get_device_properties(device if device is not None else torch.cuda.current_device()).multi_processor_count
     tiles = (rows // 128 + num_groups) * ((N + 127) // 128)
     return 128 if tiles >= 16 * sms else 256
 
