@@ -318,6 +318,18 @@ def test_every_wait_sees_the_phase_it_means(tn, group_kblocks):
     assert not found, found[0]
 
 
+@pytest.mark.parametrize("tn,weight_pairs,activation_groups", [(256, 2, 5), (128, 1, 4), (128, 3, 4), (64, 2, 4), (16, 3, 4)])
+def test_other_ring_depths(tn, weight_pairs, activation_groups):
+    """Other formats have larger stages and so shallower shared-memory rings (int4 -> int8: five
+    activation groups at the 256-token tile)."""
+    def rings():
+        r = Rings(tn)
+        r.NWP, r.NBG = weight_pairs, activation_groups
+        return r
+    found = violations(rings, random_span, runs=100, seed=31 * tn + weight_pairs)
+    assert not found, found[0]
+
+
 @pytest.mark.parametrize("tn", [128, 64, 32])
 def test_many_tiles_with_an_odd_stage_count(tn):
     """The schedule that exposed the flaw: tens of short tiles per CTA, 11 stages each."""
