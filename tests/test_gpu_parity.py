@@ -182,10 +182,11 @@ def test_w4a16_stream_k_split_is_deterministic_and_matches_unsplit():
 @pytest.mark.parametrize("K,tile", [(1408, 128), (1920, 128), (1408, 64)])
 def test_narrow_tiles_with_an_odd_stage_count_over_long_spans(K, tile):
     """Explicit 128- or 64-token tiles on a tall problem: every CTA works through tens of tiles, and
-    K = 1408 / 1920 gives a tile 11 / 15 stages. With the two issuers paired to the dequant groups by
-    the parity of a CTA-wide stage count, an odd count flipped the pairing at every tile and a hand-off
-    was lost now and then (a bounded wait gave up); the schedule now rounds such tiles up to an even
-    number of stages. Checked against the oracle on the first and last rows and on the status word."""
+    K = 1408 / 1920 gives a tile 11 / 15 stages. With the dequant groups paired to the issuers by their
+    place in a weight pair, an odd count swapped the pairing at every tile and a group could pass a
+    parity wait one phase early (a bounded wait gave up now and then; tests/test_barrier_protocol.py
+    models it). The schedule rounds such tiles up to an even number of stages, and the kernel keeps
+    group and issuer together. Checked against the oracle on the first and last rows and on the status word."""
     M, N, group = 49152, 2048, 128
     A = torch.randn(M, K, generator=gen(1)).to(torch.bfloat16)
     q = torch.randint(0, 256, (N, K // 2), generator=gen(2), dtype=torch.uint8)

@@ -137,11 +137,13 @@ int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_cta
   s->st_total = stages_for(K, act_type);
   const long long tiles = grouped_tiles >= 0 ? grouped_tiles : static_cast<long long>(s->m_tiles) * s->n_tiles;
   if (tiles <= 0) return fail("no tiles to compute");
-  // Tiles of at most 128 tokens run two issuers and two dequant groups on alternate stages, paired up
-  // by the parity of a CTA-wide stage count. A tile with an odd number of stages flips that pairing
-  // at every tile boundary; with tens of such tiles per CTA a hand-off between the groups was lost
-  // now and then (a bounded wait gave up). Those tiles get one more stage: it re-reads the last real
-  // stage's weights against activations beyond K, which the tensor map fills with zeros.
+  // Tiles of at most 128 tokens run two issuers and two dequant groups on alternate stages. When the
+  // groups were still paired to the issuers by their place in a weight pair, a tile with an odd number
+  // of stages swapped the pairing at every tile boundary, and a group could pass a parity wait one
+  // phase early (with tens of such tiles per CTA a bounded wait gave up now and then). Those tiles get
+  // one more stage: it re-reads the last real stage's weights against activations beyond K, which the
+  // tensor map fills with zeros. The kernel has since been changed to keep group and issuer together
+  // by CTA-wide stage parity; the even stage count stays (it also splits a tile's stages evenly).
   s->st_units = s->st_total + ((s->tn <= 128 && tile_kernel) ? (s->st_total & 1) : 0);
   s->units = tiles * s->st_units;
   int cap = sm_count;
@@ -151,10 +153,8 @@ int make_schedule(int M, int N, int K, int act_type, int token_tile, int max_cta
   if (g > cap) g = cap;
   s->span = static_cast<int>((s->units + g - 1) / g);
   // Narrow tiles with plenty of tiles per SM: spans of eight whole tiles, in as many CTAs as that
-  // takes (they run in waves). With tens of tiles per CTA the narrow-tile pipeline (two issuers, two
-  // dequant groups, four-stage rings) lost a hand-off now and then under full load -- a bounded wait
-  // gave up -- and its cause is not understood; short spans have not shown it. Whole tiles also need
-  // no scratch and no fix-up pass, and the imbalance of whole-tile waves is about 1 % at this size.
+  // takes (they run in waves). Whole tiles need no scratch and no fix-up pass, no segment has an odd
+  // number of stages (see above), and the imbalance of whole-tile waves is about 1 % at this size.
   s->whole_tiles = s->tn <= 128 && tile_kernel && max_ctas <= 0 && tiles >= 16LL * cap;
   if (s->whole_tiles) s->span = 8 * s->st_units;
   s->grid = static_cast<int>((s->units + s->span - 1) / s->span);
